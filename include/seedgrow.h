@@ -1,0 +1,121 @@
+/* seedgrow - C ABI of the B200 (sm_100a) re-quantise / residual / rANS library.
+ *
+ * This is the boundary a host program binds with ctypes / cgo / JNI in place of the reference's
+ * kernel-launch protocol (CuPy RawModule: seedpack/gpuquant.py:206-219, 432-456; seedpack/qr.py:925-1090;
+ * its C realisation for --cpu: seedpack/cpukernels.py:270-305).
+ *
+ * Conventions
+ *   - every function returns an int status, SG_OK (0) on success; nothing throws, nothing traps;
+ *   - pointers are DEVICE pointers unless the name starts with h_;
+ *   - `device` is the CUDA ordinal that owns the buffers, `stream` a cudaStream_t (NULL = default
+ *     stream); calls enqueue work and return without synchronising unless stated otherwise;
+ *   - the caller owns every buffer; the library allocates no device memory, scratch space is passed in;
+ *   - calls on different streams may run concurrently from different host threads.
+ */
+#ifndef SEEDGROW_H
+#define SEEDGROW_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(SG_BUILD) && defined(__GNUC__)
+#define SG_API __attribute__((visibility("default")))
+#else
+#define SG_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define SG_OK             0
+#define SG_ERR_ARG        1   /* null pointer, negative size, unknown enum */
+#define SG_ERR_TYPE       2   /* ggml type (or type/variant pair) not supported */
+#define SG_ERR_SHAPE      3   /* row length not a multiple of the type's block size */
+#define SG_ERR_ALIGN      4   /* an offset breaks the 16-byte alignment the vector loads need */
+#define SG_ERR_IMATRIX    5   /* the type needs an importance matrix and none was given */
+#define SG_ERR_SCRATCH    6   /* scratch buffer missing or too small */
+#define SG_ERR_TABLES     7   /* IQ grids not installed on this device */
+#define SG_ERR_CUDA       8   /* a CUDA runtime call failed; see sg_last_cuda_error() */
+#define SG_ERR_OVERFLOW   9   /* an output slot was too small (rANS encode); retry with more */
+#define SG_ERR_CORRUPT   10   /* a coded stream ended early or decoded out of range */
+#define SG_ERR_LIMIT     11   /* a size exceeds a documented fixed maximum */
+
+/* bits a kernel may OR into the device status word (read with sg_status_fetch) */
+#define SG_ST_OFFGRID     1   /* an IQ quantiser ended on a point that is not in the grid map */
+#define SG_ST_OVERFLOW    2   /* rANS encoder ran out of slot space */
+#define SG_ST_CORRUPT     4   /* rANS decoder read past its stream */
+
+/* source element types of sg_quantize_* */
+#define SG_DT_BF16 0
+#define SG_DT_F16  1
+#define SG_DT_F32  2
+
+/* ggml type ids handled (seedpack/requant.py:21-27) */
+#define SG_Q4_0 2
+#define SG_Q4_1 3
+#define SG_Q5_0 6
+#define SG_Q5_1 7
+#define SG_Q8_0 8
+#define SG_Q2_K 10
+#define SG_Q3_K 11
+#define SG_Q4_K 12
+#define SG_Q5_K 13
+#define SG_Q6_K 14
+#define SG_IQ2_XXS 16
+#define SG_IQ2_XS 17
+#define SG_IQ3_XXS 18
+#define SG_IQ1_S 19
+#define SG_IQ4_NL 20
+#define SG_IQ3_S 21
+#define SG_IQ2_S 22
+#define SG_IQ4_XS 23
+#define SG_IQ1_M 29
+#define SG_Q2_0 42
+
+/* One tensor of a quantise / dequantise launch.  All tensors of a launch live in the same source,
+ * destination and importance buffers at these offsets.  Mirrors the per-row descriptor arrays
+ * xoff / yoff / npr / woff of the reference launch (seedpack/gpuquant.py:432-456), one record per
+ * tensor instead of one per row. */
+typedef struct sg_tensor {
+    int64_t x_off;     /* first weight, in ELEMENTS of the source buffer (multiple of 8)              */
+    int64_t y_off;     /* first output byte in the destination buffer                                 */
+    int64_t w_off;     /* first importance weight, in floats (multiple of 4); < 0 = no importance matrix */
+    int64_t n_rows;    /* rows                                                                        */
+    int64_t n_per_row; /* weights per row (multiple of the type's block size)                         */
+} sg_tensor;
+
+SG_API int sg_version(void);
+SG_API const char *sg_status_string(int status);
+/* text of the last CUDA error seen by the calling thread ("" if none) */
+SG_API const char *sg_last_cuda_error(void);
+
+/* weights per block and bytes per block of a ggml type (seedpack/requant.py:21-27); SG_ERR_TYPE if unknown */
+SG_API int sg_type_info(int ggml_type, int *qk, int *block_bytes);
+/* does quantize_<type> insist on an importance matrix (ggml-quants.c:3303, 3481, 4521, 4705, 5122) */
+SG_API int sg_type_needs_imatrix(int ggml_type);
+
+/* Device status word: kernels OR SG_ST_* bits into it instead of asserting.  Fetch synchronises the
+ * stream, returns the bits in *h_bits and clears the word. */
+SG_API int sg_status_fetch(int device, void *stream, int *h_bits);
+
+/* ---- quantisers -------------------------------------------------------------------------------
+ * Replaces k_quantize_<type>[_v1] (seedpack/gpuquant.py:206-211), i.e. llama.cpp's
+ * quantize_<type>(row, dst, 1, n_per_row, imatrix) per row (ggml-quants.c:1212 ... 5283), byte for byte.
+ * `variant` 0 = current arithmetic, 1 = older IQ1_M split search (seedpack/gpuquant.py:182-185).
+ *
+ * Scratch: the legacy importance paths (Q4_0, Q4_1, Q5_0, Q5_1 with an importance matrix) need one
+ * float per row for the row-wide mean square (ggml-quants.c:2082-2084); sg_quantize_scratch_bytes()
+ * gives the size for a launch, 0 when none is needed.  The buffer is written by the call and may be
+ * reused by the next call on the same stream. */
+SG_API size_t sg_quantize_scratch_bytes(int ggml_type, const sg_tensor *h_tensors, int n_tensors);
+SG_API int sg_quantize_tensors(int device, void *stream, int ggml_type, int variant,
+                        const void *x, int x_dtype, void *y, const float *w,
+                        const sg_tensor *h_tensors, int n_tensors,
+                        void *scratch, size_t scratch_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SEEDGROW_H */

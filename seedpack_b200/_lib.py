@@ -1,0 +1,60 @@
+"""ctypes binding of libseedgrow.so (the C ABI declared in include/seedgrow.h).
+
+There is no fallback: if the shared object is missing or a call fails, an exception is raised.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libseedgrow.so")
+
+DT_BF16, DT_F16, DT_F32 = 0, 1, 2
+
+
+class SgError(RuntimeError):
+    def __init__(self, status, where):
+        self.status = status
+        msg = lib().sg_status_string(status).decode()
+        if status == 8:
+            msg += " (" + lib().sg_last_cuda_error().decode() + ")"
+        super().__init__(f"{where}: {msg} [status {status}]")
+
+
+class sg_tensor(ctypes.Structure):
+    _fields_ = [("x_off", ctypes.c_int64), ("y_off", ctypes.c_int64), ("w_off", ctypes.c_int64),
+                ("n_rows", ctypes.c_int64), ("n_per_row", ctypes.c_int64)]
+
+
+_lib = None
+
+# name -> (restype, argtypes); every symbol include/seedgrow.h declares
+_P, _I, _Z, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_int64
+SIGNATURES = {
+    "sg_version": (_I, []),
+    "sg_status_string": (ctypes.c_char_p, [_I]),
+    "sg_last_cuda_error": (ctypes.c_char_p, []),
+    "sg_type_info": (_I, [_I, ctypes.POINTER(_I), ctypes.POINTER(_I)]),
+    "sg_type_needs_imatrix": (_I, [_I]),
+    "sg_status_fetch": (_I, [_I, _P, ctypes.POINTER(_I)]),
+    "sg_quantize_scratch_bytes": (_Z, [_I, ctypes.POINTER(sg_tensor), _I]),
+    "sg_quantize_tensors": (_I, [_I, _P, _I, _I, _P, _I, _P, _P, ctypes.POINTER(sg_tensor), _I, _P, _Z]),
+}
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m seedpack_b200.build` "
+                               "(there is no CPU or PyTorch fallback)")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            f = getattr(L, name)
+            f.restype, f.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def check(status, where):
+    if status != 0:
+        raise SgError(status, where)

@@ -1,0 +1,52 @@
+"""Type table and importance-matrix loaders (host side).
+
+Mirrors seedpack/requant.py: `QFUN` (:21-27) and `load_imatrix` / `imatrix_chunks` (:59-91) keep their
+names and meanings; the CPU quantiser binding of the reference (:114-134) has no counterpart here -
+quantisation runs on the GPU only (see gpuquant.GPUQuant).
+"""
+import struct
+
+import numpy as np
+
+# ggml type -> (function name, block elements, block bytes)
+QFUN = {2: ("quantize_q4_0", 32, 18), 3: ("quantize_q4_1", 32, 20), 6: ("quantize_q5_0", 32, 22),
+        7: ("quantize_q5_1", 32, 24), 8: ("quantize_q8_0", 32, 34), 10: ("quantize_q2_K", 256, 84),
+        11: ("quantize_q3_K", 256, 110), 12: ("quantize_q4_K", 256, 144), 13: ("quantize_q5_K", 256, 176),
+        14: ("quantize_q6_K", 256, 210), 16: ("quantize_iq2_xxs", 256, 66), 17: ("quantize_iq2_xs", 256, 74),
+        18: ("quantize_iq3_xxs", 256, 98), 19: ("quantize_iq1_s", 256, 50), 20: ("quantize_iq4_nl", 32, 18),
+        21: ("quantize_iq3_s", 256, 110), 22: ("quantize_iq2_s", 256, 82), 23: ("quantize_iq4_xs", 256, 136),
+        29: ("quantize_iq1_m", 256, 56), 42: ("quantize_q2_0", 64, 18)}
+# types whose quantiser refuses to run without an importance matrix
+NEEDS_IMATRIX = {16, 17, 19, 22, 29}
+# (type, variant) pairs beyond variant 0 (seedpack/gpuquant.py:182-185)
+VARIANTS = {29: 1}
+
+
+def load_imatrix(path_or_bytes, divide=True):
+    """llama.cpp legacy imatrix .dat -> {tensor name: float32 array}, values divided by the call
+    count as llama-quantize does (seedpack/requant.py:59-74)."""
+    buf = open(path_or_bytes, "rb").read() if isinstance(path_or_bytes, str) else path_or_bytes
+    if buf[:4] == b"GGUF":
+        raise NotImplementedError("GGUF-form imatrix files are read by the archive layer, not here")
+    (n,), pos, out = struct.unpack_from("<i", buf), 4, {}
+    for _ in range(n):
+        (ln,) = struct.unpack_from("<i", buf, pos); pos += 4
+        name = buf[pos:pos + ln].decode(); pos += ln
+        ncall, nval = struct.unpack_from("<ii", buf, pos); pos += 8
+        v = np.frombuffer(buf, np.float32, nval, pos).copy(); pos += 4 * nval
+        if divide and ncall > 0:
+            v /= np.float32(ncall)
+        out[name] = v
+    return out
+
+
+def imatrix_chunks(buf):
+    """chunk count written after the entries of a legacy .dat, None if absent (seedpack/requant.py:77-91)"""
+    try:
+        (n,), pos = struct.unpack_from("<i", buf), 4
+        for _ in range(n):
+            (ln,) = struct.unpack_from("<i", buf, pos); pos += 4 + ln
+            _, nval = struct.unpack_from("<ii", buf, pos); pos += 8 + 4 * nval
+        return struct.unpack_from("<i", buf, pos)[0] if len(buf) >= pos + 4 else None
+    except struct.error:
+        return None

@@ -1,0 +1,80 @@
+"""GPU parity: every re-quantiser against the reference's own C code (oracle/_ref), byte for byte,
+through the C ABI (seedpack_b200.gpuquant -> libseedgrow.so)."""
+import numpy as np
+import pytest
+
+from oracle import ref
+from tests import synth
+
+pytestmark = pytest.mark.gpu
+
+TYPES = sorted(ref.QFUN)
+CASES = [(t, imx) for t in TYPES for imx in ((True,) if t in ref.NEEDS_IMATRIX else (True, False))]
+
+
+@pytest.fixture(scope="module")
+def gq():
+    from seedpack_b200.gpuquant import GPUQuant
+    return GPUQuant()
+
+
+def _diff_report(t, a, b):
+    name, qk, bs = ref.QFUN[t]
+    bad = np.flatnonzero(a != b)
+    blocks = np.unique(bad // bs)
+    first = int(blocks[0])
+    return (f"{name}: {bad.size} bytes differ in {blocks.size} of {a.size // bs} blocks; first block {first}: "
+            f"byte offsets {sorted(set((bad[bad // bs == first] % bs).tolist()))[:16]}\n"
+            f"  gpu {a[first * bs:(first + 1) * bs].tolist()}\n  ref {b[first * bs:(first + 1) * bs].tolist()}")
+
+
+@pytest.mark.parametrize("t,with_imx", CASES)
+def test_quantize_matches_reference(gq, t, with_imx):
+    import torch
+    if not ref.available():
+        pytest.skip("oracle/_ref not built")
+    nrows, npr = 24, 1024
+    bits = synth.weights(nrows, npr, seed=100 + t)
+    imx = synth.imatrix(npr, seed=t) if with_imx else None
+    want = ref.quantize(t, synth.bf16_bits_to_f32(bits).reshape(nrows, npr), imx)
+    x = torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16)
+    got = gq.quantize_tensors(t, [(x.reshape(-1), npr)], [imx])[0]
+    assert gq.status() == 0
+    assert got.size == want.size
+    assert np.array_equal(got, want), _diff_report(t, np.asarray(got), want)
+
+
+@pytest.mark.parametrize("t", [8, 2, 12, 14])
+def test_source_dtypes_agree(gq, t):
+    """bf16, f16 and f32 sources holding the same values give the same bytes"""
+    import torch
+    nrows, npr = 8, 512
+    bits = synth.weights(nrows, npr, seed=5, edge_cases=False)
+    xb = torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16).reshape(-1)
+    x32 = xb.float()
+    x16 = x32.half()                         # lossy, so compare f16 against f32 of the same f16 values
+    a = gq.quantize_tensors(t, [(xb, npr)], [None])[0]
+    b = gq.quantize_tensors(t, [(x32, npr)], [None])[0]
+    c = gq.quantize_tensors(t, [(x16, npr)], [None])[0]
+    d = gq.quantize_tensors(t, [(x16.float(), npr)], [None])[0]
+    assert np.array_equal(a, b)
+    assert np.array_equal(c, d)
+
+
+def test_ragged_multi_tensor_launch(gq):
+    """several tensors of different shapes in one call, legacy rows that are not multiples of 256"""
+    import torch
+    if not ref.available():
+        pytest.skip("oracle/_ref not built")
+    shapes = [(3, 96), (5, 1024), (1, 32), (7, 288), (2, 2048)] * 4          # 20 tensors: more than one launch group
+    for t in (2, 3, 8, 6):
+        srcs, imxs, wants = [], [], []
+        for k, (nr, npr) in enumerate(shapes):
+            bits = synth.weights(nr, npr, seed=k, edge_cases=False)
+            imx = synth.imatrix(npr, seed=k) if k % 2 == 0 else None
+            srcs.append((torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16).reshape(-1), npr))
+            imxs.append(imx)
+            wants.append(ref.quantize(t, synth.bf16_bits_to_f32(bits).reshape(nr, npr), imx))
+        got = gq.quantize_tensors(t, srcs, imxs)
+        for g, w in zip(got, wants):
+            assert np.array_equal(g, w)
