@@ -100,6 +100,17 @@ SG_API int sg_type_needs_imatrix(int ggml_type);
  * stream, returns the bits in *h_bits and clears the word. */
 SG_API int sg_status_fetch(int device, void *stream, int *h_bits);
 
+/* ---- IQ lattice tables -----------------------------------------------------------------------------
+ * Replaces GPUQuant._upload_tables / _build_tables (seedpack/gpuquant.py:311-353) and the host routines
+ * iq2xs_init_impl / iq3xs_init_impl (ggml-quants.c:2854, 3704).  The maps and neighbour lists are built on
+ * the host on first use (about a second) and copied to the device once; this is the only device
+ * allocation the library makes (about 6 MB, kept until the process ends).  Synchronises `stream`.
+ * Needed before quantising IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S, IQ1_S, IQ1_M. */
+SG_API int sg_tables_install(int device, void *stream);
+/* host view of a built table, for tests: which = 0 IQ2_XXS, 1 IQ2_XS, 2 IQ1_S/M, 3 IQ2_S, 4 IQ3_XXS, 5 IQ3_S;
+ * what = 0 grid (uint64 / uint32 per point), 1 map (int32), 2 neighbour lists (uint16) */
+SG_API int sg_tables_host(int which, int what, const void **h_ptr, size_t *h_bytes);
+
 /* ---- quantisers -------------------------------------------------------------------------------
  * Replaces k_quantize_<type>[_v1] (seedpack/gpuquant.py:206-211), i.e. llama.cpp's
  * quantize_<type>(row, dst, 1, n_per_row, imatrix) per row (ggml-quants.c:1212 ... 5283), byte for byte.

@@ -26,7 +26,7 @@ QFUN = {2: ("q4_0", 32, 18), 3: ("q4_1", 32, 20), 6: ("q5_0", 32, 22), 7: ("q5_1
         22: ("iq2_s", 256, 82), 23: ("iq4_xs", 256, 136), 29: ("iq1_m", 256, 56), 42: ("q2_0", 64, 18)}
 IQ2_INIT = {16, 17, 19, 22, 29}            # need iq2xs_init_impl(type)   seedpack/requant.py:28
 IQ3_INIT = {18: 256, 21: 512}              # need iq3xs_init_impl(grid)   seedpack/requant.py:29
-NEEDS_IMATRIX = {16, 17, 19, 22, 29}       # assert quant_weights (ggml-quants.c:3303, 3481, 4521 ...)
+NEEDS_IMATRIX = {16, 17, 19}       # assert quant_weights (ggml-quants.c:3303, 3481, 4521 ...)
 
 _libs = {}
 _lock = threading.Lock()

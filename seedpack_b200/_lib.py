@@ -36,6 +36,8 @@ SIGNATURES = {
     "sg_type_info": (_I, [_I, ctypes.POINTER(_I), ctypes.POINTER(_I)]),
     "sg_type_needs_imatrix": (_I, [_I]),
     "sg_status_fetch": (_I, [_I, _P, ctypes.POINTER(_I)]),
+    "sg_tables_install": (_I, [_I, _P]),
+    "sg_tables_host": (_I, [_I, _I, ctypes.POINTER(_P), ctypes.POINTER(_Z)]),
     "sg_quantize_scratch_bytes": (_Z, [_I, ctypes.POINTER(sg_tensor), _I]),
     "sg_quantize_tensors": (_I, [_I, _P, _I, _I, _P, _I, _P, _P, ctypes.POINTER(sg_tensor), _I, _P, _Z]),
 }

@@ -40,8 +40,8 @@ static const TypeInfo TYPES[] = {
     {SG_Q4_0, 32, 18, 0}, {SG_Q4_1, 32, 20, 0}, {SG_Q5_0, 32, 22, 0}, {SG_Q5_1, 32, 24, 0}, {SG_Q8_0, 32, 34, 0},
     {SG_Q2_K, 256, 84, 0}, {SG_Q3_K, 256, 110, 0}, {SG_Q4_K, 256, 144, 0}, {SG_Q5_K, 256, 176, 0}, {SG_Q6_K, 256, 210, 0},
     {SG_IQ2_XXS, 256, 66, 1}, {SG_IQ2_XS, 256, 74, 1}, {SG_IQ3_XXS, 256, 98, 0}, {SG_IQ1_S, 256, 50, 1},
-    {SG_IQ4_NL, 32, 18, 0}, {SG_IQ3_S, 256, 110, 0}, {SG_IQ2_S, 256, 82, 1}, {SG_IQ4_XS, 256, 136, 0},
-    {SG_IQ1_M, 256, 56, 1}, {SG_Q2_0, 64, 18, 0},
+    {SG_IQ4_NL, 32, 18, 0}, {SG_IQ3_S, 256, 110, 0}, {SG_IQ2_S, 256, 82, 0}, {SG_IQ4_XS, 256, 136, 0},
+    {SG_IQ1_M, 256, 56, 0}, {SG_Q2_0, 64, 18, 0},
 };
 
 }  // namespace sg

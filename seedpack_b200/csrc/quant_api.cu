@@ -47,7 +47,7 @@ static int launch_meansq(const Job& job, long long nrows, int dt, cudaStream_t s
 
 static bool legacy_imx_type(int t) { return t == SG_Q4_0 || t == SG_Q4_1 || t == SG_Q5_0 || t == SG_Q5_1; }
 
-static int dispatch(int type, int variant, bool imx, const Job& job, int dt, cudaStream_t st) {
+static int dispatch(int type, int variant, bool imx, int device, const Job& job, int dt, cudaStream_t st) {
     switch (type) {
         case SG_Q4_0: return imx ? launch<LegacyImx<SG_Q4_0>, true>(job, dt, st) : launch<LegacyRefSlab<SG_Q4_0>, false>(job, dt, st);
         case SG_Q4_1: return imx ? launch<LegacyImx<SG_Q4_1>, true>(job, dt, st) : launch<LegacyRefSlab<SG_Q4_1>, false>(job, dt, st);
@@ -60,7 +60,7 @@ static int dispatch(int type, int variant, bool imx, const Job& job, int dt, cud
         case SG_Q4_K: return imx ? launch<Q45K<4>, true>(job, dt, st) : launch<Q45K<4>, false>(job, dt, st);
         case SG_Q5_K: return imx ? launch<Q45K<5>, true>(job, dt, st) : launch<Q45K<5>, false>(job, dt, st);
         case SG_Q6_K: return imx ? launch<Q6K, true>(job, dt, st) : launch<Q6K, false>(job, dt, st);
-        default: return dispatch_iq(type, variant, imx, job, dt, st);
+        default: return dispatch_iq(type, variant, imx, device, job, dt, st);
     }
 }
 
@@ -100,7 +100,6 @@ extern "C" int sg_quantize_tensors(int device, void* stream, int type, int varia
         if (t.w_off < 0 && sg_type_needs_imatrix(type)) return SG_ERR_IMATRIX;
     }
     if ((uintptr_t)x % 16 || (uintptr_t)y % 16 || (w && (uintptr_t)w % 16)) return SG_ERR_ALIGN;
-    if (type >= SG_IQ2_XXS && type != SG_IQ4_NL && type != SG_IQ4_XS && type != SG_Q2_0 && !tables_ready(device)) return SG_ERR_TABLES;
     const size_t need = sg_quantize_scratch_bytes(type, h, n);
     if (need && (!scratch || scratch_bytes < need)) return SG_ERR_SCRATCH;
 
@@ -135,7 +134,7 @@ extern "C" int sg_quantize_tensors(int device, void* stream, int type, int varia
             rc = launch_meansq(job, rows, x_dtype, st);
             if (rc != SG_OK) return rc;
         }
-        rc = dispatch(type, variant, imx, job, x_dtype, st);
+        rc = dispatch(type, variant, imx, device, job, x_dtype, st);
         if (rc != SG_OK) return rc;
     }
     return SG_OK;

@@ -1,6 +1,916 @@
-// IQ quantisers (placeholder until the grid kernels land).
+// IQ quantisers: IQ4_NL / IQ4_XS (non-uniform 16-level codebook), the lattice types IQ2_XXS, IQ2_XS,
+// IQ2_S, IQ3_XXS, IQ3_S (grid + neighbour-list search) and the ternary IQ1_S / IQ1_M (sorted
+// two-boundary split search).
+//
+// Mapping: one thread per block of 32 or 16 weights, the 8 or 16 threads of a super-block are
+// neighbouring lanes of a warp; super-block quantities (in-order sum of squares, maximum scale, the
+// packed scale nibbles) travel by warp shuffle.  Per-thread block data that is indexed dynamically
+// (sign-folded values, weights, sort order) lives in shared memory laid out [element][thread], so
+// a warp's accesses hit 32 different banks.
+//
+// Reference arithmetic: ggml-quants.c:4938-5047 (IQ4), 3271-3651 (IQ2_XXS/XS), 5114-5281 (IQ2_S),
+// 3915-4351 (IQ3_XXS/S), 4444-4671 (IQ1_S), 4693-4916 (IQ1_M); the IQ1_M variant 1 is the direct-sum
+// split search of the pre-f95b0d9539 llama.cpp sources.
 #pragma once
-#include "search.cuh"
+#include "api_util.h"
+#include "quant_k.cuh"
+
 namespace sg {
-static int dispatch_iq(int, int, bool, const Job&, int, cudaStream_t) { return SG_ERR_TYPE; }
+
+// ---- device-resident tables ----------------------------------------------------------------------
+struct GridTable {
+    const void* grid;            // uint64 (IQ2 family, 8 int8 per point) or uint32 (IQ3 family, 4 int8)
+    const int* map;              // >= 0: grid index, < 0: -(offset into neighbours) - 1
+    const uint16_t* neighbours;  // [count, indices...] lists
+};
+// index: 0 IQ2_XXS (256), 1 IQ2_XS (512), 2 IQ1_S/IQ1_M (2048), 3 IQ2_S (1024), 4 IQ3_XXS (256), 5 IQ3_S (512)
+struct IqTables { GridTable t[6]; };
+
+static __constant__ int8_t c_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+constexpr int IQ_TPB = 64;      // threads per CTA of the IQ kernels (bounds their shared memory)
+
+// ==================================================================================================
+// IQ4_NL / IQ4_XS
+SG_DEVINL int best_index_iq4(float x) {
+    // best_index_int8(16, kvalues_iq4nl, x), ggml-quants.c:28-37
+    if (x <= (float)c_iq4nl[0]) return 0;
+    if (x >= (float)c_iq4nl[15]) return 15;
+    int ml = 0, mu = 15;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        if (mu - ml > 1) {
+            const int mav = (ml + mu) / 2;
+            if (x < (float)c_iq4nl[mav]) mu = mav; else ml = mav;
+        }
+    }
+    return fsub(x, (float)c_iq4nl[mu - 1]) < fsub((float)c_iq4nl[mu], x) ? mu - 1 : mu;
 }
+
+template <bool XS> struct IQ4 {
+    static constexpr int SLAB = 256, SUB = 32, LANES = 8, QK = XS ? 256 : 32, BS = XS ? 136 : 18;
+    template <int DT, bool IMX>
+    static SG_DEVINL void run(const Job& job, const Slab& sl, int sub, bool valid) {
+        const bool live = valid && sub * 32 < sl.n;
+        float x[32], wt[32];
+        if (live || XS) load_vals<DT, 32>(job.x, sl.x + sub * 32, x);
+        else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] = 0.f;
+        }
+        float sigma2;
+        if (XS) {
+            sigma2 = ordered_sumsq<32, 8>(x, sub);
+            sigma2 = fmul(sigma2, 2.f / 256);
+        } else {
+            sigma2 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sigma2 = fadd(sigma2, fmul(x[j], x[j]));
+            sigma2 = fmul(sigma2, 2.f / 32);
+        }
+        if (IMX) {
+            if (live || XS) load_f32<32>(job.w, sl.w + sub * 32, wt);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) wt[j] = fmul(wt[j], fsqrt(fadd(sigma2, fmul(x[j], x[j]))));
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) wt[j] = fmul(x[j], x[j]);
+        }
+        float amax = 0.f, mx = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { const float ax = fabsf(x[j]); if (ax > amax) { amax = ax; mx = x[j]; } }
+        float d = 0.f;
+        const float v0 = (float)c_iq4nl[0];
+        if (!(amax < SG_GROUP_MAX_EPS)) {
+            d = fdiv(-mx, v0);                        // ntry > 0: -max / values[0]
+            float id = frcp(d);
+            float sumqx = 0.f, sumq2 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float q = (float)c_iq4nl[best_index_iq4(fmul(id, x[j]))];
+                sumqx = fadd(sumqx, fmul(fmul(wt[j], q), x[j]));
+                sumq2 = fadd(sumq2, fmul(fmul(wt[j], q), q));
+            }
+            d = sumq2 > 0.f ? fdiv(sumqx, sumq2) : 0.f;
+            float best = fmul(d, sumqx);
+#pragma unroll 1
+            for (int itry = -7; itry <= 7; ++itry) {
+                id = fdiv((float)(itry + (int)c_iq4nl[0]), mx);
+                sumqx = 0.f; sumq2 = 0.f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float q = (float)c_iq4nl[best_index_iq4(fmul(id, x[j]))];
+                    sumqx = fadd(sumqx, fmul(fmul(wt[j], q), x[j]));
+                    sumq2 = fadd(sumq2, fmul(fmul(wt[j], q), q));
+                }
+                if (sumq2 > 0.f && fmul(sumqx, sumqx) > fmul(best, sumq2)) { d = fdiv(sumqx, sumq2); best = fmul(d, sumqx); }
+            }
+        }
+        // d is scales[ib]
+        float idl;
+        uint16_t dh;
+        int l6 = 0;
+        if (XS) {
+            float scales[8];
+            gather<8>(d, scales);
+            float max_scale = 0.f, amax_scale = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { const float a = fabsf(scales[j]); if (a > amax_scale) { amax_scale = a; max_scale = scales[j]; } }
+            const float dd = fmul(-max_scale, 1.0f / 32);
+            dh = f32_to_f16(dd);
+            const float id = dd != 0.f ? frcp(dd) : 0.f;
+            int l = clampi(nearest_int(fmul(id, d)), -32, 31);
+            const float dl = fmul(dd, (float)l);
+            idl = dl != 0.f ? frcp(dl) : 0.f;
+            l6 = l + 32;
+        } else {
+            dh = f32_to_f16(d);
+            idl = d != 0.f ? frcp(d) : 0.f;
+        }
+        uint32_t qs[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t a = (uint32_t)best_index_iq4(fmul(idl, x[j]));
+            const uint32_t b = (uint32_t)best_index_iq4(fmul(idl, x[j + 16]));
+            qs[j >> 2] |= (a | (b << 4)) << (8 * (j & 3));
+        }
+        if (XS) {
+            // block_iq4_xs: d, scales_h (u16), scales_l[4], qs[128]
+            unsigned l6s[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) l6s[j] = (unsigned)gshfl<8>(l6, j);
+            if (!valid) return;
+            uint8_t* y = job.y + out_offset<256, 256, 136>(sl, 0);
+            if (sub == 0) {
+                uint32_t sh = 0, slw = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    sh |= (l6s[j] >> 4) << (2 * j);
+                    slw |= (l6s[j] & 0xf) << (4 * j);
+                }
+                st4(y, (uint32_t)dh | ((sh & 0xffff) << 16));
+                st4(y + 4, slw);
+            }
+            uint8_t* p = y + 8 + 16 * sub;
+            st4(p, qs[0]); st4(p + 4, qs[1]); st4(p + 8, qs[2]); st4(p + 12, qs[3]);
+        } else {
+            if (!live) return;
+            uint8_t* y = job.y + out_offset<256, 32, 18>(sl, sub);
+            st2(y, dh);
+#pragma unroll
+            for (int m = 0; m < 4; ++m) st4_a2(y + 2 + 4 * m, qs[m]);
+        }
+    }
+};
+
+// ==================================================================================================
+// Lattice types.  Per-thread arrays in shared memory, [element][thread].
+template <int BLK> struct IqSmem {
+    float xval[BLK][IQ_TPB];
+    float wgt[BLK][IQ_TPB];
+    float waux[BLK][IQ_TPB];
+};
+
+// codes of up to 8 groups, 16 bits per group (the group's map index u)
+struct Codes {
+    unsigned long long a, b;
+    SG_DEVINL Codes() : a(0), b(0) {}
+    SG_DEVINL unsigned get(int k) const { return (unsigned)((k < 4 ? a : b) >> (16 * (k & 3))) & 0xffffu; }
+    SG_DEVINL void set(int k, unsigned u) {
+        const int sh = 16 * (k & 3);
+        if (k < 4) a = (a & ~(0xffffull << sh)) | ((unsigned long long)u << sh);
+        else       b = (b & ~(0xffffull << sh)) | ((unsigned long long)u << sh);
+    }
+};
+
+// TYPE-specific constants of the five lattice quantisers
+template <int TYPE> struct Lat;
+template <> struct Lat<SG_IQ2_XXS> { static constexpr int BLK = 32, G = 8, CB = 2, KMAXQ = 3, TAB = 0, BS = 66, IS0 = -6, IS1 = 6; static constexpr bool PARITY = true; };
+template <> struct Lat<SG_IQ2_XS>  { static constexpr int BLK = 16, G = 8, CB = 2, KMAXQ = 3, TAB = 1, BS = 74, IS0 = -9, IS1 = 9; static constexpr bool PARITY = true; };
+template <> struct Lat<SG_IQ2_S>   { static constexpr int BLK = 16, G = 8, CB = 2, KMAXQ = 3, TAB = 3, BS = 82, IS0 = -9, IS1 = 9; static constexpr bool PARITY = false; };
+template <> struct Lat<SG_IQ3_XXS> { static constexpr int BLK = 32, G = 4, CB = 3, KMAXQ = 8, TAB = 4, BS = 98, IS0 = -15, IS1 = 15; static constexpr bool PARITY = true; };
+template <> struct Lat<SG_IQ3_S>   { static constexpr int BLK = 32, G = 4, CB = 3, KMAXQ = 8, TAB = 5, BS = 110, IS0 = -9, IS1 = 9; static constexpr bool PARITY = false; };
+
+template <int G> SG_DEVINL void grid_point(const GridTable& t, int idx, int (&pg)[G]) {
+    if (G == 8) {
+        const unsigned long long v = __ldg(static_cast<const unsigned long long*>(t.grid) + idx);
+#pragma unroll
+        for (int i = 0; i < G; ++i) pg[i] = (int)(int8_t)(v >> (8 * i));
+    } else {
+        const unsigned v = __ldg(static_cast<const unsigned*>(t.grid) + idx);
+#pragma unroll
+        for (int i = 0; i < G; ++i) pg[i] = (int)(int8_t)(v >> (8 * i));
+    }
+}
+
+// iq2_find_best_neighbour / iq3_find_best_neighbour (ggml-quants.c:3271-3293, 3915-3937): first strictly
+// smaller weighted distance wins.  Returns the grid index, and the point's codes packed as a map index.
+template <int G, int CB, int BLK>
+SG_DEVINL int best_neighbour(const GridTable& t, int list, const IqSmem<BLK>& sm, int tid, int e0, float scale, unsigned& u_out, int* status) {
+    const uint16_t* nb = t.neighbours + list;
+    const int n = __ldg(nb);
+    float best_d2 = 3.402823466e+38F;
+    int grid_index = -1;
+    float xv[G], wv[G];
+#pragma unroll
+    for (int i = 0; i < G; ++i) { xv[i] = sm.xval[e0 + i][tid]; wv[i] = sm.waux[e0 + i][tid]; }
+#pragma unroll 1
+    for (int j = 1; j <= n; ++j) {
+        const int gi = __ldg(nb + j);
+        int pg[G];
+        grid_point<G>(t, gi, pg);
+        float d2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            const float diff = fsub(fmul(scale, (float)pg[i]), xv[i]);
+            d2 = fadd(d2, fmul(fmul(wv[i], diff), diff));
+        }
+        if (d2 < best_d2) { best_d2 = d2; grid_index = gi; }
+    }
+    if (grid_index < 0) { atomicOr(status, SG_ST_OFFGRID); grid_index = 0; }
+    int pg[G];
+    grid_point<G>(t, grid_index, pg);
+    unsigned u = 0;
+#pragma unroll
+    for (int i = 0; i < G; ++i) u |= (unsigned)((pg[i] - 1) / 2) << (CB * i);
+    u_out = u;
+    return grid_index;
+}
+
+// sumqx / sumq2 over the block in index order with q = 2*L + 1
+template <int BLK, int G, int CB>
+SG_DEVINL void block_sums(const Codes& c, const IqSmem<BLK>& sm, int tid, float& sumqx, float& sumq2) {
+    sumqx = 0.f; sumq2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < BLK / G; ++k) {
+        const unsigned u = c.get(k);
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            const float q = (float)(2 * (int)((u >> (CB * i)) & ((1u << CB) - 1)) + 1);
+            const float w = sm.wgt[k * G + i][tid];
+            sumqx = fadd(sumqx, fmul(fmul(w, sm.xval[k * G + i][tid]), q));
+            sumq2 = fadd(sumq2, fmul(fmul(w, q), q));
+        }
+    }
+}
+
+template <int TYPE> struct Lattice {
+    using P = Lat<TYPE>;
+    static constexpr int SLAB = 256, SUB = P::BLK, LANES = 256 / P::BLK, QK = 256, BS = P::BS;
+    static constexpr int BLK = P::BLK, G = P::G, CB = P::CB, NG = BLK / G, KMAXQ = P::KMAXQ;
+    using Smem = IqSmem<BLK>;
+
+    template <int DT, bool IMX>
+    static SG_DEVINL void run(const Job& job, const Slab& sl, int sub, bool valid, const IqTables& tabs, IqSmem<BLK>& sm) {
+        const GridTable& T = tabs.t[P::TAB];
+        const int tid = threadIdx.x;
+        float scale = 0.f;                 // scales[ib]
+        Codes L;
+        unsigned signs[4] = {0, 0, 0, 0};  // block_signs[k], per group of 8 weights
+        bool wrote = false;                // did this block reach the code-emitting tail (else its bytes stay zero)
+        {
+            float x[BLK];
+            load_vals<DT, BLK>(job.x, sl.x + sub * BLK, x);
+            const float sumx2 = ordered_sumsq<BLK, LANES>(x, sub);
+            const float sigma2 = TYPE == SG_IQ2_XXS || TYPE == SG_IQ2_XS ? fmul(sumx2, 1.0f / 256)
+                                                                         : fmul(fmul(2.f, sumx2), 1.0f / 256);
+            float qw[BLK];
+            if (IMX) load_f32<BLK>(job.w, sl.w + sub * BLK, qw);
+#pragma unroll
+            for (int i = 0; i < BLK; ++i) {
+                float w;
+                if (IMX) w = fmul(qw[i], fsqrt(fadd(sigma2, fmul(x[i], x[i]))));
+                else if (TYPE == SG_IQ2_S) w = fadd(fmul(0.25f, sigma2), fmul(x[i], x[i]));
+                else w = fmul(x[i], x[i]);
+                sm.wgt[i][tid] = w;
+                sm.waux[i][tid] = fsqrt(w);
+            }
+            // sign folding (ggml-quants.c:3341-3362): groups of 8; with PARITY an odd number of flips is repaired
+            // by un-flipping the weight with the smallest w*x*x (first minimum)
+#pragma unroll
+            for (int k = 0; k < BLK / 8; ++k) {
+                int nflip = 0;
+                unsigned s = 0;
+                float xv[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float v = x[8 * k + i];
+                    if (v >= 0.f) xv[i] = v;
+                    else { xv[i] = -v; ++nflip; s |= 1u << i; }
+                }
+                if (P::PARITY) {
+                    if (nflip & 1) {
+                        int imin = 0;
+                        float mn = fmul(fmul(sm.wgt[8 * k][tid], x[8 * k]), x[8 * k]);
+#pragma unroll
+                        for (int i = 1; i < 8; ++i) {
+                            const float ax = fmul(fmul(sm.wgt[8 * k + i][tid], x[8 * k + i]), x[8 * k + i]);
+                            if (ax < mn) { mn = ax; imin = i; }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) if (i == imin) xv[i] = -xv[i];
+                        s ^= 1u << imin;
+                    }
+                    s &= 127;
+                }
+                signs[k] = s;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sm.xval[8 * k + i][tid] = xv[i];
+            }
+        }
+        float mx = sm.xval[0][tid];
+#pragma unroll
+        for (int i = 1; i < BLK; ++i) mx = fmaxf(mx, sm.xval[i][tid]);
+        const float eps = TYPE == SG_IQ3_XXS ? 1e-8f : TYPE == SG_IQ2_S ? 1e-8f : SG_GROUP_MAX_EPS;
+        const bool dead = TYPE == SG_IQ3_S ? !(mx != 0.f) : (mx < eps);
+        const float c2k1 = (float)(2 * KMAXQ - 1);
+        if (!dead) {
+            bool go = true;
+            float best = 0.f;
+            float rng;                       // denominator of the candidate inverse scales
+            unsigned ongrid = TYPE == SG_IQ3_S ? 0u : 0xffu;
+            if (TYPE == SG_IQ2_XXS) {
+                float xv[32], wv[32];
+                int Lq[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) { xv[i] = sm.xval[i][tid]; wv[i] = sm.wgt[i][tid]; }
+                scale = make_qp_quants<32>(KMAXQ + 1, xv, Lq, wv);
+                rng = fmul(scale, (float)KMAXQ);       // eff_max
+                if (rng <= 0.f) go = false;
+            } else {
+                rng = mx;
+                scale = fdiv(mx, TYPE == SG_IQ2_XS || TYPE == SG_IQ2_S ? c_div[DIV_5] : c_div[DIV_15]);
+            }
+            if (go) {
+                const float step = (TYPE == SG_IQ3_XXS || TYPE == SG_IQ3_S) ? 0.2f : 0.1f;
+#pragma unroll 1
+                for (int is = P::IS0; is <= P::IS1; ++is) {
+                    const float id = fdiv(fadd(c2k1, fmul((float)is, step)), rng);
+                    const float this_scale = frcp(id);
+                    Codes aux;
+                    unsigned og = 0;
+#pragma unroll 1
+                    for (int k = 0; k < NG; ++k) {
+                        unsigned u = 0;
+#pragma unroll
+                        for (int i = 0; i < G; ++i) {
+                            const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
+                            u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
+                        }
+                        const int gi = __ldg(T.map + u);
+                        if (gi < 0) best_neighbour<G, CB, BLK>(T, -gi - 1, sm, tid, G * k, this_scale, u, job.status);
+                        else og |= 1u << k;
+                        aux.set(k, u);
+                    }
+                    float sumqx, sumq2;
+                    block_sums<BLK, G, CB>(aux, sm, tid, sumqx, sumq2);
+                    if (sumq2 > 0.f && fmul(sumqx, sumqx) > fmul(best, sumq2)) {
+                        scale = fdiv(sumqx, sumq2); best = fmul(scale, sumqx);
+                        L = aux; ongrid = og;
+                    }
+                }
+                // second pass at the winning scale
+                bool refit;
+                if (TYPE == SG_IQ2_XXS) refit = scale > 0.f;
+                else {
+                    const unsigned all = (1u << NG) - 1;
+                    refit = (ongrid & all) != all && scale > 0.f;
+                }
+                if (refit) {
+                    const float id = frcp(scale);
+#pragma unroll 1
+                    for (int k = 0; k < NG; ++k) {
+                        if ((TYPE == SG_IQ2_XS || TYPE == SG_IQ2_S || TYPE == SG_IQ3_XXS) && ((ongrid >> k) & 1)) continue;
+                        unsigned u = 0;
+#pragma unroll
+                        for (int i = 0; i < G; ++i) {
+                            const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
+                            u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
+                        }
+                        const int gi = __ldg(T.map + u);
+                        if (gi < 0) best_neighbour<G, CB, BLK>(T, -gi - 1, sm, tid, G * k, scale, u, job.status);
+                        L.set(k, u);           // on the grid the codes ARE the grid point
+                    }
+                    float sumqx, sumq2;
+                    block_sums<BLK, G, CB>(L, sm, tid, sumqx, sumq2);
+                    if (sumq2 > 0.f) scale = fdiv(sumqx, sumq2);
+                }
+                if (scale < 0.f) {
+                    scale = -scale;
+                    if (P::PARITY) {
+#pragma unroll
+                        for (int k = 0; k < (TYPE == SG_IQ2_XS ? 2 : 4); ++k) signs[k] = (~signs[k]) & 127;
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < BLK / 8; ++k) signs[k] = (~signs[k]) & 0xff;
+                    }
+                }
+                wrote = true;
+            }
+        }
+        if (!wrote) scale = 0.f;
+        // grid indices of the final codes
+        unsigned gidx[NG];
+#pragma unroll
+        for (int k = 0; k < NG; ++k) {
+            int gi = wrote ? __ldg(T.map + L.get(k)) : 0;
+            if (gi < 0) { atomicOr(job.status, SG_ST_OFFGRID); gi = 0; }
+            gidx[k] = (unsigned)gi;
+        }
+        // super-block scale
+        float scales[LANES];
+        gather<LANES>(scale, scales);
+        float max_scale = 0.f;
+#pragma unroll
+        for (int j = 0; j < LANES; ++j) max_scale = fmaxf(max_scale, scales[j]);
+        const bool nz = max_scale != 0.f;
+        const float d = fdiv(max_scale, c_div[DIV_31]);
+        const float fudge = TYPE == SG_IQ3_XXS ? 1.0125f : TYPE == SG_IQ3_S ? 1.033f : TYPE == SG_IQ2_S ? 0.9875f : 1.0f;
+        const uint16_t dh = nz ? f32_to_f16(fudge == 1.0f ? d : fmul(d, fudge)) : f32_to_f16(0.f);
+        int l4 = 0;
+        if (nz) l4 = clampi(nearest_int(fmul(0.5f, fsub(fmul(frcp(d), scale), 1.f))), 0, 15);
+        const unsigned l4n = (unsigned)__shfl_xor_sync(SG_FULL, l4, 1);     // partner's nibble
+        unsigned qh_bits = 0;                 // this block's contribution to the shared high-bit bytes
+        if (TYPE == SG_IQ2_S) qh_bits = (gidx[0] >> 8) | ((gidx[1] >> 8) << 2);       // 4 bits
+        const unsigned qh_n = (unsigned)__shfl_xor_sync(SG_FULL, (int)qh_bits, 1);
+        // IQ3_S advances its qs / signs cursors only for blocks that were coded (ggml-quants.c:4241-4243 `continue`
+        // skips `qs += bs4; signs += bs8` at 4327-4329), so coded blocks are packed towards the front and the
+        // tail stays zero; qh keeps absolute positions.
+        int slot = sub;
+        if (TYPE == SG_IQ3_S) {
+            const unsigned lanebase = (threadIdx.x & 31) & ~7u;
+            const unsigned m = (__ballot_sync(SG_FULL, wrote) >> lanebase) & 0xffu;
+            const unsigned below = (1u << sub) - 1;
+            slot = wrote ? __popc(m & below) : __popc(m) + __popc(~m & below);
+        }
+        if (!valid) return;
+        uint8_t* y = job.y + out_offset<256, 256, BS>(sl, 0);
+        if (sub == 0) st2(y, dh);
+        if (TYPE == SG_IQ2_XXS) {
+            uint32_t w0 = 0, w1 = 0;
+            if (nz && wrote) {
+                w0 = gidx[0] | (gidx[1] << 8) | (gidx[2] << 16) | (gidx[3] << 24);
+                w1 = signs[0] | (signs[1] << 7) | (signs[2] << 14) | (signs[3] << 21);
+            }
+            if (nz) w1 |= (uint32_t)l4 << 28;
+            st4_a2(y + 2 + 8 * sub, w0); st4_a2(y + 6 + 8 * sub, w1);
+        } else if (TYPE == SG_IQ2_XS) {
+            uint32_t w0 = 0;
+            if (nz && wrote) w0 = (gidx[0] | (signs[0] << 9)) | ((gidx[1] | (signs[1] << 9)) << 16);
+            st4_a2(y + 2 + 4 * sub, w0);
+            if (!(sub & 1)) y[66 + (sub >> 1)] = (uint8_t)(nz ? (l4 | (l4n << 4)) : 0);
+        } else if (TYPE == SG_IQ2_S) {
+            // block_iq2_s: d, qs[64] (32 grid bytes + 32 sign bytes), qh[8], scales[8]
+            st2(y + 2 + 2 * sub, wrote ? ((gidx[0] & 255) | ((gidx[1] & 255) << 8)) : 0);
+            st2(y + 34 + 2 * sub, wrote ? (signs[0] | (signs[1] << 8)) : 0);
+            if (!(sub & 1)) {
+                y[66 + (sub >> 1)] = (uint8_t)((wrote ? qh_bits : 0) | (qh_n << 4));
+                y[74 + (sub >> 1)] = (uint8_t)(nz ? (l4 | (l4n << 4)) : 0);
+            }
+        } else if (TYPE == SG_IQ3_XXS) {
+            // block_iq3_xxs: d, qs[64 grid bytes + 8 x u32 scales_and_signs]
+            uint32_t w0 = 0, w1 = 0, ss = 0;
+            if (nz && wrote) {
+                w0 = gidx[0] | (gidx[1] << 8) | (gidx[2] << 16) | (gidx[3] << 24);
+                w1 = gidx[4] | (gidx[5] << 8) | (gidx[6] << 16) | (gidx[7] << 24);
+                ss = signs[0] | (signs[1] << 7) | (signs[2] << 14) | (signs[3] << 21);
+            }
+            if (nz) ss |= (uint32_t)l4 << 28;
+            st4_a2(y + 2 + 8 * sub, w0); st4_a2(y + 6 + 8 * sub, w1);
+            st4_a2(y + 66 + 4 * sub, ss);
+        } else {   // IQ3_S: d, qs[64], qh[8], signs[32], scales[4]
+            uint32_t w0 = 0, w1 = 0, sg = 0, qh = 0;
+            if (wrote) {
+                w0 = (gidx[0] & 255) | ((gidx[1] & 255) << 8) | ((gidx[2] & 255) << 16) | ((gidx[3] & 255) << 24);
+                w1 = (gidx[4] & 255) | ((gidx[5] & 255) << 8) | ((gidx[6] & 255) << 16) | ((gidx[7] & 255) << 24);
+                sg = signs[0] | (signs[1] << 8) | (signs[2] << 16) | (signs[3] << 24);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) qh |= (gidx[k] >> 8) << k;
+            }
+            st4_a2(y + 2 + 8 * slot, w0); st4_a2(y + 6 + 8 * slot, w1);
+            y[66 + sub] = (uint8_t)qh;
+            st4_a2(y + 74 + 4 * slot, sg);
+            if (!(sub & 1)) y[106 + (sub >> 1)] = (uint8_t)(nz ? (l4 | (l4n << 4)) : 0);
+        }
+    }
+};
+
+// ==================================================================================================
+// IQ1_S / IQ1_M
+template <int BLK, int NPS> struct Iq1Smem {
+    float xb[BLK][IQ_TPB];
+    float wgt[BLK][IQ_TPB];
+    float pa[NPS][IQ_TPB];        // prefix sums of weight * x in sorted order
+    float pb[NPS][IQ_TPB];        // prefix sums of weight
+    uint8_t idx[BLK][IQ_TPB];     // sorted position -> element
+    uint8_t L[BLK][IQ_TPB];       // ternary codes 0,1,2
+};
+
+// iq1_find_best_neighbour2 (ggml-quants.c:4444-4499).  The exhaustive fall-back of the C code is only
+// reachable when every distance is NaN; that case sets SG_ST_OFFGRID instead.
+template <class SM>
+SG_DEVINL int best_neighbour_iq1(const GridTable& t, int list, SM& sm, int tid, int e0, float scale,
+                                 const float (&xg)[3], int* status) {
+    const uint16_t* nb = t.neighbours + list;
+    const int n = __ldg(nb);
+    float best = 3.402823466e+38F;
+    int grid_index = -1;
+    float xv[8], wv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { xv[i] = sm.xb[e0 + i][tid]; wv[i] = sm.wgt[e0 + i][tid]; }
+#pragma unroll 1
+    for (int j = 1; j <= n; ++j) {
+        const int gi = __ldg(nb + j);
+        int pg[8];
+        grid_point<8>(t, gi, pg);
+        float d2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = (pg[i] - 1) / 2;
+            const float q = c == 0 ? xg[0] : c == 1 ? xg[1] : xg[2];
+            const float diff = fsub(fmul(scale, q), xv[i]);
+            d2 = fadd(d2, fmul(fmul(wv[i], diff), diff));
+        }
+        if (d2 < best) { best = d2; grid_index = gi; }
+    }
+    if (grid_index < 0) { atomicOr(status, SG_ST_OFFGRID); grid_index = 0; }
+    int pg[8];
+    grid_point<8>(t, grid_index, pg);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sm.L[e0 + i][tid] = (uint8_t)((pg[i] - 1) / 2);
+    return grid_index;
+}
+
+// stable insertion sort of (value, index) by value (seedpack/gpuquant.py:70-80 replaces qsort with exactly this)
+template <int BLK, class SM> SG_DEVINL void sort_block(SM& sm, int tid) {
+#pragma unroll 1
+    for (int j = 0; j < BLK; ++j) sm.idx[j][tid] = (uint8_t)j;
+#pragma unroll 1
+    for (int i = 1; i < BLK; ++i) {
+        const int ti = sm.idx[i][tid];
+        const float tv = sm.xb[ti][tid];
+        int j = i;
+        while (j > 0) {
+            const int pj = sm.idx[j - 1][tid];
+            if (!(sm.xb[pj][tid] > tv)) break;
+            sm.idx[j][tid] = (uint8_t)pj;
+            --j;
+        }
+        sm.idx[j][tid] = (uint8_t)ti;
+    }
+}
+
+template <bool M, int VARIANT> struct IQ1 {
+    static constexpr int BLK = M ? 16 : 32, NPS = M ? 34 : 33;
+    static constexpr int SLAB = 256, SUB = BLK, LANES = 256 / BLK, QK = 256, BS = M ? 56 : 50;
+    using SM = Iq1Smem<BLK, NPS>;
+    using Smem = SM;
+
+    template <int DT, bool IMX>
+    static SG_DEVINL void run(const Job& job, const Slab& sl, int sub, bool valid, const IqTables& tabs, SM& sm) {
+        const GridTable& T = tabs.t[2];
+        const int tid = threadIdx.x;
+        const float x_p[3] = {-1 + 0.125f, 0.125f, 1 + 0.125f};
+        const float x_m[3] = {-1 - 0.125f, -0.125f, 1 - 0.125f};
+        float sigma2, mx;
+        {
+            float x[BLK];
+            load_vals<DT, BLK>(job.x, sl.x + sub * BLK, x);
+            const float sumx2 = ordered_sumsq<BLK, LANES>(x, sub);
+            sigma2 = fmul(fmul(2.f, sumx2), 1.0f / 256);
+            float qw[BLK];
+            if (IMX) load_f32<BLK>(job.w, sl.w + sub * BLK, qw);
+            mx = fabsf(x[0]);
+#pragma unroll
+            for (int i = 0; i < BLK; ++i) {
+                sm.xb[i][tid] = x[i];
+                sm.wgt[i][tid] = IMX ? fmul(qw[i], fsqrt(fadd(sigma2, fmul(x[i], x[i])))) : fmul(x[i], x[i]);
+                if (i) mx = fmaxf(mx, fabsf(x[i]));
+            }
+        }
+        float scale = 0.f;
+        int shift = M ? 0 : 1;             // shifts[ib]: IQ1_S +1 / -1, IQ1_M best_k 0..3
+        unsigned index[BLK / 8];
+#pragma unroll
+        for (int k = 0; k < BLK / 8; ++k) index[k] = 0;
+        bool wrote = false;
+        if (!(mx < (M ? 1e-7f : 1e-12f))) {
+            sort_block<BLK>(sm, tid);
+            float best_score = -3.402823466e+38F;
+            scale = mx;
+            int besti1 = -1, besti2 = -1, best_k = M ? -1 : 0;
+            if (!M) {
+                sm.pa[0][tid] = 0.f; sm.pb[0][tid] = 0.f;
+                {
+                    float a = 0.f, b = 0.f;
+#pragma unroll 1
+                    for (int j = 0; j < BLK; ++j) {
+                        const int i = sm.idx[j][tid];
+                        const float w = sm.wgt[i][tid];
+                        a = fadd(a, fmul(w, sm.xb[i][tid]));
+                        b = fadd(b, w);
+                        sm.pa[j + 1][tid] = a; sm.pb[j + 1][tid] = b;
+                    }
+                }
+                const float sx0 = sm.pa[0][tid], sw0 = sm.pb[0][tid], sxn = sm.pa[BLK][tid], swn = sm.pb[BLK][tid];
+#pragma unroll 1
+                for (int i1 = 0; i1 <= BLK; ++i1) {
+                    const float sx1 = sm.pa[i1][tid], sw1 = sm.pb[i1][tid];
+                    const float ax = fsub(sx1, sx0), aw = fsub(sw1, sw0);
+#pragma unroll 1
+                    for (int i2 = i1; i2 <= BLK; ++i2) {
+                        const float sx2 = sm.pa[i2][tid], sw2 = sm.pb[i2][tid];
+                        const float bx = fsub(sx2, sx1), cx = fsub(sxn, sx2);
+                        const float bw = fsub(sw2, sw1), cw = fsub(swn, sw2);
+                        float sumqx = fadd(fadd(fmul(ax, x_p[0]), fmul(bx, x_p[1])), fmul(cx, x_p[2]));
+                        float sumq2 = fadd(fadd(fmul(fmul(aw, x_p[0]), x_p[0]), fmul(fmul(bw, x_p[1]), x_p[1])), fmul(fmul(cw, x_p[2]), x_p[2]));
+                        if (sumq2 > 0.f && fmul(sumqx, sumqx) > fmul(best_score, sumq2)) {
+                            scale = fdiv(sumqx, sumq2); best_score = fmul(scale, sumqx);
+                            besti1 = i1; besti2 = i2; best_k = 1;
+                        }
+                        sumqx = fadd(fadd(fmul(ax, x_m[0]), fmul(bx, x_m[1])), fmul(cx, x_m[2]));
+                        sumq2 = fadd(fadd(fmul(fmul(aw, x_m[0]), x_m[0]), fmul(fmul(bw, x_m[1]), x_m[1])), fmul(fmul(cw, x_m[2]), x_m[2]));
+                        if (sumq2 > 0.f && fmul(sumqx, sumqx) > fmul(best_score, sumq2)) {
+                            scale = fdiv(sumqx, sumq2); best_score = fmul(scale, sumqx);
+                            besti1 = i1; besti2 = i2; best_k = -1;
+                        }
+                    }
+                }
+            } else if (VARIANT == 0) {
+                // per-half prefix sums: pa[h*17 + j], pb[h*17 + j]   (ggml-quants.c:4777-4822)
+                sm.pa[0][tid] = 0.f; sm.pa[17][tid] = 0.f; sm.pb[0][tid] = 0.f; sm.pb[17][tid] = 0.f;
+#pragma unroll 1
+                for (int j = 0; j < 16; ++j) {
+                    const int i = sm.idx[j][tid];
+                    const int h = i < 8 ? 0 : 1;
+                    const float w = sm.wgt[i][tid];
+                    sm.pa[h * 17 + j + 1][tid] = fadd(sm.pa[h * 17 + j][tid], fmul(w, sm.xb[i][tid]));
+                    sm.pa[(1 - h) * 17 + j + 1][tid] = sm.pa[(1 - h) * 17 + j][tid];
+                    sm.pb[h * 17 + j + 1][tid] = fadd(sm.pb[h * 17 + j][tid], w);
+                    sm.pb[(1 - h) * 17 + j + 1][tid] = sm.pb[(1 - h) * 17 + j][tid];
+                }
+                const float txs0 = sm.pa[16][tid], txs1 = sm.pa[33][tid], tws0 = sm.pb[16][tid], tws1 = sm.pb[33][tid];
+                const float p2 = x_p[2], m2 = x_m[2];
+                const float cp1 = fsub(fmul(x_p[0], x_p[0]), fmul(x_p[1], x_p[1]));
+                const float cp2 = fsub(fmul(x_p[1], x_p[1]), fmul(x_p[2], x_p[2]));
+                const float cm1 = fsub(fmul(x_m[0], x_m[0]), fmul(x_m[1], x_m[1]));
+                const float cm2 = fsub(fmul(x_m[1], x_m[1]), fmul(x_m[2], x_m[2]));
+                const float tp0 = fmul(txs0, p2), tp1 = fmul(txs1, p2), tm0 = fmul(txs0, m2), tm1 = fmul(txs1, m2);
+                const float wp0 = fmul(fmul(tws0, p2), p2), wp1 = fmul(fmul(tws1, p2), p2);
+                const float wm0 = fmul(fmul(tws0, m2), m2), wm1 = fmul(fmul(tws1, m2), m2);
+#pragma unroll 1
+                for (int i1 = 0; i1 <= 16; ++i1) {
+                    const float x10 = sm.pa[i1][tid], x11 = sm.pa[17 + i1][tid];
+                    const float w10 = sm.pb[i1][tid], w11 = sm.pb[17 + i1][tid];
+#pragma unroll 1
+                    for (int i2 = i1; i2 <= 16; ++i2) {
+                        const float x20 = sm.pa[i2][tid], x21 = sm.pa[17 + i2][tid];
+                        const float w20 = sm.pb[i2][tid], w21 = sm.pb[17 + i2][tid];
+                        const float s0 = fadd(x10, x20), s1 = fadd(x11, x21);
+                        const float qx_p0 = fsub(tp0, s0), qx_m0 = fsub(tm0, s0), qx_p1 = fsub(tp1, s1), qx_m1 = fsub(tm1, s1);
+                        const float q2_p0 = fadd(fadd(wp0, fmul(w10, cp1)), fmul(w20, cp2));
+                        const float q2_m0 = fadd(fadd(wm0, fmul(w10, cm1)), fmul(w20, cm2));
+                        const float q2_p1 = fadd(fadd(wp1, fmul(w11, cp1)), fmul(w21, cp2));
+                        const float q2_m1 = fadd(fadd(wm1, fmul(w11, cm1)), fmul(w21, cm2));
+                        const float sqx[4] = {fadd(qx_p0, qx_p1), fadd(qx_p0, qx_m1), fadd(qx_m0, qx_p1), fadd(qx_m0, qx_m1)};
+                        const float sq2[4] = {fadd(q2_p0, q2_p1), fadd(q2_p0, q2_m1), fadd(q2_m0, q2_p1), fadd(q2_m0, q2_m1)};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            if (sq2[k] > 0.f && fmul(sqx[k], sqx[k]) > fmul(best_score, sq2[k])) {
+                                scale = fdiv(sqx[k], sq2[k]); best_score = fmul(scale, sqx[k]);
+                                besti1 = i1; besti2 = i2; best_k = k;
+                            }
+                        }
+                    }
+                }
+            } else {
+                // direct sums per split, three ranges of the sorted order (pre-f95b0d9539 llama.cpp)
+#pragma unroll 1
+                for (int i1 = 0; i1 <= 16; ++i1) {
+#pragma unroll 1
+                    for (int i2 = i1; i2 <= 16; ++i2) {
+                        float sqx[4] = {0.f, 0.f, 0.f, 0.f}, sq2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+                        for (int j = 0; j < 16; ++j) {
+                            const int i = sm.idx[j][tid];
+                            const int g = j < i1 ? 0 : j < i2 ? 1 : 2;
+                            const float xp = g == 0 ? x_p[0] : g == 1 ? x_p[1] : x_p[2];
+                            const float xm = g == 0 ? x_m[0] : g == 1 ? x_m[1] : x_m[2];
+                            const float w = sm.wgt[i][tid], xv = sm.xb[i][tid];
+                            const float pqx = fmul(fmul(w, xp), xv), mqx = fmul(fmul(w, xm), xv);
+                            const float pq2 = fmul(fmul(w, xp), xp), mq2 = fmul(fmul(w, xm), xm);
+                            const bool first = i < 8;
+                            // k: 0 = (+,+), 1 = (+,-), 2 = (-,+), 3 = (-,-): first sign for the first half of the block
+                            sqx[0] = fadd(sqx[0], pqx);                 sq2[0] = fadd(sq2[0], pq2);
+                            sqx[1] = fadd(sqx[1], first ? pqx : mqx);   sq2[1] = fadd(sq2[1], first ? pq2 : mq2);
+                            sqx[2] = fadd(sqx[2], first ? mqx : pqx);   sq2[2] = fadd(sq2[2], first ? mq2 : pq2);
+                            sqx[3] = fadd(sqx[3], mqx);                 sq2[3] = fadd(sq2[3], mq2);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            if (sq2[k] > 0.f && fmul(sqx[k], sqx[k]) > fmul(best_score, sq2[k])) {
+                                scale = fdiv(sqx[k], sq2[k]); best_score = fmul(scale, sqx[k]);
+                                besti1 = i1; besti2 = i2; best_k = k;
+                            }
+                        }
+                    }
+                }
+            }
+            const bool found = besti1 >= 0 && besti2 >= 0 && (M ? best_k >= 0 : best_k != 0);
+            if (found) {
+#pragma unroll 1
+                for (int j = 0; j < BLK; ++j) sm.L[sm.idx[j][tid]][tid] = (uint8_t)(j < besti1 ? 0 : j < besti2 ? 1 : 2);
+                if (scale < 0.f) {
+#pragma unroll 1
+                    for (int j = 0; j < BLK; ++j) sm.L[j][tid] = (uint8_t)(2 - sm.L[j][tid]);
+                    scale = -scale;
+                    best_k = M ? 3 - best_k : -best_k;
+                }
+                bool all_on_grid = true;
+#pragma unroll
+                for (int k = 0; k < BLK / 8; ++k) {
+                    const bool plus = M ? (k == 0 ? best_k < 2 : (best_k % 2 == 0)) : best_k == 1;
+                    const float xx[3] = {plus ? x_p[0] : x_m[0], plus ? x_p[1] : x_m[1], plus ? x_p[2] : x_m[2]};
+                    unsigned u = 0;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) u |= (unsigned)sm.L[8 * k + j][tid] << (2 * j);
+                    int gi = __ldg(T.map + u);
+                    if (gi < 0) {
+                        all_on_grid = false;
+                        gi = best_neighbour_iq1(T, -gi - 1, sm, tid, 8 * k, scale, xx, job.status);
+                    }
+                    index[k] = (unsigned)gi;
+                }
+                if (!all_on_grid) {
+                    float sumqx = 0.f, sumq2 = 0.f;
+#pragma unroll
+                    for (int k = 0; k < BLK / 8; ++k) {
+                        const bool plus = M ? (k == 0 ? best_k < 2 : (best_k % 2 == 0)) : best_k == 1;
+                        int pg[8];
+                        grid_point<8>(T, (int)index[k], pg);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int c = (pg[j] - 1) / 2;
+                            const float q = plus ? (c == 0 ? x_p[0] : c == 1 ? x_p[1] : x_p[2]) : (c == 0 ? x_m[0] : c == 1 ? x_m[1] : x_m[2]);
+                            const float w = sm.wgt[8 * k + j][tid];
+                            sumqx = fadd(sumqx, fmul(fmul(w, q), sm.xb[8 * k + j][tid]));
+                            sumq2 = fadd(sumq2, fmul(fmul(w, q), q));
+                        }
+                    }
+                    if (sumqx > 0.f && sumq2 > 0.f) scale = fdiv(sumqx, sumq2);
+                }
+                shift = best_k;
+                wrote = true;
+            } else {
+                scale = 0.f;
+            }
+        }
+        if (!wrote) { scale = 0.f; shift = M ? 0 : 1; }
+        float scales[LANES];
+        gather<LANES>(scale, scales);
+        float max_scale = 0.f;
+#pragma unroll
+        for (int j = 0; j < LANES; ++j) max_scale = fmaxf(max_scale, scales[j]);
+        const bool nz = max_scale != 0.f;
+        float d = fdiv(max_scale, c_div[DIV_15]);
+        const float id = frcp(d);
+        int l3 = 0;
+        if (nz) l3 = clampi(nearest_int(fmul(0.5f, fsub(fmul(id, scale), 1.f))), 0, 7);
+        uint8_t* y = job.y + out_offset<256, 256, BS>(sl, 0);
+        if (!M) {
+            // block_iq1_s: d, qs[32], qh[8] (u16)
+            unsigned h = 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) h |= (index[k] >> 8) << (3 * k);
+            if (nz) h |= (unsigned)(l3 | (shift == -1 ? 8 : 0)) << 12;
+            if (!valid) return;
+            if (sub == 0) st2(y, nz ? f32_to_f16(fmul(d, 1.125f)) : f32_to_f16(0.f));
+            st4_a2(y + 2 + 4 * sub, (index[0] & 255) | ((index[1] & 255) << 8) | ((index[2] & 255) << 16) | ((index[3] & 255) << 24));
+            st2(y + 34 + 2 * sub, h);
+        } else {
+            // final pass over the super-block in block order (ggml-quants.c:4884-4909): an in-order chain, handed
+            // from lane to lane
+            float sumqx_f = 0.f, sumq2_f = 0.f;
+#pragma unroll 1
+            for (int stage = 0; stage < 16; ++stage) {
+                float a = sumqx_f, b = sumq2_f;
+                if (sub == stage && nz) {
+                    const float ql = (float)(2 * l3 + 1);
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const bool plus = k == 0 ? shift < 2 : (shift % 2 == 0);
+                        int pg[8];
+                        grid_point<8>(T, (int)index[k], pg);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int c = (pg[j] - 1) / 2;
+                            const float xx = plus ? (c == 0 ? x_p[0] : c == 1 ? x_p[1] : x_p[2]) : (c == 0 ? x_m[0] : c == 1 ? x_m[1] : x_m[2]);
+                            const float q = fmul(xx, ql);
+                            const float w = sm.wgt[8 * k + j][tid];
+                            a = fadd(a, fmul(fmul(w, q), sm.xb[8 * k + j][tid]));
+                            b = fadd(b, fmul(fmul(w, q), q));
+                        }
+                    }
+                }
+                sumqx_f = gshfl<16>(a, stage);
+                sumq2_f = gshfl<16>(b, stage);
+            }
+            if (sumq2_f > 0.f) d = fdiv(sumqx_f, sumq2_f);
+            const unsigned s16 = f32_to_f16(fmul(d, 1.1125f));
+            // scales: four u16, each 4 x 3-bit block scales + one nibble of the fp16 super-scale
+            unsigned l3s[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) l3s[k] = (unsigned)gshfl<16>(l3, (sub & ~3) + k);
+            const unsigned masks = shift == 0 ? 0x00u : shift == 1 ? 0x80u : shift == 2 ? 0x08u : 0x88u;
+            if (!valid) return;
+            st2(y + 2 * sub, (index[0] & 255) | ((index[1] & 255) << 8));
+            y[32 + sub] = (uint8_t)((index[0] >> 8) | ((index[1] >> 8) << 4) | (nz ? masks : 0u));
+            if ((sub & 3) == 0) {
+                unsigned v = 0;
+                if (nz) {
+                    v = l3s[0] | (l3s[1] << 3) | (l3s[2] << 6) | (l3s[3] << 9);
+                    const int q = sub >> 2;
+                    v |= ((s16 >> (4 * q)) & 0xf) << 12;
+                }
+                st2(y + 48 + 2 * (sub >> 2), v);
+            }
+        }
+    }
+};
+
+// ---- launch ------------------------------------------------------------------------------------------
+const IqTables* device_tables(int device);     // tables.cu; null until sg_tables_install ran on the device
+
+template <class T, int DT, bool IMX>
+__global__ void __launch_bounds__(IQ_TPB) k_quant_iq(const __grid_constant__ Job job, const __grid_constant__ IqTables tabs) {
+    __shared__ typename T::Smem sm;
+    constexpr int LANES = T::LANES;
+    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long s = g / LANES;
+    const int sub = (int)(g - s * LANES);
+    const bool valid = s < job.nslabs;
+    if (!valid) s = job.nslabs - 1;
+    const Slab sl = locate<T::SLAB>(job, s);
+    T::template run<DT, IMX>(job, sl, sub, valid, tabs, sm);
+}
+
+template <class T, int DT, bool IMX>
+__global__ void __launch_bounds__(128) k_quant_iq4(const __grid_constant__ Job job) {
+    constexpr int LANES = T::LANES;
+    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long s = g / LANES;
+    const int sub = (int)(g - s * LANES);
+    const bool valid = s < job.nslabs;
+    if (!valid) s = job.nslabs - 1;
+    const Slab sl = locate<T::SLAB>(job, s);
+    T::template run<DT, IMX>(job, sl, sub, valid);
+}
+
+template <class T, bool IMX>
+static int launch_iq(const Job& job, int dt, cudaStream_t st, const IqTables& tabs) {
+    const long long threads = job.nslabs * T::LANES;
+    const unsigned grid = (unsigned)((threads + IQ_TPB - 1) / IQ_TPB);
+    if (grid == 0) return SG_OK;
+    switch (dt) {
+        case SG_DT_BF16: k_quant_iq<T, SG_DT_BF16, IMX><<<grid, IQ_TPB, 0, st>>>(job, tabs); break;
+        case SG_DT_F16:  k_quant_iq<T, SG_DT_F16, IMX><<<grid, IQ_TPB, 0, st>>>(job, tabs); break;
+        case SG_DT_F32:  k_quant_iq<T, SG_DT_F32, IMX><<<grid, IQ_TPB, 0, st>>>(job, tabs); break;
+        default: return SG_ERR_ARG;
+    }
+    return cuda_ok(cudaGetLastError());
+}
+template <class T, bool IMX>
+static int launch_iq4(const Job& job, int dt, cudaStream_t st) {
+    const long long threads = job.nslabs * T::LANES;
+    const unsigned grid = (unsigned)((threads + 127) / 128);
+    if (grid == 0) return SG_OK;
+    switch (dt) {
+        case SG_DT_BF16: k_quant_iq4<T, SG_DT_BF16, IMX><<<grid, 128, 0, st>>>(job); break;
+        case SG_DT_F16:  k_quant_iq4<T, SG_DT_F16, IMX><<<grid, 128, 0, st>>>(job); break;
+        case SG_DT_F32:  k_quant_iq4<T, SG_DT_F32, IMX><<<grid, 128, 0, st>>>(job); break;
+        default: return SG_ERR_ARG;
+    }
+    return cuda_ok(cudaGetLastError());
+}
+
+static int dispatch_iq(int type, int variant, bool imx, int device, const Job& job, int dt, cudaStream_t st) {
+    if (type == SG_IQ4_NL) return imx ? launch_iq4<IQ4<false>, true>(job, dt, st) : launch_iq4<IQ4<false>, false>(job, dt, st);
+    if (type == SG_IQ4_XS) return imx ? launch_iq4<IQ4<true>, true>(job, dt, st) : launch_iq4<IQ4<true>, false>(job, dt, st);
+    const IqTables* tp = device_tables(device);
+    if (!tp) return SG_ERR_TABLES;
+    const IqTables& tabs = *tp;
+    switch (type) {
+        case SG_IQ2_XXS: return imx ? launch_iq<Lattice<SG_IQ2_XXS>, true>(job, dt, st, tabs) : SG_ERR_IMATRIX;
+        case SG_IQ2_XS:  return imx ? launch_iq<Lattice<SG_IQ2_XS>, true>(job, dt, st, tabs) : SG_ERR_IMATRIX;
+        case SG_IQ2_S:   return imx ? launch_iq<Lattice<SG_IQ2_S>, true>(job, dt, st, tabs) : launch_iq<Lattice<SG_IQ2_S>, false>(job, dt, st, tabs);
+        case SG_IQ3_XXS: return imx ? launch_iq<Lattice<SG_IQ3_XXS>, true>(job, dt, st, tabs) : launch_iq<Lattice<SG_IQ3_XXS>, false>(job, dt, st, tabs);
+        case SG_IQ3_S:   return imx ? launch_iq<Lattice<SG_IQ3_S>, true>(job, dt, st, tabs) : launch_iq<Lattice<SG_IQ3_S>, false>(job, dt, st, tabs);
+        case SG_IQ1_S:   return imx ? launch_iq<IQ1<false, 0>, true>(job, dt, st, tabs) : SG_ERR_IMATRIX;
+        case SG_IQ1_M:
+            if (variant == 1) return imx ? launch_iq<IQ1<true, 1>, true>(job, dt, st, tabs) : launch_iq<IQ1<true, 1>, false>(job, dt, st, tabs);
+            return imx ? launch_iq<IQ1<true, 0>, true>(job, dt, st, tabs) : launch_iq<IQ1<true, 0>, false>(job, dt, st, tabs);
+        default: return SG_ERR_TYPE;
+    }
+}
+
+}  // namespace sg

@@ -17,7 +17,7 @@ QFUN = {2: ("quantize_q4_0", 32, 18), 3: ("quantize_q4_1", 32, 20), 6: ("quantiz
         21: ("quantize_iq3_s", 256, 110), 22: ("quantize_iq2_s", 256, 82), 23: ("quantize_iq4_xs", 256, 136),
         29: ("quantize_iq1_m", 256, 56), 42: ("quantize_q2_0", 64, 18)}
 # types whose quantiser refuses to run without an importance matrix
-NEEDS_IMATRIX = {16, 17, 19, 22, 29}
+NEEDS_IMATRIX = {16, 17, 19}
 # (type, variant) pairs beyond variant 0 (seedpack/gpuquant.py:182-185)
 VARIANTS = {29: 1}
 

@@ -78,3 +78,20 @@ def test_ragged_multi_tensor_launch(gq):
         got = gq.quantize_tensors(t, srcs, imxs)
         for g, w in zip(got, wants):
             assert np.array_equal(g, w)
+
+
+@pytest.mark.parametrize("with_imx", [True, False])
+def test_iq1_m_variant_1(gq, with_imx):
+    """the older IQ1_M split search (direct sums instead of prefix sums) is a separate variant"""
+    import torch
+    if not ref.available():
+        pytest.skip("oracle/_ref not built")
+    nrows, npr = 16, 1024
+    bits = synth.weights(nrows, npr, seed=77)
+    imx = synth.imatrix(npr, seed=3) if with_imx else None
+    x32 = synth.bf16_bits_to_f32(bits).reshape(nrows, npr)
+    want = ref.quantize(29, x32, imx, variant=1)
+    x = torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16)
+    got = gq.quantize_tensors(29, [(x.reshape(-1), npr)], [imx], variant=1)[0]
+    assert gq.status() == 0
+    assert np.array_equal(got, want), _diff_report(29, np.asarray(got), want)
