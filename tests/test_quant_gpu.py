@@ -95,3 +95,19 @@ def test_iq1_m_variant_1(gq, with_imx):
     got = gq.quantize_tensors(29, [(x.reshape(-1), npr)], [imx], variant=1)[0]
     assert gq.status() == 0
     assert np.array_equal(got, want), _diff_report(29, np.asarray(got), want)
+
+
+def test_quantize_matches_golden_vectors(gq):
+    """outputs of the reference's own --cpu path, committed under tests/golden/"""
+    import os
+    import torch
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "quant_golden.npz"))
+    bits, imx = gold["bits"], gold["imatrix"]
+    x = torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16).reshape(-1)
+    for key in gold.files:
+        if not key.startswith("t"):
+            continue
+        t, use, v = key[1:].split("_")
+        got = gq.quantize_tensors(int(t), [(x, bits.shape[1])], [imx if use == "imx" else None], variant=int(v[1:]))[0]
+        assert np.array_equal(got, gold[key]), key
+    assert gq.status() == 0
