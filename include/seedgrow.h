@@ -126,6 +126,53 @@ SG_API int sg_quantize_tensors(int device, void *stream, int ggml_type, int vari
                         const sg_tensor *h_tensors, int n_tensors,
                         void *scratch, size_t scratch_bytes);
 
+/* ---- per-block residual ------------------------------------------------------------------------------
+ * Replaces the host-side NumPy helpers _xor_async / _diff_async / _count_diff / _xor3 (seedpack/repo3.py:456-510),
+ * which need a device-to-host copy of every prediction first.
+ *
+ * sg_residual_xor: out = a ^ b ^ c over nbytes (b and c may be NULL; out may be NULL when only the count is
+ * wanted, and may alias a).  *d_nonzero (device, caller-zeroed, accumulated with atomics) += non-zero bytes of
+ * the result: with b this is _count_diff(a, b); 0 means "prediction exact".  Any alignment is accepted; 16-byte
+ * aligned pointers take the vector path. */
+SG_API int sg_residual_xor(int device, void *stream, const void *a, const void *b, const void *c, void *out,
+                           size_t nbytes, unsigned long long *d_nonzero);
+/* Block-wise comparison of a stored tensor with its prediction (same(), seedpack/qr.py:114-117): ne_flags[i]
+ * (optional) = 1 where block i differs, *d_differ += number of differing blocks.  block_bytes must be even. */
+SG_API int sg_residual_blocks(int device, void *stream, const void *file, const void *pred, int block_bytes,
+                              long long n_blocks, unsigned char *ne_flags, unsigned long long *d_differ);
+
+/* ---- segment-parallel rANS over a symbol stream ------------------------------------------------------
+ * The coder of the reference's residual and base codecs (PUT / GET, seedpack/qr.py:651-663; seedpack/rans.py:54-105
+ * with PROB_BITS = pb): 32-bit state, byte renormalisation, RANS_L = 2^23, static tables whose frequencies sum
+ * to 2^pb.  Stream model: nsym byte symbols in blocks of block_len (multiple of 16); block b uses context table
+ * block_tab[b]; segments of seg_len symbols (multiple of block_len) are independent streams.  A segment's bytes
+ * are its final state, big endian, then the renormalisation bytes in decode order - the layout of the `s` part of
+ * a QR batch (seedpack/qr.py:1058-1061).
+ *
+ * sg_rans_hist    counts[tab * 256 + sym] += occurrences (caller zeroes counts)          (qr_hist's hadd, qr.py:380-383)
+ * sg_rans_tables  frequencies [ntab][256] (each used row summing to 2^pb) -> encoder entries enc_tab
+ *                 (8 bytes per (table, symbol): reciprocal, freq | cum << 16) and, if lut != NULL, the decoder's
+ *                 symbol-per-slot table [ntab << pb]                                     (cum_of gpu2.py:483-486, build_lut qr.py:889-895)
+ * sg_rans_encode  every segment into its private slot of `cap` bytes (multiple of 16, >= 128), written from the
+ *                 slot's end downwards; out_len[s] = bytes used, 0xffffffff = slot too small   (qr_enc's framing, qr.py:712-758)
+ * sg_scan_gather  off[0..nseg] = exclusive prefix sum of out_len (off[nseg] = total), then the segments' bytes
+ *                 copied to dst + off[s]; an overflowed segment sets SG_ST_OVERFLOW      (cumsum + gather, qr.py:1054-1056, 880-887)
+ * sg_rans_decode  inverse of encode; reads of segment s stay inside [off[s], off[s+1]) and a segment that does
+ *                 not end in the initial state sets SG_ST_CORRUPT (the reference reads unchecked, qr.py:662).
+ *                 `in` must be 16-byte aligned and readable up to the next multiple of 16 past off[nseg]. */
+SG_API int sg_rans_hist(int device, void *stream, const unsigned char *sym, const unsigned short *block_tab,
+                        int block_len, long long nsym, unsigned *counts);
+SG_API int sg_rans_tables(int device, void *stream, const unsigned short *freq, int ntab, int pb, void *enc_tab,
+                          unsigned char *lut);
+SG_API int sg_rans_encode(int device, void *stream, const unsigned char *sym, const unsigned short *block_tab,
+                          int block_len, long long nsym, int seg_len, int pb, const void *enc_tab,
+                          unsigned char *slots, size_t cap, unsigned *out_len);
+SG_API int sg_scan_gather(int device, void *stream, const unsigned char *slots, size_t cap, const unsigned *out_len,
+                          int nseg, unsigned char *dst, unsigned long long dst_cap, unsigned long long *off);
+SG_API int sg_rans_decode(int device, void *stream, const unsigned char *in, const unsigned long long *off,
+                          const unsigned short *block_tab, int block_len, long long nsym, int seg_len, int pb,
+                          const void *enc_tab, const unsigned char *lut, unsigned char *sym_out);
+
 #ifdef __cplusplus
 }
 #endif
