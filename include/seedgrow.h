@@ -173,6 +173,25 @@ SG_API int sg_rans_decode(int device, void *stream, const unsigned char *in, con
                           const unsigned short *block_tab, int block_len, long long nsym, int seg_len, int pb,
                           const void *enc_tab, const unsigned char *lut, unsigned char *sym_out);
 
+/* Allocation-free variant for hosts that cannot tolerate (or cannot supply memory for) a device allocation while
+ * they run - a packer that has split the measured free device memory into fixed windows, or a pipeline whose
+ * other streams must not be stalled by cudaMalloc's device-wide synchronisation.  It has no counterpart in the
+ * reference, whose kernels take every buffer from the caller's CuPy pool.
+ *
+ * Same result as sg_quantize_tensors for Q4_0, Q4_1, Q5_0, Q5_1 WITH an importance matrix (every tensor needs
+ * w_off >= 0; other types and matrix-free tensors need no scratch, use sg_quantize_tensors), but the per-row
+ * scratch is a fixed 256 KiB array inside the library, present on every GPU that loads it until the process exits.
+ * Limits and rules:
+ *   - at most 65536 rows per call over all tensors, else SG_ERR_LIMIT (split the launch);
+ *   - the first call on a device looks up the array's device address; make that first call outside any stream
+ *     capture;
+ *   - all calls share the one array (it is fully rewritten by each call before it is read, nothing needs
+ *     clearing), so two calls whose kernels may overlap on the GPU - different streams, or different threads -
+ *     race on it: keep calls to this entry point on one stream per device.
+ * Calls cudaMalloc / cudaFree never; returns the same status codes as sg_quantize_tensors. */
+SG_API int sg_quantize_legacy_imx_static(int device, void *stream, int ggml_type, const void *x, int x_dtype,
+                                         void *y, const float *w, const sg_tensor *h_tensors, int n_tensors);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,6 +1,7 @@
 // C-ABI entry points of the re-quantisers and their launch logic.
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "api_util.h"
 #include "quant_iq.cuh"
@@ -138,4 +139,54 @@ extern "C" int sg_quantize_tensors(int device, void* stream, int type, int varia
         if (rc != SG_OK) return rc;
     }
     return SG_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant of the importance-weighted legacy quantisers.
+//
+// Some hosts must not see a device allocation from this library once they are running: an archiver that has
+// measured free device memory and carved it into fixed windows (a hidden cudaMalloc can fail, or take the
+// block the next window was counting on), or a pipelined service in which cudaMalloc's implicit
+// device-wide synchronisation would stall every other stream.  Such callers cannot provide the per-row
+// scratch of sg_quantize_tensors from a pool either, so the scratch lives here, in a fixed array that
+// every GPU loading the library holds until the process exits.
+constexpr long long SG_STATIC_ROWS = 65536;                          // rows per call: 256 KiB of device memory
+static __device__ __align__(256) float g_static_rowstat[SG_STATIC_ROWS];
+
+static std::mutex g_static_mu;
+static float* g_static_ptr[64] = {nullptr};
+
+// Device address of the array for `device`, which must be current.  The array's name is only a host-side
+// handle; the address a kernel can use comes from cudaGetSymbolAddress, once per device.
+static int static_rowstat(int device, float** out) {
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_ptr[device]) {
+        float* p = nullptr;
+        const int rc = cuda_ok(cudaGetSymbolAddress((void**)&p, g_static_rowstat));
+        if (rc != SG_OK) return rc;
+        if (!p) return SG_ERR_CUDA;
+        g_static_ptr[device] = p;
+    }
+    *out = g_static_ptr[device];
+    return SG_OK;
+}
+
+extern "C" int sg_quantize_legacy_imx_static(int device, void* stream, int type, const void* x, int x_dtype, void* y,
+                                             const float* w, const sg_tensor* h, int n) {
+    if (!legacy_imx_type(type)) return SG_ERR_TYPE;
+    if (n < 0 || (n > 0 && (!h || !x || !y || !w))) return SG_ERR_ARG;
+    long long rows = 0;
+    for (int i = 0; i < n; ++i) {
+        if (h[i].w_off < 0) return SG_ERR_IMATRIX;           // the matrix-free routines need no scratch: use sg_quantize_tensors
+        if (h[i].n_rows < 0) return SG_ERR_ARG;
+        rows += h[i].n_rows;
+        if (rows > SG_STATIC_ROWS) return SG_ERR_LIMIT;
+    }
+    if (n == 0) return SG_OK;
+    int rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    float* scratch = nullptr;
+    rc = static_rowstat(device, &scratch);
+    if (rc != SG_OK) return rc;
+    return sg_quantize_tensors(device, stream, type, 0, x, x_dtype, y, w, h, n, scratch, (size_t)SG_STATIC_ROWS * sizeof(float));
 }
