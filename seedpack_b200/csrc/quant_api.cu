@@ -35,6 +35,20 @@ static int launch(const Job& job, int dt, cudaStream_t st) {
     return cuda_ok(cudaGetLastError());
 }
 
+template <int TYPE>
+static int launch_legacy_ref(const Job& job, int dt, cudaStream_t st) {
+    const long long threads = job.nslabs * (256 / LegacyRef<TYPE>::QK);
+    const unsigned grid = (unsigned)((threads + 127) / 128);
+    if (grid == 0) return SG_OK;
+    switch (dt) {
+        case SG_DT_BF16: k_quant_legacy_ref<TYPE, SG_DT_BF16><<<grid, 128, 0, st>>>(job); break;
+        case SG_DT_F16:  k_quant_legacy_ref<TYPE, SG_DT_F16><<<grid, 128, 0, st>>>(job); break;
+        case SG_DT_F32:  k_quant_legacy_ref<TYPE, SG_DT_F32><<<grid, 128, 0, st>>>(job); break;
+        default: return SG_ERR_ARG;
+    }
+    return cuda_ok(cudaGetLastError());
+}
+
 static int launch_meansq(const Job& job, long long nrows, int dt, cudaStream_t st) {
     const unsigned grid = (unsigned)((nrows + 3) / 4);
     switch (dt) {
@@ -50,12 +64,12 @@ static bool legacy_imx_type(int t) { return t == SG_Q4_0 || t == SG_Q4_1 || t ==
 
 static int dispatch(int type, int variant, bool imx, int device, const Job& job, int dt, cudaStream_t st) {
     switch (type) {
-        case SG_Q4_0: return imx ? launch<LegacyImx<SG_Q4_0>, true>(job, dt, st) : launch<LegacyRefSlab<SG_Q4_0>, false>(job, dt, st);
-        case SG_Q4_1: return imx ? launch<LegacyImx<SG_Q4_1>, true>(job, dt, st) : launch<LegacyRefSlab<SG_Q4_1>, false>(job, dt, st);
-        case SG_Q5_0: return imx ? launch<LegacyImx<SG_Q5_0>, true>(job, dt, st) : launch<LegacyRefSlab<SG_Q5_0>, false>(job, dt, st);
-        case SG_Q5_1: return imx ? launch<LegacyImx<SG_Q5_1>, true>(job, dt, st) : launch<LegacyRefSlab<SG_Q5_1>, false>(job, dt, st);
-        case SG_Q8_0: return launch<LegacyRefSlab<SG_Q8_0>, false>(job, dt, st);
-        case SG_Q2_0: return launch<LegacyRefSlab<SG_Q2_0>, false>(job, dt, st);
+        case SG_Q4_0: return imx ? launch<LegacyImx<SG_Q4_0>, true>(job, dt, st) : launch_legacy_ref<SG_Q4_0>(job, dt, st);
+        case SG_Q4_1: return imx ? launch<LegacyImx<SG_Q4_1>, true>(job, dt, st) : launch_legacy_ref<SG_Q4_1>(job, dt, st);
+        case SG_Q5_0: return imx ? launch<LegacyImx<SG_Q5_0>, true>(job, dt, st) : launch_legacy_ref<SG_Q5_0>(job, dt, st);
+        case SG_Q5_1: return imx ? launch<LegacyImx<SG_Q5_1>, true>(job, dt, st) : launch_legacy_ref<SG_Q5_1>(job, dt, st);
+        case SG_Q8_0: return launch_legacy_ref<SG_Q8_0>(job, dt, st);
+        case SG_Q2_0: return launch_legacy_ref<SG_Q2_0>(job, dt, st);
         case SG_Q2_K: return imx ? launch<Q2K, true>(job, dt, st) : launch<Q2K, false>(job, dt, st);
         case SG_Q3_K: return imx ? launch<Q3K, true>(job, dt, st) : launch<Q3K, false>(job, dt, st);
         case SG_Q4_K: return imx ? launch<Q45K<4>, true>(job, dt, st) : launch<Q45K<4>, false>(job, dt, st);

@@ -32,25 +32,24 @@ constexpr int IQ_TPB = 64;      // threads per CTA of the IQ kernels (bounds the
 
 // ==================================================================================================
 // IQ4_NL / IQ4_XS
-SG_DEVINL int best_index_iq4(float x) {
-    // best_index_int8(16, kvalues_iq4nl, x), ggml-quants.c:28-37
-    if (x <= (float)c_iq4nl[0]) return 0;
-    if (x >= (float)c_iq4nl[15]) return 15;
-    int ml = 0, mu = 15;
-#pragma unroll
-    for (int it = 0; it < 4; ++it) {
-        if (mu - ml > 1) {
-            const int mav = (ml + mu) / 2;
-            if (x < (float)c_iq4nl[mav]) mu = mav; else ml = mav;
-        }
-    }
-    return fsub(x, (float)c_iq4nl[mu - 1]) < fsub((float)c_iq4nl[mu], x) ? mu - 1 : mu;
+// best_index_int8(16, kvalues_iq4nl, x), ggml-quants.c:28-37, without data-dependent table walks: the binary
+// search ends with val[ml] <= x < val[ml + 1], i.e. ml = number of interior levels that are <= x (the two early
+// returns of the C code fall out of the same formula); the levels themselves come from a 16-entry table in
+// shared memory (16 distinct banks, so a warp's lookups never conflict).  Returns the index, *q = its level.
+SG_DEVINL int best_index_iq4(float x, const float* __restrict__ kv, float* q) {
+    int ml = (x >= -104.f) + (x >= -83.f) + (x >= -65.f) + (x >= -49.f) + (x >= -35.f) + (x >= -22.f) + (x >= -10.f) +
+             (x >= 1.f) + (x >= 13.f) + (x >= 25.f) + (x >= 38.f) + (x >= 53.f) + (x >= 69.f) + (x >= 89.f);
+    if (x != x) ml = 14;                                   // NaN: every `x < val` test of the search fails
+    const float a = kv[ml], b = kv[ml + 1];
+    const bool lower = fsub(x, a) < fsub(b, x);
+    *q = lower ? a : b;
+    return lower ? ml : ml + 1;
 }
 
 template <bool XS> struct IQ4 {
     static constexpr int SLAB = 256, SUB = 32, LANES = 8, QK = XS ? 256 : 32, BS = XS ? 136 : 18;
     template <int DT, bool IMX>
-    static SG_DEVINL void run(const Job& job, const Slab& sl, int sub, bool valid) {
+    static SG_DEVINL void run(const Job& job, const Slab& sl, int sub, bool valid, const float* __restrict__ kv) {
         const bool live = valid && sub * 32 < sl.n;
         float x[32], wt[32];
         if (live || XS) load_vals<DT, 32>(job.x, sl.x + sub * 32, x);
@@ -80,14 +79,15 @@ template <bool XS> struct IQ4 {
 #pragma unroll
         for (int j = 0; j < 32; ++j) { const float ax = fabsf(x[j]); if (ax > amax) { amax = ax; mx = x[j]; } }
         float d = 0.f;
-        const float v0 = (float)c_iq4nl[0];
+        const float v0 = kv[0];                       // -127, read at run time: the division below must stay a division
         if (!(amax < SG_GROUP_MAX_EPS)) {
             d = fdiv(-mx, v0);                        // ntry > 0: -max / values[0]
             float id = frcp(d);
             float sumqx = 0.f, sumq2 = 0.f;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                const float q = (float)c_iq4nl[best_index_iq4(fmul(id, x[j]))];
+                float q;
+                best_index_iq4(fmul(id, x[j]), kv, &q);
                 sumqx = fadd(sumqx, fmul(fmul(wt[j], q), x[j]));
                 sumq2 = fadd(sumq2, fmul(fmul(wt[j], q), q));
             }
@@ -95,11 +95,12 @@ template <bool XS> struct IQ4 {
             float best = fmul(d, sumqx);
 #pragma unroll 1
             for (int itry = -7; itry <= 7; ++itry) {
-                id = fdiv((float)(itry + (int)c_iq4nl[0]), mx);
+                id = fdiv((float)(itry - 127), mx);
                 sumqx = 0.f; sumq2 = 0.f;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                    const float q = (float)c_iq4nl[best_index_iq4(fmul(id, x[j]))];
+                    float q;
+                    best_index_iq4(fmul(id, x[j]), kv, &q);
                     sumqx = fadd(sumqx, fmul(fmul(wt[j], q), x[j]));
                     sumq2 = fadd(sumq2, fmul(fmul(wt[j], q), q));
                 }
@@ -130,8 +131,9 @@ template <bool XS> struct IQ4 {
         uint32_t qs[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const uint32_t a = (uint32_t)best_index_iq4(fmul(idl, x[j]));
-            const uint32_t b = (uint32_t)best_index_iq4(fmul(idl, x[j + 16]));
+            float qa, qb;
+            const uint32_t a = (uint32_t)best_index_iq4(fmul(idl, x[j]), kv, &qa);
+            const uint32_t b = (uint32_t)best_index_iq4(fmul(idl, x[j + 16]), kv, &qb);
             qs[j >> 2] |= (a | (b << 4)) << (8 * (j & 3));
         }
         if (XS) {
@@ -862,8 +864,11 @@ __global__ void __launch_bounds__(128) k_quant_iq4(const __grid_constant__ Job j
     const int sub = (int)(g - s * LANES);
     const bool valid = s < job.nslabs;
     if (!valid) s = job.nslabs - 1;
+    __shared__ float kv[16];
+    if (threadIdx.x < 16) kv[threadIdx.x] = (float)c_iq4nl[threadIdx.x];
+    __syncthreads();
     const Slab sl = locate<T::SLAB>(job, s);
-    T::template run<DT, IMX>(job, sl, sub, valid);
+    T::template run<DT, IMX>(job, sl, sub, valid, kv);
 }
 
 template <class T, bool IMX>

@@ -194,6 +194,52 @@ template <int TYPE> struct LegacyRefSlab {
     }
 };
 
+// Memory-bound launch shape for the matrix-free legacy types: 128 blocks per CTA.  Each thread builds its block
+// in shared memory; when the CTA's 128 blocks are one contiguous, 16-byte aligned run of the output (the usual
+// case: full slabs of one tensor) the CTA then streams 128 * BS bytes out with 16-byte stores.  Blocks of
+// 18..34 bytes written straight from the threads would cost up to 17 two-byte stores each.
+template <int TYPE, int DT>
+__global__ void __launch_bounds__(128) k_quant_legacy_ref(const __grid_constant__ Job job) {
+    using R = LegacyRef<TYPE>;
+    constexpr int QK = R::QK, BS = R::BS, LANES = 256 / QK;
+    __shared__ __align__(16) uint8_t stage[128 * BS];
+    __shared__ long long s_first;
+    __shared__ int s_ok;
+    const long long g = (long long)blockIdx.x * 128 + threadIdx.x;
+    const long long s = g / LANES;
+    const int sub = (int)(g - s * LANES);
+    const bool valid = s < job.nslabs;
+    bool live = false;
+    long long yoff = 0;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (valid) {
+        const Slab sl = locate<256>(job, s);
+        live = sub * QK < sl.n;
+        if (live) {
+            yoff = out_offset<256, QK, BS>(sl, sub);
+            float x[QK];
+            load_vals<DT, QK>(job.x, sl.x + sub * QK, x);
+            R::block(x, stage + threadIdx.x * BS);
+        }
+    }
+    if (threadIdx.x == 0) s_first = yoff;
+    __syncthreads();
+    // contiguous run?  every thread's block must sit at first + tid * BS, and the run must start 16-byte aligned
+    const bool mine = live && yoff == s_first + (long long)threadIdx.x * BS && ((s_first + (long long)(uintptr_t)job.y) & 15) == 0;
+    if (!mine) s_ok = 0;
+    __syncthreads();
+    if (s_ok) {
+        uint4* dst = reinterpret_cast<uint4*>(job.y + s_first);
+        const uint4* src = reinterpret_cast<const uint4*>(stage);
+        for (int i = threadIdx.x; i < 128 * BS / 16; i += 128) dst[i] = src[i];
+    } else if (live) {
+        uint8_t* y = job.y + yoff;
+        const uint16_t* src = reinterpret_cast<const uint16_t*>(stage + threadIdx.x * BS);
+        for (int i = 0; i < BS / 2; ++i) reinterpret_cast<uint16_t*>(y)[i] = src[i];
+    }
+}
+
 // ---- importance-matrix paths -----------------------------------------------------------------------
 template <int TYPE> struct LegacyImx {
     static constexpr int SLAB = 256, SUB = 32, LANES = 8, QK = 32;
