@@ -173,6 +173,29 @@ SG_API int sg_rans_decode(int device, void *stream, const unsigned char *in, con
                           const unsigned short *block_tab, int block_len, long long nsym, int seg_len, int pb,
                           const void *enc_tab, const unsigned char *lut, unsigned char *sym_out);
 
+/* ---- QR: quantiser-aware residual coder ---------------------------------------------------------------
+ * Replaces qr_hist / qr_enc / qr_dec (seedpack/qr.py:674-807) for the scalar-code types
+ * (2 3 6 7 8 10 11 12 13 14 20 23 42).  A batch = tensors of one ggml type T laid back to back as blocks:
+ *   F stored blocks, P predicted blocks (both nblocks * block_bytes), ne[b] = 1 where block b differs from its
+ *   prediction (from sg_residual_blocks), seed = base weights buffer (per tensor: byte offset + type in TM),
+ *   tm / sg = per-tensor and per-segment records with the reference's layouts
+ *     TM { int64 blk0, seed_off; int32 seed_type, cols; int64 imx_off }   (qr.py:898)
+ *     SG { int32 t, nb; int64 b0 }                                        (qr.py:900)
+ *   seed types: 30 BF16, 0 F32, 1 F16, 98 none (per-column RMS floats), 99 explicit (x, h) float pairs.
+ * Context tables are addressed by their raw id (0..293, qr.py:50-53): counts is [294 * 256], enc_tab / lut come from
+ * sg_rans_tables on the full 294-row frequency array (unused rows zero), pb = 12.  mv = model version (1 or 2,
+ * qr.py:54).  Streams, slots, out_len and offsets are those of sg_rans_encode / sg_scan_gather / sg_rans_decode.
+ * sg_qr_decode writes every block of F (equal blocks are copied from P). */
+SG_API int sg_qr_hist(int device, void *stream, int T, const unsigned char *F, const unsigned char *P,
+                      const unsigned char *ne, const unsigned char *seed, const void *tm, const void *sg, int nseg,
+                      unsigned *counts, int mv);
+SG_API int sg_qr_encode(int device, void *stream, int T, const unsigned char *F, const unsigned char *P,
+                        const unsigned char *ne, const unsigned char *seed, const void *tm, const void *sg, int nseg,
+                        const void *enc_tab, unsigned char *slots, size_t cap, unsigned *out_len, int mv);
+SG_API int sg_qr_decode(int device, void *stream, int T, const unsigned char *in, const unsigned long long *off,
+                        const unsigned char *P, const unsigned char *seed, const void *tm, const void *sg, int nseg,
+                        const void *enc_tab, const unsigned char *lut, unsigned char *F, int mv);
+
 /* Allocation-free variant for hosts that cannot tolerate (or cannot supply memory for) a device allocation while
  * they run - a packer that has split the measured free device memory into fixed windows, or a pipeline whose
  * other streams must not be stalled by cudaMalloc's device-wide synchronisation.  It has no counterpart in the

@@ -1,0 +1,214 @@
+"""QR: quantiser-aware residual coding of a stored quantised tensor against its regrown prediction - host side.
+
+Mirror of the reference's `qr.encode` / `qr.decode` (seedpack/qr.py:1007-1090) over the seedgrow C ABI, with the
+same argument meanings and the same bytes out: segment layout (`seg_blocks`, `_layout`, qr.py:952-968), batch
+split (`batches`, 971-980), table normalisation (rans.normalize = qr.py:904-923), table storage
+(`store_tables` / `load_tables`, seedpack/gpu2.py:489-500), the pack framing (seedpack/codecs_gguf.py:33-56) and
+the slot-doubling retry (qr.py:1043-1053).  Arrays are torch CUDA tensors (or host numpy / bytes, uploaded here).
+"""
+import ctypes
+import struct
+
+import numpy as np
+import torch
+
+from . import _lib, zstd
+from .rans import PB, normalize
+
+SELF_TYPES = {2, 3, 6, 7, 8, 10, 11, 12, 13, 14, 20, 23, 42}
+GRID_TYPES = {16, 17, 18, 19, 21, 22, 29}
+QR_TYPES = SELF_TYPES | GRID_TYPES
+BS = {2: 18, 3: 20, 6: 22, 7: 24, 8: 34, 10: 84, 11: 110, 12: 144, 13: 176, 14: 210, 20: 18, 23: 136, 42: 18,
+      16: 66, 17: 74, 18: 98, 19: 50, 21: 110, 22: 82, 29: 56}
+QK = {t: (32 if t in (2, 3, 6, 7, 8, 20) else 64 if t == 42 else 256) for t in QR_TYPES}
+NSB_MAX = 20
+NTAB2 = NSB_MAX + 64 + 2 + 208
+MODEL = 2
+BATCH = 384 << 20
+TM_DT = np.dtype([("blk0", "<i8"), ("seed_off", "<i8"), ("seed_type", "<i4"), ("cols", "<i4"), ("imx_off", "<i8")])
+SG_DT = np.dtype([("t", "<i4"), ("nb", "<i4"), ("b0", "<i8")])
+
+
+# ---- framing shared with the archive layer -----------------------------------------------------------------------
+def pack(chunks):
+    out = [struct.pack("<I", len(chunks))]
+    for name, data in chunks.items():
+        nb = name.encode()
+        out += [struct.pack("<H", len(nb)), nb, struct.pack("<Q", len(data)), bytes(data)]
+    return b"".join(out)
+
+
+def unpack(buf):
+    (n,), pos, chunks = struct.unpack_from("<I", buf), 4, {}
+    for _ in range(n):
+        (ln,) = struct.unpack_from("<H", buf, pos); pos += 2
+        name = bytes(buf[pos:pos + ln]).decode(); pos += ln
+        (dl,) = struct.unpack_from("<Q", buf, pos); pos += 8
+        chunks[name] = buf[pos:pos + dl]; pos += dl
+    return chunks
+
+
+def store_tables(freq, used):
+    u = np.asarray(used).astype(np.int64)
+    du = np.diff(u, prepend=0).astype(np.uint32)
+    return zstd.compress(struct.pack("<I", len(u)) + du.tobytes() + np.ascontiguousarray(freq, np.uint16).tobytes(), 19)
+
+
+def load_tables(buf):
+    raw = zstd.decompress(bytes(buf), max_output_size=1 << 30)
+    (n,) = struct.unpack_from("<I", raw)
+    used = np.cumsum(np.frombuffer(raw, np.uint32, n, 4).astype(np.int64))
+    freq = np.frombuffer(raw, np.uint16, n * 256, 4 + 4 * n).reshape(n, 256)
+    return freq, used
+
+
+def seg_blocks(T):
+    """blocks per rANS segment: about 16 K symbols"""
+    return max(16, 16384 // QK[T])
+
+
+def _layout(T, nblocks):
+    sb = seg_blocks(T)
+    tm = np.zeros(len(nblocks), TM_DT)
+    segs, b0 = [], 0
+    for i, nb in enumerate(nblocks):
+        tm[i]["blk0"] = b0
+        for o in range(0, nb, sb):
+            segs.append((i, min(sb, nb - o), b0 + o))
+        b0 += nb
+    sg = np.array(segs, SG_DT) if segs else np.zeros(0, SG_DT)
+    return tm, sg, b0
+
+
+def batches(T, sizes):
+    """tensor indices split into coding batches of about BATCH bytes (same split on both sides)"""
+    out, cur, n = [], [], 0
+    for i, s in enumerate(sizes):
+        if cur and n + s > BATCH:
+            out.append(cur); cur, n = [], 0
+        cur.append(i); n += s
+    if cur:
+        out.append(cur)
+    return out
+
+
+# ---- device plumbing ---------------------------------------------------------------------------------------------------
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _dev_u8(a, device):
+    if isinstance(a, torch.Tensor):
+        return a.to(device).view(torch.uint8).reshape(-1)
+    return torch.from_numpy(np.frombuffer(memoryview(a), np.uint8).copy() if not isinstance(a, np.ndarray) else np.ascontiguousarray(a).view(np.uint8).reshape(-1)).to(device)
+
+
+def _gather(arrs, device):
+    parts = [_dev_u8(a, device) for a in arrs]
+    return parts[0].contiguous() if len(parts) == 1 else torch.cat(parts)
+
+
+class QRCodec:
+    def __init__(self, device=None):
+        self.device = torch.device("cuda", torch.cuda.current_device() if device is None else device)
+        self.lib = _lib.lib()
+
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _status(self):
+        bits = ctypes.c_int(0)
+        _lib.check(self.lib.sg_status_fetch(self.device.index, self._stream(), ctypes.byref(bits)), "sg_status_fetch")
+        return bits.value
+
+    def _records(self, T, nbs, seed_offs, seed_types, cols, imx_offs):
+        tm, sg, nb = _layout(T, nbs)
+        tm["seed_off"], tm["seed_type"], tm["cols"], tm["imx_off"] = seed_offs, seed_types, cols, imx_offs
+        tm_d = torch.from_numpy(tm.view(np.uint8).copy()).to(self.device)
+        sg_d = torch.from_numpy(sg.view(np.uint8).copy()).to(self.device)
+        return tm_d, sg_d, len(sg), nb
+
+    def _tables(self, freq, used, lut):
+        full = np.zeros((NTAB2, 256), np.uint16)
+        full[np.asarray(used)] = freq
+        f = torch.from_numpy(full.view(np.int16)).to(self.device)
+        enc = torch.empty(NTAB2 * 256 * 2, dtype=torch.int32, device=self.device)
+        l = torch.empty(NTAB2 << PB, dtype=torch.uint8, device=self.device) if lut else None
+        _lib.check(self.lib.sg_rans_tables(self.device.index, self._stream(), _p(f), NTAB2, PB, _p(enc), _p(l)), "sg_rans_tables")
+        return enc, l
+
+    def encode(self, T, items, seed_dev, imx_dev=None, mv=None):
+        """items: [(file tensor bytes, predicted bytes, seed byte offset, seed type[, weights per row, imatrix
+        offset])] of one batch, all of ggml type T -> bytes of the coded batch (seedpack/qr.py:1007-1061)"""
+        if T not in SELF_TYPES:
+            raise NotImplementedError(f"QR coding of ggml type {T} (grid types) is not available yet")
+        mv = MODEL if mv is None else mv
+        bs, d, st = BS[T], self.device.index, self._stream()
+        nbs = [len(it[0]) // bs for it in items]
+        tm_d, sg_d, nseg, nb = self._records(T, nbs, [it[2] for it in items], [it[3] for it in items],
+                                             [it[4] if len(it) > 4 else 0 for it in items],
+                                             [it[5] if len(it) > 5 else -1 for it in items])
+        F = _gather([it[0] for it in items], self.device)
+        P = _gather([it[1] for it in items], self.device)
+        seed = _dev_u8(seed_dev, self.device)
+        ne = torch.empty(max(nb, 1), dtype=torch.uint8, device=self.device)
+        ndiff = torch.zeros(1, dtype=torch.int64, device=self.device)
+        _lib.check(self.lib.sg_residual_blocks(d, st, _p(F), _p(P), bs, nb, _p(ne), _p(ndiff)), "sg_residual_blocks")
+        counts = torch.zeros(NTAB2 * 256, dtype=torch.int32, device=self.device)
+        _lib.check(self.lib.sg_qr_hist(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(counts), mv), "sg_qr_hist")
+        freq, used = normalize(counts.cpu().numpy().astype(np.uint32).reshape(NTAB2, 256))
+        enc, _ = self._tables(freq, used, lut=False)
+        cap = seg_blocks(T) * (QK[T] + NSB_MAX) * 2 + 1024
+        cap = (cap + 15) // 16 * 16
+        for _ in range(3):
+            slots = torch.empty(max(nseg, 1) * cap, dtype=torch.uint8, device=self.device)
+            lens = torch.zeros(max(nseg, 1), dtype=torch.int32, device=self.device)
+            _lib.check(self.lib.sg_qr_encode(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(enc), _p(slots),
+                                             cap, _p(lens), mv), "sg_qr_encode")
+            off = torch.empty(nseg + 1, dtype=torch.int64, device=self.device)
+            _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, None, 0, _p(off)), "sg_scan_gather")
+            if not (self._status() & 2):
+                break
+            cap *= 2
+        else:
+            raise RuntimeError("QR segment overflow")
+        total = int(off[-1].item())
+        dst = torch.empty(total + 32, dtype=torch.uint8, device=self.device)
+        _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, _p(dst), total, _p(off)), "sg_scan_gather")
+        stream = dst[:total].cpu().numpy().tobytes()
+        lens_h = lens[:nseg].cpu().numpy().view(np.uint32)
+        out = {"t": store_tables(freq, used), "l": zstd.compress(lens_h.astype(np.uint32).tobytes(), 19), "s": stream}
+        if mv != 1:
+            out["v"] = bytes([mv])
+        return pack(out)
+
+    def decode(self, T, buf, items, seed_dev, imx_dev=None):
+        """items: [(predicted bytes, seed byte offset, seed type[, weights per row, imatrix offset])] -> device uint8
+        tensor of the batch's tensors back to back (seedpack/qr.py:1064-1090)"""
+        if T not in SELF_TYPES:
+            raise NotImplementedError(f"QR coding of ggml type {T} (grid types) is not available yet")
+        ch = unpack(buf)
+        mv = ch["v"][0] if "v" in ch else 1
+        bs, d, st = BS[T], self.device.index, self._stream()
+        nbs = [len(it[0]) // bs for it in items]
+        tm_d, sg_d, nseg, nb = self._records(T, nbs, [it[1] for it in items], [it[2] for it in items],
+                                             [it[3] if len(it) > 3 else 0 for it in items],
+                                             [it[4] if len(it) > 4 else -1 for it in items])
+        P = _gather([it[0] for it in items], self.device)
+        seed = _dev_u8(seed_dev, self.device)
+        freq, used = load_tables(ch["t"])
+        enc, lut = self._tables(freq, used, lut=True)
+        lens = np.frombuffer(zstd.decompress(bytes(ch["l"]), max_output_size=1 << 30), np.uint32).astype(np.uint64)
+        offs = np.zeros(nseg + 1, np.uint64); offs[1:] = np.cumsum(lens)
+        s = np.frombuffer(ch["s"], np.uint8)
+        if int(offs[-1]) != len(s):
+            raise ValueError("QR batch: segment lengths do not add up to the stream length")
+        sd = torch.zeros((len(s) + 31) // 16 * 16, dtype=torch.uint8, device=self.device)
+        sd[:len(s)] = torch.from_numpy(s.copy()).to(self.device)
+        F = torch.empty(nb * bs, dtype=torch.uint8, device=self.device)
+        off_d = torch.from_numpy(offs.view(np.int64)).to(self.device)
+        _lib.check(self.lib.sg_qr_decode(d, st, T, _p(sd), _p(off_d), _p(P), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(enc), _p(lut), _p(F),
+                                         mv), "sg_qr_decode")
+        if self._status() & 4:
+            raise ValueError("QR batch: corrupt stream")
+        return F

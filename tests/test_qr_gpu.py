@@ -1,0 +1,77 @@
+"""QR residual coder through the C ABI against coded batches made by the reference's own qr.encode
+(tests/golden/qr_golden.npz, written by tests/golden/make_qr_golden.py): the whole packed batch - tables, segment
+lengths, stream, model byte - must be byte-identical, and decoding the reference's batch must restore the file."""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+G = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "qr_golden.npz"))
+TYPES = [int(t) for t in G["types"]]
+SHAPES = [tuple(int(v) for v in s) for s in G["shapes"]]
+OFFS = [int(o) for o in G["seed_offs"]]
+
+
+def _items(T):
+    from seedpack_b200.qr import BS
+    F, P, bs = G[f"F_{T}"], G[f"P_{T}"], BS[T]
+    from seedpack_b200.qr import QK
+    enc, dec, o = [], [], 0
+    for k, (nr, npr) in enumerate(SHAPES):
+        n = nr * npr // QK[T] * bs
+        enc.append((F[o:o + n], P[o:o + n], OFFS[k], 30, npr, -1))
+        dec.append((P[o:o + n], OFFS[k], 30, npr, -1))
+        o += n
+    return enc, dec
+
+
+@pytest.mark.parametrize("mv", [1, 2])
+@pytest.mark.parametrize("T", TYPES)
+def test_encode_is_byte_identical_to_reference(T, mv):
+    from seedpack_b200.qr import QRCodec, unpack
+    c = QRCodec()
+    enc, _ = _items(T)
+    got = c.encode(T, enc, G["seed_bits"].view(np.uint8), None, mv=mv)
+    want = G[f"B_{T}_{mv}"].tobytes()
+    if got != want:
+        a, b = unpack(got), unpack(want)
+        diff = {k: (len(a.get(k, b"")), len(b.get(k, b"")), bytes(a.get(k, b"")) == bytes(b.get(k, b""))) for k in set(a) | set(b)}
+        raise AssertionError(f"type {T} model {mv}: parts (ours, reference, equal) = {diff}")
+
+
+@pytest.mark.parametrize("mv", [1, 2])
+@pytest.mark.parametrize("T", TYPES)
+def test_decode_of_reference_batch_restores_file(T, mv):
+    from seedpack_b200.qr import QRCodec
+    c = QRCodec()
+    _, dec = _items(T)
+    out = c.decode(T, G[f"B_{T}_{mv}"].tobytes(), dec, G["seed_bits"].view(np.uint8))
+    assert np.array_equal(out.cpu().numpy(), G[f"F_{T}"])
+
+
+def test_exact_prediction_codes_to_flags_only():
+    """a file equal to its prediction: one flag symbol per block, every other table unused"""
+    from seedpack_b200.qr import QRCodec, unpack, load_tables
+    c = QRCodec()
+    T = 12
+    enc, dec = _items(T)
+    same = [(it[1], it[1]) + it[2:] for it in enc]
+    buf = c.encode(T, same, G["seed_bits"].view(np.uint8))
+    freq, used = load_tables(unpack(buf)["t"])
+    assert used.tolist() == [85] and freq[0, 1] == 4096          # FLAG + prev = 1, symbol "equal"
+    out = c.decode(T, buf, dec, G["seed_bits"].view(np.uint8))
+    assert np.array_equal(out.cpu().numpy(), G[f"P_{T}"])
+
+
+def test_corrupt_batch_is_rejected():
+    from seedpack_b200.qr import QRCodec, unpack, pack
+    c = QRCodec()
+    _, dec = _items(8)
+    ch = {k: bytes(v) for k, v in unpack(G["B_8_2"].tobytes()).items()}
+    s = bytearray(ch["s"]); s[len(s) // 2] ^= 0x40; ch["s"] = bytes(s)
+    try:
+        out = c.decode(8, pack(ch), dec, G["seed_bits"].view(np.uint8))
+    except ValueError:
+        return
+    assert not np.array_equal(out.cpu().numpy(), G["F_8"])
