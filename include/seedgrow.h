@@ -174,8 +174,9 @@ SG_API int sg_rans_decode(int device, void *stream, const unsigned char *in, con
                           const void *enc_tab, const unsigned char *lut, unsigned char *sym_out);
 
 /* ---- QR: quantiser-aware residual coder ---------------------------------------------------------------
- * Replaces qr_hist / qr_enc / qr_dec (seedpack/qr.py:674-807) for the scalar-code types
- * (2 3 6 7 8 10 11 12 13 14 20 23 42).  A batch = tensors of one ggml type T laid back to back as blocks:
+ * Replaces qr_hist / qr_enc / qr_dec (seedpack/qr.py:674-807) for the scalar-code types (2 3 6 7 8 10 11 12 13 14
+ * 20 23 42) and the lattice types (16 17 18 19 21 22 29; these need sg_tables_install first and use the importance
+ * vector imx + TM.imx_off of each tensor, imx_off < 0 = none; imx may be NULL when no tensor has one).  A batch = tensors of one ggml type T laid back to back as blocks:
  *   F stored blocks, P predicted blocks (both nblocks * block_bytes), ne[b] = 1 where block b differs from its
  *   prediction (from sg_residual_blocks), seed = base weights buffer (per tensor: byte offset + type in TM),
  *   tm / sg = per-tensor and per-segment records with the reference's layouts
@@ -188,13 +189,14 @@ SG_API int sg_rans_decode(int device, void *stream, const unsigned char *in, con
  * sg_qr_decode writes every block of F (equal blocks are copied from P). */
 SG_API int sg_qr_hist(int device, void *stream, int T, const unsigned char *F, const unsigned char *P,
                       const unsigned char *ne, const unsigned char *seed, const void *tm, const void *sg, int nseg,
-                      unsigned *counts, int mv);
+                      const float *imx, unsigned *counts, int mv);
 SG_API int sg_qr_encode(int device, void *stream, int T, const unsigned char *F, const unsigned char *P,
                         const unsigned char *ne, const unsigned char *seed, const void *tm, const void *sg, int nseg,
-                        const void *enc_tab, unsigned char *slots, size_t cap, unsigned *out_len, int mv);
+                        const float *imx, const void *enc_tab, unsigned char *slots, size_t cap, unsigned *out_len,
+                        int mv);
 SG_API int sg_qr_decode(int device, void *stream, int T, const unsigned char *in, const unsigned long long *off,
                         const unsigned char *P, const unsigned char *seed, const void *tm, const void *sg, int nseg,
-                        const void *enc_tab, const unsigned char *lut, unsigned char *F, int mv);
+                        const float *imx, const void *enc_tab, const unsigned char *lut, unsigned char *F, int mv);
 
 /* Allocation-free variant for hosts that cannot tolerate (or cannot supply memory for) a device allocation while
  * they run - a packer that has split the measured free device memory into fixed windows, or a pipeline whose

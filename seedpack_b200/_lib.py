@@ -47,9 +47,9 @@ SIGNATURES = {
     "sg_rans_encode": (_I, [_I, _P, _P, _P, _I, _L, _I, _I, _P, _P, _Z, _P]),
     "sg_scan_gather": (_I, [_I, _P, _P, _Z, _P, _I, _P, ctypes.c_uint64, _P]),
     "sg_rans_decode": (_I, [_I, _P, _P, _P, _P, _I, _L, _I, _I, _P, _P, _P]),
-    "sg_qr_hist": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _I]),
-    "sg_qr_encode": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _Z, _P, _I]),
-    "sg_qr_decode": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I]),
+    "sg_qr_hist": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I]),
+    "sg_qr_encode": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _Z, _P, _I]),
+    "sg_qr_decode": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I]),
     "sg_quantize_legacy_imx_static": (_I, [_I, _P, _I, _P, _I, _P, _P, ctypes.POINTER(sg_tensor), _I]),
 }
 

@@ -35,80 +35,257 @@ template <class E> SG_DEVINL void field_symbols(int kd, int any, int tv, int dl,
     else emit(fctx(kd, any), dl & 255);
 }
 
-// ---- histogram -----------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(64) k_qr_hist(int T, const uchar* __restrict__ F, const uchar* __restrict__ P,
-                                                const uchar* __restrict__ ne, const uchar* __restrict__ seed,
-                                                const TM* __restrict__ tm, const SG* __restrict__ sg, int nseg,
-                                                unsigned* __restrict__ counts, int mv) {
+// ---- one coder for the three passes ---------------------------------------------------------------------------
+struct Coder {
+    int mode;                       // 0 histogram, 1 encode (symbols arrive in reverse decode order), 2 decode
+    unsigned* counts;
+    const RansSym* enc; const uchar* lut;
+    unsigned x; ByteWriterDown wr; ByteReaderUp rd; uchar* slot; bool ovf;
+    SG_DEVINL void sym(int tab, int& s) {
+        if (mode == 0) { atomicAdd(counts + tab * 256 + s, 1u); return; }
+        if (mode == 1) {
+            if (ovf) return;
+            rans_put<12>(x, wr, enc[tab * 256 + s]);
+            if (wr.ptr() < slot + 64) ovf = true;
+            return;
+        }
+        s = (int)rans_get<12>(x, rd, lut + ((size_t)tab << 12), enc + tab * 256);
+    }
+    SG_DEVINL void put(int tab, int s) { sym(tab, s); }
+    SG_DEVINL int get(int tab) { int s = 0; sym(tab, s); return s; }
+};
+
+// ---- grid types: rank of the true lattice point among all points, by weighted distance to the seed -------------
+// Per pair of weights a table in shared memory holds the weighted squared error of every pair of levels, so the
+// distance of a lattice point is N/2 lookups (qr.py:496-515).  Laid out [entry][thread]: conflict-free.
+constexpr int TOPK = 16;
+constexpr int QR_TPB = 64;
+
+template <int N, bool SGN>
+SG_DEVINL void pair_tables(float* tab, const float* uu, const float* ww, float dl) {
+    constexpr int B = N == 8 ? 2 : 3, L = 1 << B, E = L * L;
+    for (int p = 0; p < N / 2; ++p)
+        for (int e = 0; e < E; ++e) {
+            const int la = e & (L - 1), lb = e >> B;
+            const float qa = SGN ? (float)(2 * la + 1) : (float)(la - 1) + dl;
+            const float qb = SGN ? (float)(2 * lb + 1) : (float)(lb - 1) + dl;
+            const float ea = qa - uu[2 * p], eb = qb - uu[2 * p + 1];
+            tab[(p * E + e) * QR_TPB + threadIdx.x] = ww[2 * p] * (ea * ea) + ww[2 * p + 1] * (eb * eb);
+        }
+}
+template <int N> SG_DEVINL float point_dist(const float* tab, unsigned key) {
+    constexpr int B = N == 8 ? 2 : 3, E = 1 << (2 * B);
+    float d = 0.f;
+#pragma unroll
+    for (int p = 0; p < N / 2; ++p) d = d + tab[(p * E + ((key >> (2 * B * p)) & (E - 1))) * QR_TPB + threadIdx.x];
+    return isnan(d) ? __int_as_float(0x7f800000) : d;
+}
+// the two smallest distances and the rank of point t in the order (distance, index)        (encode / histogram)
+template <int N> SG_DEVINL void scan_rank(const float* tab, const uint16_t* __restrict__ gk, int gs, int t, float& d1, float& d2, int& rank) {
+    const float inf = __int_as_float(0x7f800000);
+    const float dt = point_dist<N>(tab, gk[t]);
+    d1 = inf; d2 = inf; rank = 0;
+    for (int k = 0; k < gs; ++k) {
+        const float d = point_dist<N>(tab, __ldg(gk + k));
+        if (d < d1) { d2 = d1; d1 = d; } else if (d < d2) d2 = d;
+        rank += d < dt || (d == dt && k < t);
+    }
+}
+// the first TOPK points of that order                                                       (decode)
+template <int N> SG_DEVINL void scan_top(const float* tab, const uint16_t* __restrict__ gk, int gs, float& d1, float& d2, int* top) {
+    const float inf = __int_as_float(0x7f800000);
+    float td[TOPK];
+#pragma unroll
+    for (int j = 0; j < TOPK; ++j) { td[j] = inf; top[j] = j; }
+    for (int k = 0; k < gs; ++k) {
+        const float d = point_dist<N>(tab, __ldg(gk + k));
+        if (d < td[TOPK - 1]) {
+            td[TOPK - 1] = d; top[TOPK - 1] = k;
+#pragma unroll
+            for (int j = TOPK - 1; j > 0; --j)
+                if (td[j] < td[j - 1]) { const float a = td[j]; td[j] = td[j - 1]; td[j - 1] = a; const int b = top[j]; top[j] = top[j - 1]; top[j - 1] = b; }
+        }
+    }
+    d1 = td[0]; d2 = td[1];
+}
+
+// all symbols of one differing block of a grid type after its scale fields (qr.py:553-637).  fb: stored block (decode:
+// being rebuilt, fields already written), tv: its unpacked fields.
+template <int N, bool SGN>
+SG_DEVINL void grid_block(Coder& c, int T, int mv, uchar* fb, const uchar* pb, const int* tv, const uint16_t* __restrict__ gk,
+                          long long gw0, int st, const uchar* sbase, int cols, const float* im, float* tab) {
+    constexpr int B = N == 8 ? 2 : 3, ng = 8 / N;
+    const int gs = grid_size(T);
+    const bool par = parity_type(T), dec = c.mode == 2;
+    float sx2 = 0.f;
+    for (int i = 0; i < 256; ++i) { float xv, hv; seed_val(st, sbase, gw0 + i, xv, hv, cols); sx2 += xv * xv; }
+    const float sigma2 = (T == 16 || T == 17) ? sx2 * (1.0f / 256.f) : 2.f * sx2 * (1.0f / 256.f);
+    const long long col0 = cols > 0 ? gw0 % cols : 0;
+    for (int ui = 0; ui < 32; ++ui) {
+        const int u = dec ? ui : 31 - ui;
+        const int p4 = pos4(col0 + 8 * u, cols);
+        const int rank0 = mv >= 2 ? GRANK2 + 4 * p4 : GRID_RANK;
+        const int sign0 = mv >= 2 ? GSIGN2 + 16 * p4 : GRID_SIGN;
+        if (dec && T == 29) { if (c.get(GRID_SHIFT) ^ get_shift(pb, u)) put_shift(fb, u); }
+        float gu[8], gw[8], gs_, gdl;
+        int pn[8];
+        gscale(T, fb, tv, u, gs_, gdl);
+        {
+            float x[8], v[8];
+            for (int i = 0; i < 8; ++i) {
+                const long long gwi = gw0 + 8 * u + i;
+                float hv; seed_val(st, sbase, gwi, x[i], hv, cols);
+                float wi = sqrtf(sigma2 + x[i] * x[i]);
+                if (im) wi = wi * im[gwi % cols];
+                gw[i] = wi;
+                pn[i] = x[i] < 0.f;
+                v[i] = SGN ? fabsf(x[i]) : x[i];
+            }
+            if (SGN && par) {                  // an odd number of negatives: the least weighty one flips back
+                int cnt = 0;
+                for (int i = 0; i < 8; ++i) cnt += pn[i];
+                if (cnt & 1) {
+                    int imin = 0; float mn = gw[0] * x[0] * x[0];
+                    for (int i = 1; i < 8; ++i) { const float a = gw[i] * x[i] * x[i]; if (a < mn) { mn = a; imin = i; } }
+                    pn[imin] ^= 1; v[imin] = -v[imin];
+                }
+            }
+            for (int i = 0; i < 8; ++i) gu[i] = v[i] / gs_;
+        }
+        int tg[2] = {0, 0};
+        auto sign_ctx = [&](int j) {
+            const int lev = (gk[tg[j / N]] >> (B * (j % N))) & ((1 << B) - 1);
+            const float m4 = fabsf(gu[j]) * 4.f;
+            return sign0 + (lev == 0) * 8 + (m4 < 7.f ? (int)m4 : 7);
+        };
+        if (!dec) {
+            for (int gg = 0; gg < ng; ++gg) tg[gg] = get_gidx(T, fb, u * ng + gg);
+            if (SGN) for (int j = 7; j >= 0; --j) {
+                if (par && j == 7) continue;
+                c.put(sign_ctx(j), get_neg(T, fb, 8 * u + j) ^ pn[j]);
+            }
+            for (int gg = ng - 1; gg >= 0; --gg) {
+                pair_tables<N, SGN>(tab, gu + gg * N, gw + gg * N, gdl);
+                int rank; float d1, d2;
+                scan_rank<N>(tab, gk, gs, tg[gg], d1, d2, rank);
+                const int ctx = rank0 + gapctx(d1, d2);
+                if (rank >= TOPK) { c.put(FESC_HI, tg[gg] >> 8); c.put(FESC_LO, tg[gg] & 255); c.put(ctx, TOPK); }
+                else c.put(ctx, rank);
+            }
+            if (T == 29) c.put(GRID_SHIFT, get_shift(fb, u) ^ get_shift(pb, u));
+            if (c.ovf) return;
+        } else {
+            for (int gg = 0; gg < ng; ++gg) {
+                pair_tables<N, SGN>(tab, gu + gg * N, gw + gg * N, gdl);
+                int top[TOPK]; float d1, d2;
+                scan_top<N>(tab, gk, gs, d1, d2, top);
+                const int r = c.get(rank0 + gapctx(d1, d2));
+                int t;
+                if (r >= TOPK) { const int lo = c.get(FESC_LO), hi = c.get(FESC_HI); t = (lo | (hi << 8)) % gs; }
+                else {
+                    t = top[0];
+#pragma unroll
+                    for (int j = 1; j < TOPK; ++j) if (j == r) t = top[j];
+                }
+                put_gidx(T, fb, u * ng + gg, t);
+                tg[gg] = t;
+            }
+            if (SGN) for (int j = 0; j < 8; ++j) {
+                if (par && j == 7) continue;
+                if (c.get(sign_ctx(j)) ^ pn[j]) put_neg(T, fb, 8 * u + j);
+            }
+            if (c.rd.over) return;
+        }
+    }
+}
+SG_DEVINL void grid_code(Coder& c, int T, int mv, uchar* fb, const uchar* pb, const int* tv, const uint16_t* gk, long long gw0, int st,
+                         const uchar* sbase, int cols, const float* im, float* tab) {
+    switch (T) {
+        case 18: case 21: grid_block<4, true>(c, T, mv, fb, pb, tv, gk, gw0, st, sbase, cols, im, tab); return;
+        case 19: case 29: grid_block<8, false>(c, T, mv, fb, pb, tv, gk, gw0, st, sbase, cols, im, tab); return;
+        default: grid_block<8, true>(c, T, mv, fb, pb, tv, gk, gw0, st, sbase, cols, im, tab);
+    }
+}
+
+// ---- the three passes -------------------------------------------------------------------------------------------
+extern __shared__ float gtab[];          // grid types only: 64 (IQ3: 128) floats per thread
+
+struct Args {
+    int T, mv, nseg;
+    const uchar *F, *P, *ne, *seed;
+    const TM* tm; const SG* sg;
+    const uint16_t* gk; const float* imx;
+};
+
+// scalar-code types: the codes of one differing block, forwards (histogram, decode) or backwards (encode)
+SG_DEVINL void scalar_codes(Coder& c, int T, int mv, uchar* fb, const uchar* pb, const int* tv, const Setup& u, long long gw0) {
+    const long long col0 = u.m.cols > 0 ? gw0 % u.m.cols : 0;
+    const bool fwd = c.mode != 1, dec = c.mode == 2;
+    int tsub = -1; float ta = 0.f, tc = 0.f;
+    for (int i = 0; i < u.qk; ++i) {
+        const int w = fwd ? i : u.qk - 1 - i;
+        if (w / u.sublen != tsub) { tsub = w / u.sublen; wscale(T, tv, tsub, ta, tc); }
+        float xv, hv; seed_val(u.m.seed_type, u.sbase, gw0 + w, xv, hv, u.m.cols);
+        int r, sgn, ctx; predict_code(T, ta, tc, pb, w, xv, hv, u.hboff, r, sgn, ctx, mv, pos8(col0 + w, u.m.cols));
+        if (dec) {
+            int q = r + sgn * (int)(signed char)c.get(ctx);
+            if (T == 8) q = (int)(signed char)(q & 255);
+            put_code(T, fb, w, q);
+        } else c.put(ctx, (sgn * (get_code(T, fb, w) - r)) & 255);
+    }
+}
+
+__global__ void __launch_bounds__(QR_TPB) k_qr_hist(const Args a, unsigned* __restrict__ counts) {
     const int s = blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= nseg) return;
-    const Setup u = setup(T, seed, tm, sg, s);
-    unsigned flagc[4] = {0, 0, 0, 0};                 // [prev * 2 + eq]
+    if (s >= a.nseg) return;
+    const int T = a.T, mv = a.mv;
+    const Setup u = setup(T, a.seed, a.tm, a.sg, s);
+    const float* im = u.m.imx_off >= 0 ? a.imx + u.m.imx_off : nullptr;
+    Coder c; c.mode = 0; c.counts = counts; c.ovf = false;
+    unsigned flagc[4] = {0, 0, 0, 0};                 // [prev * 2 + eq], added once per lane
     int prev = 1;
-    auto add = [&](int tab, int sym) { atomicAdd(counts + tab * 256 + sym, 1u); };
     for (long long b = u.g.b0; b < u.g.b0 + u.g.nb; ++b) {
-        const int eq = !ne[b];
+        const int eq = !a.ne[b];
         ++flagc[prev * 2 + eq];
         prev = eq;
         if (eq) continue;
-        const uchar* fb = F + b * u.bs; const uchar* pb = P + b * u.bs;
+        const uchar* fb = a.F + b * u.bs; const uchar* pb = a.P + b * u.bs;
         int tv[MAXF], pv[MAXF];
         unpack_fields(T, fb, tv); unpack_fields(T, pb, pv);
         int any = 0;
         for (int k = 0; k < u.nf; ++k) {
-            const int dl = tv[k] - fpred(T, mv, pv, k, tv[0], u.nf > 1 ? tv[1] : 0);
-            field_symbols(fkind(T, k), any, tv[k], dl, add);
+            const int kd = fkind(T, k), dl = tv[k] - fpred(T, mv, pv, k, tv[0], u.nf > 1 ? tv[1] : 0);
+            if (kd < 2 && (dl < -127 || dl > 127)) { c.put(fctx(kd, any), 128); c.put(FESC_LO, tv[k] & 255); c.put(FESC_HI, tv[k] >> 8); }
+            else c.put(fctx(kd, any), dl & 255);
             any |= dl != 0;
         }
         const long long gw0 = (b - u.m.blk0) * u.qk;
-        const long long col0 = u.m.cols > 0 ? gw0 % u.m.cols : 0;
-        int tsub = -1; float ta = 0.f, tc = 0.f;
-        for (int w = 0; w < u.qk; ++w) {
-            if (w / u.sublen != tsub) { tsub = w / u.sublen; wscale(T, tv, tsub, ta, tc); }
-            float xv, hv; seed_val(u.m.seed_type, u.sbase, gw0 + w, xv, hv, u.m.cols);
-            int r, sgn, ctx; predict_code(T, ta, tc, pb, w, xv, hv, u.hboff, r, sgn, ctx, mv, pos8(col0 + w, u.m.cols));
-            add(ctx, (sgn * (get_code(T, fb, w) - r)) & 255);
-        }
+        if (is_grid(T)) grid_code(c, T, mv, const_cast<uchar*>(fb), pb, tv, a.gk, gw0, u.m.seed_type, u.sbase, u.m.cols, im, gtab);
+        else scalar_codes(c, T, mv, const_cast<uchar*>(fb), pb, tv, u, gw0);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) if (flagc[i]) atomicAdd(counts + (FLAG + (i >> 1)) * 256 + (i & 1), flagc[i]);
 }
 
-// ---- encode ----------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(64) k_qr_enc(int T, const uchar* __restrict__ F, const uchar* __restrict__ P,
-                                               const uchar* __restrict__ ne, const uchar* __restrict__ seed,
-                                               const TM* __restrict__ tm, const SG* __restrict__ sg, int nseg,
-                                               const RansSym* __restrict__ enc, uchar* __restrict__ out, size_t cap,
-                                               unsigned* __restrict__ out_len, int mv) {
+__global__ void __launch_bounds__(QR_TPB) k_qr_enc(const Args a, const RansSym* __restrict__ enc, uchar* __restrict__ out, size_t cap,
+                                                   unsigned* __restrict__ out_len) {
     const int s = blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= nseg) return;
-    const Setup u = setup(T, seed, tm, sg, s);
-    uchar* slot = out + (size_t)s * cap;
-    ByteWriterDown wr; wr.init(slot + cap);
-    unsigned x = RANS_L;
-    bool ovf = false;
-    auto put = [&](int tab, int sym) {
-        if (ovf) return;
-        rans_put<12>(x, wr, enc[tab * 256 + sym]);
-        if (wr.ptr() < slot + 64) ovf = true;
-    };
-    for (long long b = u.g.b0 + u.g.nb - 1; b >= u.g.b0; --b) {
-        const int eq = !ne[b];
-        const int prev = b > u.g.b0 ? !ne[b - 1] : 1;
-        if (eq) { put(FLAG + prev, 1); continue; }
-        const uchar* fb = F + b * u.bs; const uchar* pb = P + b * u.bs;
+    if (s >= a.nseg) return;
+    const int T = a.T, mv = a.mv;
+    const Setup u = setup(T, a.seed, a.tm, a.sg, s);
+    const float* im = u.m.imx_off >= 0 ? a.imx + u.m.imx_off : nullptr;
+    Coder c; c.mode = 1; c.enc = enc; c.slot = out + (size_t)s * cap; c.wr.init(c.slot + cap); c.x = RANS_L; c.ovf = false;
+    for (long long b = u.g.b0 + u.g.nb - 1; b >= u.g.b0 && !c.ovf; --b) {
+        const int eq = !a.ne[b];
+        const int prev = b > u.g.b0 ? !a.ne[b - 1] : 1;
+        if (eq) { c.put(FLAG + prev, 1); continue; }
+        const uchar* fb = a.F + b * u.bs; const uchar* pb = a.P + b * u.bs;
         int tv[MAXF], pv[MAXF];
         unpack_fields(T, fb, tv); unpack_fields(T, pb, pv);
         const long long gw0 = (b - u.m.blk0) * u.qk;
-        const long long col0 = u.m.cols > 0 ? gw0 % u.m.cols : 0;
-        int tsub = -1; float ta = 0.f, tc = 0.f;
-        for (int w = u.qk - 1; w >= 0; --w) {
-            if (w / u.sublen != tsub) { tsub = w / u.sublen; wscale(T, tv, tsub, ta, tc); }
-            float xv, hv; seed_val(u.m.seed_type, u.sbase, gw0 + w, xv, hv, u.m.cols);
-            int r, sgn, ctx; predict_code(T, ta, tc, pb, w, xv, hv, u.hboff, r, sgn, ctx, mv, pos8(col0 + w, u.m.cols));
-            put(ctx, (sgn * (get_code(T, fb, w) - r)) & 255);
-        }
-        {   // fields, last to first; `any` is what the decoder will have seen before field k
+        if (is_grid(T)) grid_code(c, T, mv, const_cast<uchar*>(fb), pb, tv, a.gk, gw0, u.m.seed_type, u.sbase, u.m.cols, im, gtab);
+        else scalar_codes(c, T, mv, const_cast<uchar*>(fb), pb, tv, u, gw0);
+        {   // fields, last to first; anyk = what the decoder will have seen before field k
             int dl[MAXF], anyk[MAXF], any = 0;
             for (int k = 0; k < u.nf; ++k) {
                 dl[k] = tv[k] - fpred(T, mv, pv, k, tv[0], u.nf > 1 ? tv[1] : 0);
@@ -116,35 +293,33 @@ __global__ void __launch_bounds__(64) k_qr_enc(int T, const uchar* __restrict__ 
             }
             for (int k = u.nf - 1; k >= 0; --k) {
                 const int kd = fkind(T, k);
-                if (kd < 2 && (dl[k] < -127 || dl[k] > 127)) { put(FESC_HI, tv[k] >> 8); put(FESC_LO, tv[k] & 255); put(fctx(kd, anyk[k]), 128); }
-                else put(fctx(kd, anyk[k]), dl[k] & 255);
+                if (kd < 2 && (dl[k] < -127 || dl[k] > 127)) { c.put(FESC_HI, tv[k] >> 8); c.put(FESC_LO, tv[k] & 255); c.put(fctx(kd, anyk[k]), 128); }
+                else c.put(fctx(kd, anyk[k]), dl[k] & 255);
             }
         }
-        put(FLAG + prev, 0);
-        if (ovf) break;
+        c.put(FLAG + prev, 0);
     }
-    if (ovf) { out_len[s] = 0xffffffffu; return; }
-    rans_flush(x, wr);
-    wr.flush(slot);
-    out_len[s] = (unsigned)(slot + cap - wr.ptr());
+    if (c.ovf) { out_len[s] = 0xffffffffu; return; }
+    rans_flush(c.x, c.wr);
+    c.wr.flush(c.slot);
+    out_len[s] = (unsigned)(c.slot + cap - c.wr.ptr());
 }
 
-// ---- decode ----------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(64) k_qr_dec(int T, const uchar* __restrict__ in, const unsigned long long* __restrict__ off,
-                                               const uchar* __restrict__ P, const uchar* __restrict__ seed,
-                                               const TM* __restrict__ tm, const SG* __restrict__ sg, int nseg,
-                                               const RansSym* __restrict__ enc, const uchar* __restrict__ lut,
-                                               uchar* __restrict__ F, int mv, int* __restrict__ status) {
+__global__ void __launch_bounds__(QR_TPB) k_qr_dec(const Args a, const uchar* __restrict__ in, const unsigned long long* __restrict__ off,
+                                                   const RansSym* __restrict__ enc, const uchar* __restrict__ lut, uchar* __restrict__ F,
+                                                   int* __restrict__ status) {
     const int s = blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= nseg) return;
-    const Setup u = setup(T, seed, tm, sg, s);
-    ByteReaderUp rd; rd.init(in + off[s], in + off[s + 1]);
-    unsigned x = rans_init(rd);
-    auto get = [&](int tab) -> int { return (int)rans_get<12>(x, rd, lut + ((size_t)tab << 12), enc + tab * 256); };
+    if (s >= a.nseg) return;
+    const int T = a.T, mv = a.mv;
+    const Setup u = setup(T, a.seed, a.tm, a.sg, s);
+    const float* im = u.m.imx_off >= 0 ? a.imx + u.m.imx_off : nullptr;
+    Coder c; c.mode = 2; c.enc = enc; c.lut = lut; c.ovf = false;
+    c.rd.init(in + off[s], in + off[s + 1]);
+    c.x = rans_init(c.rd);
     int prev = 1;
     for (long long b = u.g.b0; b < u.g.b0 + u.g.nb; ++b) {
-        uchar* fb = F + b * u.bs; const uchar* pb = P + b * u.bs;
-        const int eq = get(FLAG + prev);
+        uchar* fb = F + b * u.bs; const uchar* pb = a.P + b * u.bs;
+        const int eq = c.get(FLAG + prev);
         prev = eq;
         if (eq) { for (int i = 0; i < u.bs; ++i) fb[i] = pb[i]; continue; }
         for (int i = 0; i < u.bs; ++i) fb[i] = 0;
@@ -154,9 +329,9 @@ __global__ void __launch_bounds__(64) k_qr_dec(int T, const uchar* __restrict__ 
         for (int k = 0; k < u.nf; ++k) {
             const int kd = fkind(T, k);
             const int pr = fpred(T, mv, pv, k, k > 0 ? tv[0] : 0, k > 1 ? tv[1] : 0);
-            const int sym = get(fctx(kd, any));
+            const int sym = c.get(fctx(kd, any));
             int t;
-            if (kd < 2 && sym == 128) { const int lo = get(FESC_LO), hi = get(FESC_HI); t = lo | (hi << 8); }
+            if (kd < 2 && sym == 128) { const int lo = c.get(FESC_LO), hi = c.get(FESC_HI); t = lo | (hi << 8); }
             else {
                 t = pr + (int)(signed char)sym;
                 if (kd < 2) t &= 0xffff;
@@ -166,20 +341,11 @@ __global__ void __launch_bounds__(64) k_qr_dec(int T, const uchar* __restrict__ 
         }
         pack_fields(T, fb, tv);
         const long long gw0 = (b - u.m.blk0) * u.qk;
-        const long long col0 = u.m.cols > 0 ? gw0 % u.m.cols : 0;
-        int tsub = -1; float ta = 0.f, tc = 0.f;
-        for (int w = 0; w < u.qk; ++w) {
-            if (w / u.sublen != tsub) { tsub = w / u.sublen; wscale(T, tv, tsub, ta, tc); }
-            float xv, hv; seed_val(u.m.seed_type, u.sbase, gw0 + w, xv, hv, u.m.cols);
-            int r, sgn, ctx; predict_code(T, ta, tc, pb, w, xv, hv, u.hboff, r, sgn, ctx, mv, pos8(col0 + w, u.m.cols));
-            const int v = get(ctx);
-            int q = r + sgn * (int)(signed char)v;
-            if (T == 8) q = (int)(signed char)(q & 255);
-            put_code(T, fb, w, q);
-        }
-        if (rd.over) break;
+        if (is_grid(T)) grid_code(c, T, mv, fb, pb, tv, a.gk, gw0, u.m.seed_type, u.sbase, u.m.cols, im, gtab);
+        else scalar_codes(c, T, mv, fb, pb, tv, u, gw0);
+        if (c.rd.over) break;
     }
-    if (rd.over || x != RANS_L || rd.p != rd.end) atomicOr(status, SG_ST_CORRUPT);
+    if (c.rd.over || c.x != RANS_L || c.rd.p != c.rd.end) atomicOr(status, SG_ST_CORRUPT);
 }
 
 }  // namespace qr
@@ -188,50 +354,72 @@ __global__ void __launch_bounds__(64) k_qr_dec(int T, const uchar* __restrict__ 
 using namespace sg;
 using namespace sg::qr;
 
-static int qr_args(int T, const void* P, const void* seed, const void* tm, const void* sgp, int nseg, int mv) {
+static size_t grid_smem(int T) {
+    switch (T) { case 18: case 21: return (size_t)QR_TPB * 4 * 128; case 16: case 17: case 19: case 22: case 29: return (size_t)QR_TPB * 4 * 64; }
+    return 0;
+}
+static int grid_table_index(int T) {
+    switch (T) { case 16: return 0; case 17: return 1; case 19: case 29: return 2; case 22: return 3; case 18: return 4; case 21: return 5; }
+    return -1;
+}
+namespace sg { const uint16_t* device_grid_keys(int device, int which); }      // tables.cu
+
+static int qr_args(int device, Args& a, int T, const void* F, const void* P, const void* ne, const void* seed, const void* tm,
+                   const void* sgp, int nseg, const float* imx, int mv) {
     if (!P || !seed || !tm || !sgp || nseg < 0 || (mv != 1 && mv != 2)) return SG_ERR_ARG;
-    switch (T) { case 2: case 3: case 6: case 7: case 8: case 10: case 11: case 12: case 13: case 14: case 20: case 23: case 42: return SG_OK; }
-    return SG_ERR_TYPE;      // the grid types (16 17 18 19 21 22 29) are coded by sg_qr_grid_* once available
+    int qk, bs;
+    if (sg_type_info(T, &qk, &bs) != SG_OK) return SG_ERR_TYPE;
+    a.T = T; a.mv = mv; a.nseg = nseg;
+    a.F = (const uchar*)F; a.P = (const uchar*)P; a.ne = (const uchar*)ne; a.seed = (const uchar*)seed;
+    a.tm = (const TM*)tm; a.sg = (const SG*)sgp; a.imx = imx; a.gk = nullptr;
+    const int gi = grid_table_index(T);
+    if (gi >= 0) {
+        a.gk = device_grid_keys(device, gi);
+        if (!a.gk) return SG_ERR_TABLES;
+    }
+    return SG_OK;
 }
 
 extern "C" int sg_qr_hist(int device, void* stream, int T, const unsigned char* F, const unsigned char* P, const unsigned char* ne,
-                          const unsigned char* seed, const void* tm, const void* sgp, int nseg, unsigned* counts, int mv) {
-    int rc = qr_args(T, P, seed, tm, sgp, nseg, mv);
+                          const unsigned char* seed, const void* tm, const void* sgp, int nseg, const float* imx, unsigned* counts, int mv) {
+    Args a;
+    int rc = qr_args(device, a, T, F, P, ne, seed, tm, sgp, nseg, imx, mv);
     if (rc != SG_OK) return rc;
     if (!F || !ne || !counts) return SG_ERR_ARG;
     if (nseg == 0) return SG_OK;
     rc = use_device(device);
     if (rc != SG_OK) return rc;
-    k_qr_hist<<<(nseg + 63) / 64, 64, 0, (cudaStream_t)stream>>>(T, F, P, ne, seed, (const TM*)tm, (const SG*)sgp, nseg, counts, mv);
+    k_qr_hist<<<(nseg + QR_TPB - 1) / QR_TPB, QR_TPB, grid_smem(T), (cudaStream_t)stream>>>(a, counts);
     return cuda_ok(cudaGetLastError());
 }
 
 extern "C" int sg_qr_encode(int device, void* stream, int T, const unsigned char* F, const unsigned char* P, const unsigned char* ne,
-                            const unsigned char* seed, const void* tm, const void* sgp, int nseg, const void* enc_tab,
+                            const unsigned char* seed, const void* tm, const void* sgp, int nseg, const float* imx, const void* enc_tab,
                             unsigned char* slots, size_t cap, unsigned* out_len, int mv) {
-    int rc = qr_args(T, P, seed, tm, sgp, nseg, mv);
+    Args a;
+    int rc = qr_args(device, a, T, F, P, ne, seed, tm, sgp, nseg, imx, mv);
     if (rc != SG_OK) return rc;
     if (!F || !ne || !enc_tab || !slots || !out_len) return SG_ERR_ARG;
     if (cap < 128 || cap % 16 || (uintptr_t)slots % 16) return SG_ERR_ALIGN;
     if (nseg == 0) return SG_OK;
     rc = use_device(device);
     if (rc != SG_OK) return rc;
-    k_qr_enc<<<(nseg + 63) / 64, 64, 0, (cudaStream_t)stream>>>(T, F, P, ne, seed, (const TM*)tm, (const SG*)sgp, nseg,
-                                                                (const RansSym*)enc_tab, slots, cap, out_len, mv);
+    k_qr_enc<<<(nseg + QR_TPB - 1) / QR_TPB, QR_TPB, grid_smem(T), (cudaStream_t)stream>>>(a, (const RansSym*)enc_tab, slots, cap, out_len);
     return cuda_ok(cudaGetLastError());
 }
 
 extern "C" int sg_qr_decode(int device, void* stream, int T, const unsigned char* in, const unsigned long long* off,
-                            const unsigned char* P, const unsigned char* seed, const void* tm, const void* sgp, int nseg,
+                            const unsigned char* P, const unsigned char* seed, const void* tm, const void* sgp, int nseg, const float* imx,
                             const void* enc_tab, const unsigned char* lut, unsigned char* F, int mv) {
-    int rc = qr_args(T, P, seed, tm, sgp, nseg, mv);
+    Args a;
+    int rc = qr_args(device, a, T, nullptr, P, nullptr, seed, tm, sgp, nseg, imx, mv);
     if (rc != SG_OK) return rc;
     if (!in || !off || !enc_tab || !lut || !F) return SG_ERR_ARG;
     if ((uintptr_t)in % 16) return SG_ERR_ALIGN;
     if (nseg == 0) return SG_OK;
     rc = use_device(device);
     if (rc != SG_OK) return rc;
-    k_qr_dec<<<(nseg + 63) / 64, 64, 0, (cudaStream_t)stream>>>(T, in, off, P, seed, (const TM*)tm, (const SG*)sgp, nseg,
-                                                                (const RansSym*)enc_tab, lut, F, mv, status_word(device));
+    k_qr_dec<<<(nseg + QR_TPB - 1) / QR_TPB, QR_TPB, grid_smem(T), (cudaStream_t)stream>>>(a, in, off, (const RansSym*)enc_tab, lut, F,
+                                                                                       status_word(device));
     return cuda_ok(cudaGetLastError());
 }

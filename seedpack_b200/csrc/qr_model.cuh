@@ -303,5 +303,98 @@ SG_DEVINL void predict_code(int T, float a, float c, const uchar* pblk, int w, f
     if (mv >= 2 && hu == 0.f && hboff != HBOFF_COL) ctx = CODE2 + p8 * 16 + min(15, (int)__fmul_rn(fabsf(fr), 32.f));
 }
 
+// ==== grid (IQ) types ===========================================================================================
+// A unit = 8 consecutive weights: one lattice point (IQ3: two points of 4), one sign group, one scale.
+SG_DEVINL int grid_size(int T) {
+    switch (T) { case 16: case 18: return 256; case 17: case 21: return 512; case 22: return 1024; }
+    return 2048;
+}
+SG_DEVINL bool parity_type(int T) { return T == 16 || T == 17 || T == 18; }      // 7 stored sign bits + parity
+
+// where the index of lattice group g is kept: 8 low bits in a byte, the rest (1-3 bits) elsewhere
+struct GidxLoc { int lo_byte, hi_byte, hi_shift, hi_bits; };
+SG_DEVINL GidxLoc gidx_loc(int T, int g) {
+    GidxLoc L = {2 + g, 0, 0, 0};
+    switch (T) {
+        case 16: L.lo_byte = 2 + 8 * (g >> 2) + (g & 3); break;
+        case 17: L.lo_byte = 2 + 2 * g; L.hi_byte = 3 + 2 * g; L.hi_bits = 1; break;
+        case 22: L.hi_byte = 66 + (g >> 2); L.hi_shift = 2 * (g & 3); L.hi_bits = 2; break;
+        case 21: L.hi_byte = 66 + (g >> 3); L.hi_shift = g & 7; L.hi_bits = 1; break;
+        case 19: L.hi_byte = -1; break;                                   // 3 bits inside the 16-bit qh word, below
+        case 29: L.lo_byte = g; L.hi_byte = 32 + (g >> 1); L.hi_shift = 4 * (g & 1); L.hi_bits = 3; break;
+    }
+    return L;
+}
+SG_DEVINL int get_gidx(int T, const uchar* b, int g) {
+    const GidxLoc L = gidx_loc(T, g);
+    if (T == 19) return b[L.lo_byte] | (((u16(b + 34 + 2 * (g >> 2)) >> (3 * (g & 3))) & 7) << 8);
+    int k = b[L.lo_byte];
+    if (L.hi_bits) k |= ((b[L.hi_byte] >> L.hi_shift) & ((1 << L.hi_bits) - 1)) << 8;
+    return k;
+}
+SG_DEVINL void put_gidx(int T, uchar* b, int g, int k) {
+    const GidxLoc L = gidx_loc(T, g);
+    if (T == 16 || T == 18) { b[L.lo_byte] |= (uchar)k; return; }
+    b[L.lo_byte] |= (uchar)(k & 255);
+    if (T == 19) {
+        const int v = ((k >> 8) & 7) << (3 * (g & 3));
+        b[34 + 2 * (g >> 2)] |= (uchar)(v & 255); b[35 + 2 * (g >> 2)] |= (uchar)(v >> 8);
+        return;
+    }
+    b[L.hi_byte] |= (uchar)(((k >> 8) & ((1 << L.hi_bits) - 1)) << L.hi_shift);
+}
+// bit position (from the start of the block) of the stored sign of weight w; -1: the type stores no signs
+SG_DEVINL int sign_bit_pos(int T, int w) {
+    const int j = w & 7;
+    switch (T) {
+        case 16: return 8 * (2 + 8 * (w >> 5) + 4) + 7 * ((w >> 3) & 3) + j;
+        case 17: return 8 * (2 + 2 * (w >> 3)) + 9 + j;
+        case 18: return 8 * (66 + 4 * (w >> 5)) + 7 * ((w >> 3) & 3) + j;
+        case 22: return 8 * (34 + (w >> 3)) + j;
+        case 21: return 8 * (74 + (w >> 3)) + j;
+    }
+    return -1;
+}
+// 1 = weight w is stored negative.  Parity types keep 7 bits per group of 8; the eighth makes the count even.
+SG_DEVINL int get_neg(int T, const uchar* b, int w) {
+    if (sign_bit_pos(T, w) < 0) return 0;
+    if (!parity_type(T)) { const int p = sign_bit_pos(T, w); return (b[p >> 3] >> (p & 7)) & 1; }
+    const int p0 = sign_bit_pos(T, w & ~7);
+    int s7 = 0;
+    for (int i = 0; i < 7; ++i) s7 |= ((b[(p0 + i) >> 3] >> ((p0 + i) & 7)) & 1) << i;
+    const int j = w & 7;
+    return j < 7 ? (s7 >> j) & 1 : __popc(s7) & 1;
+}
+SG_DEVINL void put_neg(int T, uchar* b, int w) {         // parity types: only for w % 8 < 7
+    const int p = sign_bit_pos(T, w);
+    if (p >= 0) b[p >> 3] |= (uchar)(1 << (p & 7));
+}
+// IQ1_M: shift bit of unit u (bit 3 or 7 of the qh byte of its pair of units)
+SG_DEVINL int get_shift(const uchar* b, int u) { return (b[32 + (u >> 1)] >> ((u & 1) ? 7 : 3)) & 1; }
+SG_DEVINL void put_shift(uchar* b, int u) { b[32 + (u >> 1)] |= (u & 1) ? 0x80 : 0x08; }
+
+// scale of unit u and the IQ1 shift: value = s (2 l + 1), IQ1: s (l - 1 + dl).  The quantisers' fudge factors on
+// the stored fp16 are undone by multiplying with the rounded reciprocal (what the reference's GPU build does
+// for a division by a literal, seedpack/cpukernels.py:254-264).  v = the block's unpacked fields.
+SG_DEVINL void gscale(int T, const uchar* b, const int* v, int u, float& s, float& dl) {
+    float d = h2fv((unsigned)v[0]);
+    int ls;
+    dl = 0.f;
+    switch (T) {
+        case 16: case 18: ls = v[1 + (u >> 2)]; break;
+        case 17: ls = v[1 + (u >> 1)]; break;
+        case 22: d = d * (1.0f / 0.9875f); ls = v[1 + (u >> 1)]; break;
+        case 21: d = d * (1.0f / 1.033f); ls = v[1 + (u >> 2)]; break;
+        case 19: d = d * (1.0f / 1.125f); ls = v[1 + (u >> 2)] & 7; dl = (v[1 + (u >> 2)] & 8) ? -0.125f : 0.125f; break;
+        case 29: d = d * (1.0f / 1.1125f); ls = v[1 + (u >> 1)]; dl = get_shift(b, u) ? -0.125f : 0.125f; break;
+        default: d = 0.f; ls = 0;
+    }
+    s = d * (float)(2 * ls + 1);
+}
+SG_DEVINL int gapctx(float d1, float d2) {
+    const float g = (d2 - d1) / (d1 + 1e-30f);
+    return (g >= 0.05f) + (g >= 0.2f) + (g >= 0.6f);
+}
+
 }  // namespace qr
 }  // namespace sg

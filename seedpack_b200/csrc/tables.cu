@@ -99,6 +99,7 @@ static std::mutex g_mu;
 static HostTable* g_host = nullptr;          // six tables, built once per process
 static constexpr int MAX_DEV = 64;
 static IqTables* g_dev[MAX_DEV] = {nullptr};
+static const uint16_t* g_keys[MAX_DEV][6] = {{nullptr}};     // per lattice: one packed code tuple per point
 
 static const HostTable* host_tables() {
     if (!g_host) {
@@ -116,6 +117,14 @@ const IqTables* device_tables(int device) {
 }
 
 bool tables_ready(int device) { return device_tables(device) != nullptr; }
+
+// packed level tuple of every lattice point (2 bits x 8 or 3 bits x 4): what the QR coder calls grid keys
+// (seedpack/qr.py:936-949)
+const uint16_t* device_grid_keys(int device, int which) {
+    if (device < 0 || device >= MAX_DEV || which < 0 || which >= 6) return nullptr;
+    std::lock_guard<std::mutex> lk(g_mu);
+    return g_keys[device][which];
+}
 
 }  // namespace sg
 
@@ -141,10 +150,11 @@ extern "C" int sg_tables_install(int device, void* stream) {
     const HostTable* h = host_tables();
     cudaStream_t st = (cudaStream_t)stream;
     // one allocation holds every table, each part 256-byte aligned
-    size_t off = 0, offs[6][3];
+    size_t off = 0, offs[6][4];
     for (int i = 0; i < 6; ++i) {
-        const size_t sz[3] = {h[i].dim == 8 ? h[i].grid64.size() * 8 : h[i].grid32.size() * 4, h[i].map.size() * 4, h[i].nb.size() * 2};
-        for (int k = 0; k < 3; ++k) { offs[i][k] = off; off += (sz[k] + 255) / 256 * 256; }
+        const size_t sz[4] = {h[i].dim == 8 ? h[i].grid64.size() * 8 : h[i].grid32.size() * 4, h[i].map.size() * 4, h[i].nb.size() * 2,
+                              (size_t)SPEC[i].n * 2};
+        for (int k = 0; k < 4; ++k) { offs[i][k] = off; off += (sz[k] + 255) / 256 * 256; }
     }
     uint8_t* base = nullptr;
     rc = cuda_ok(cudaMalloc(&base, off));
@@ -155,12 +165,14 @@ extern "C" int sg_tables_install(int device, void* stream) {
         const size_t sz[3] = {h[i].dim == 8 ? h[i].grid64.size() * 8 : h[i].grid32.size() * 4, h[i].map.size() * 4, h[i].nb.size() * 2};
         for (int k = 0; k < 3 && rc == SG_OK; ++k)
             rc = cuda_ok(cudaMemcpyAsync(base + offs[i][k], src[k], sz[k], cudaMemcpyHostToDevice, st));
+        if (rc == SG_OK) rc = cuda_ok(cudaMemcpyAsync(base + offs[i][3], SPEC[i].packed, (size_t)SPEC[i].n * 2, cudaMemcpyHostToDevice, st));
+        g_keys[device][i] = (const uint16_t*)(base + offs[i][3]);
         t->t[i].grid = base + offs[i][0];
         t->t[i].map = (const int*)(base + offs[i][1]);
         t->t[i].neighbours = (const uint16_t*)(base + offs[i][2]);
     }
     if (rc == SG_OK) rc = cuda_ok(cudaStreamSynchronize(st));
-    if (rc != SG_OK) { cudaFree(base); delete t; return rc; }
+    if (rc != SG_OK) { cudaFree(base); delete t; for (int i = 0; i < 6; ++i) g_keys[device][i] = nullptr; return rc; }
     g_dev[device] = t;
     return SG_OK;
 }

@@ -121,6 +121,16 @@ class QRCodec:
         _lib.check(self.lib.sg_status_fetch(self.device.index, self._stream(), ctypes.byref(bits)), "sg_status_fetch")
         return bits.value
 
+    def _imx(self, T, imx_dev):
+        if T in GRID_TYPES:
+            from . import tables
+            tables.install(self.device.index)
+        if imx_dev is None:
+            return None
+        if isinstance(imx_dev, torch.Tensor):
+            return imx_dev.to(self.device, torch.float32).contiguous().reshape(-1)
+        return torch.from_numpy(np.ascontiguousarray(imx_dev, np.float32).reshape(-1)).to(self.device)
+
     def _records(self, T, nbs, seed_offs, seed_types, cols, imx_offs):
         tm, sg, nb = _layout(T, nbs)
         tm["seed_off"], tm["seed_type"], tm["cols"], tm["imx_off"] = seed_offs, seed_types, cols, imx_offs
@@ -140,9 +150,10 @@ class QRCodec:
     def encode(self, T, items, seed_dev, imx_dev=None, mv=None):
         """items: [(file tensor bytes, predicted bytes, seed byte offset, seed type[, weights per row, imatrix
         offset])] of one batch, all of ggml type T -> bytes of the coded batch (seedpack/qr.py:1007-1061)"""
-        if T not in SELF_TYPES:
-            raise NotImplementedError(f"QR coding of ggml type {T} (grid types) is not available yet")
+        if T not in QR_TYPES:
+            raise ValueError(f"ggml type {T} has no QR model")
         mv = MODEL if mv is None else mv
+        imx = self._imx(T, imx_dev)
         bs, d, st = BS[T], self.device.index, self._stream()
         nbs = [len(it[0]) // bs for it in items]
         tm_d, sg_d, nseg, nb = self._records(T, nbs, [it[2] for it in items], [it[3] for it in items],
@@ -155,15 +166,15 @@ class QRCodec:
         ndiff = torch.zeros(1, dtype=torch.int64, device=self.device)
         _lib.check(self.lib.sg_residual_blocks(d, st, _p(F), _p(P), bs, nb, _p(ne), _p(ndiff)), "sg_residual_blocks")
         counts = torch.zeros(NTAB2 * 256, dtype=torch.int32, device=self.device)
-        _lib.check(self.lib.sg_qr_hist(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(counts), mv), "sg_qr_hist")
+        _lib.check(self.lib.sg_qr_hist(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(counts), mv), "sg_qr_hist")
         freq, used = normalize(counts.cpu().numpy().astype(np.uint32).reshape(NTAB2, 256))
         enc, _ = self._tables(freq, used, lut=False)
-        cap = seg_blocks(T) * (QK[T] + NSB_MAX) * 2 + 1024
+        cap = seg_blocks(T) * (3 * BS[T] if T in GRID_TYPES else (QK[T] + NSB_MAX) * 2) + 1024
         cap = (cap + 15) // 16 * 16
         for _ in range(3):
             slots = torch.empty(max(nseg, 1) * cap, dtype=torch.uint8, device=self.device)
             lens = torch.zeros(max(nseg, 1), dtype=torch.int32, device=self.device)
-            _lib.check(self.lib.sg_qr_encode(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(enc), _p(slots),
+            _lib.check(self.lib.sg_qr_encode(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(enc), _p(slots),
                                              cap, _p(lens), mv), "sg_qr_encode")
             off = torch.empty(nseg + 1, dtype=torch.int64, device=self.device)
             _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, None, 0, _p(off)), "sg_scan_gather")
@@ -185,8 +196,9 @@ class QRCodec:
     def decode(self, T, buf, items, seed_dev, imx_dev=None):
         """items: [(predicted bytes, seed byte offset, seed type[, weights per row, imatrix offset])] -> device uint8
         tensor of the batch's tensors back to back (seedpack/qr.py:1064-1090)"""
-        if T not in SELF_TYPES:
-            raise NotImplementedError(f"QR coding of ggml type {T} (grid types) is not available yet")
+        if T not in QR_TYPES:
+            raise ValueError(f"ggml type {T} has no QR model")
+        imx = self._imx(T, imx_dev)
         ch = unpack(buf)
         mv = ch["v"][0] if "v" in ch else 1
         bs, d, st = BS[T], self.device.index, self._stream()
@@ -207,7 +219,7 @@ class QRCodec:
         sd[:len(s)] = torch.from_numpy(s.copy()).to(self.device)
         F = torch.empty(nb * bs, dtype=torch.uint8, device=self.device)
         off_d = torch.from_numpy(offs.view(np.int64)).to(self.device)
-        _lib.check(self.lib.sg_qr_decode(d, st, T, _p(sd), _p(off_d), _p(P), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(enc), _p(lut), _p(F),
+        _lib.check(self.lib.sg_qr_decode(d, st, T, _p(sd), _p(off_d), _p(P), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(enc), _p(lut), _p(F),
                                          mv), "sg_qr_decode")
         if self._status() & 4:
             raise ValueError("QR batch: corrupt stream")

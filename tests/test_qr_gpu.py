@@ -75,3 +75,46 @@ def test_corrupt_batch_is_rejected():
     except ValueError:
         return
     assert not np.array_equal(out.cpu().numpy(), G["F_8"])
+
+
+# ---- lattice (IQ) types ---------------------------------------------------------------------------------------------
+GG = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "qr_grid_golden.npz"))
+GTYPES = [int(t) for t in GG["types"]]
+GSHAPES = [tuple(int(v) for v in s) for s in GG["shapes"]]
+
+
+def _grid_items(T):
+    from seedpack_b200.qr import BS
+    F, P, bs = GG[f"F_{T}"], GG[f"P_{T}"], BS[T]
+    enc, dec, o = [], [], 0
+    for k, (nr, npr) in enumerate(GSHAPES):
+        n = nr * npr // 256 * bs
+        so, io = int(GG["seed_offs"][k]), int(GG["imx_offs"][k])
+        enc.append((F[o:o + n], P[o:o + n], so, 30, npr, io))
+        dec.append((P[o:o + n], so, 30, npr, io))
+        o += n
+    return enc, dec
+
+
+@pytest.mark.parametrize("mv", [1, 2])
+@pytest.mark.parametrize("T", GTYPES)
+def test_grid_encode_is_byte_identical_to_reference(T, mv):
+    from seedpack_b200.qr import QRCodec, unpack
+    c = QRCodec()
+    enc, _ = _grid_items(T)
+    got = c.encode(T, enc, GG["seed_bits"].view(np.uint8), GG["imx"], mv=mv)
+    want = GG[f"B_{T}_{mv}"].tobytes()
+    if got != want:
+        a, b = unpack(got), unpack(want)
+        diff = {k: (len(a.get(k, b"")), len(b.get(k, b"")), bytes(a.get(k, b"")) == bytes(b.get(k, b""))) for k in set(a) | set(b)}
+        raise AssertionError(f"type {T} model {mv}: parts (ours, reference, equal) = {diff}")
+
+
+@pytest.mark.parametrize("mv", [1, 2])
+@pytest.mark.parametrize("T", GTYPES)
+def test_grid_decode_of_reference_batch_restores_file(T, mv):
+    from seedpack_b200.qr import QRCodec
+    c = QRCodec()
+    _, dec = _grid_items(T)
+    out = c.decode(T, GG[f"B_{T}_{mv}"].tobytes(), dec, GG["seed_bits"].view(np.uint8), GG["imx"])
+    assert np.array_equal(out.cpu().numpy(), GG[f"F_{T}"])
