@@ -198,6 +198,41 @@ SG_API int sg_qr_decode(int device, void *stream, int T, const unsigned char *in
                         const unsigned char *P, const unsigned char *seed, const void *tm, const void *sg, int nseg,
                         const float *imx, const void *enc_tab, const unsigned char *lut, unsigned char *F, int mv);
 
+/* ---- R2: BF16 base-model codec and its order-fixed statistics ------------------------------------------------
+ * Replaces v2_hist / v2_enc / v2_dec / row_hash (seedpack/bf16v2.py:63-155) and the statistics of BF16v2._stats
+ * (seedpack/bf16v2.py:225-244) built on detmath (seedpack/detmath.py:67-106).  15 probability bits, segments of 16384
+ * weights, symbols per weight in decode order: exponent, mantissa, sign.  Records keep the reference's layouts:
+ *   TB { int64 doff; int32 rowlen, rowbase, colbase, tab, rmap, pad }   one per tensor of the launch (bf16v2.py:158)
+ *   SG { int32 t, n; int64 i0 }                                         one per segment                (bf16v2.py:159)
+ * dev = buffer holding the tensors (TB.doff = byte offset), rfi / cfi / scl = side information (int16 per row, int16 and
+ * int8 per column), rowmap = compact-to-original row numbers of tensors with duplicate rows removed (TB.rmap >= 0).
+ * Tables are addressed by raw id (role * 656 + context): counts has nroles * 656 * 256 entries; enc_tab / lut come
+ * from sg_rans_tables(..., pb = 15).  sg_r2_decode takes the first and one-past-last stream byte of every segment.
+ * sg_r2_stats writes rfi[nrows], cfi[rowlen], scl[rowlen] of one tensor; scratch from sg_r2_stats_scratch_bytes. */
+SG_API int sg_r2_hist(int device, void *stream, const unsigned char *dev, const void *tb, const void *sg, int nseg,
+                      const short *rfi, const short *cfi, const signed char *scl, const int *rowmap, unsigned *counts);
+SG_API int sg_r2_encode(int device, void *stream, const unsigned char *dev, const void *tb, const void *sg, int nseg,
+                        const short *rfi, const short *cfi, const signed char *scl, const int *rowmap,
+                        const void *enc_tab, unsigned char *slots, size_t cap, unsigned *out_len);
+SG_API int sg_r2_decode(int device, void *stream, const unsigned char *in, const unsigned long long *in_off,
+                        const unsigned long long *in_end, unsigned char *dev, const void *tb, const void *sg, int nseg,
+                        const short *rfi, const short *cfi, const signed char *scl, const int *rowmap,
+                        const void *enc_tab, const unsigned char *lut);
+/* 64-bit fingerprint of every row of a (nrows, rowlen) uint16 matrix (row_hash, bf16v2.py:148-155) */
+SG_API int sg_row_hash(int device, void *stream, const void *w, int nrows, int rowlen, unsigned long long *h);
+/* w[pairs[2p]] = w[pairs[2p + 1]] for rows of rowlen uint16: duplicate rows restored after decoding (bf16v2.py:475-480) */
+SG_API int sg_copy_rows(int device, void *stream, void *w, int rowlen, const long long *pairs, int npairs);
+SG_API size_t sg_r2_stats_scratch_bytes(int nrows, int rowlen);
+SG_API int sg_r2_stats(int device, void *stream, const void *w, int nrows, int rowlen, short *rfi, short *cfi,
+                       signed char *scl, void *scratch, size_t scratch_bytes);
+/* detmath (seedpack/detmath.py:67-106, 178-215): float64 log2 / exp2 from IEEE basic operations; sums (of squares)
+ * along rows / down columns of a float32 matrix in index order; mask (optional) leaves rows out of the column sums */
+SG_API int sg_dm_log2(int device, void *stream, const double *x, long long n, double *y);
+SG_API int sg_dm_exp2(int device, void *stream, const double *x, long long n, double *y);
+SG_API int sg_dm_rows(int device, void *stream, const float *x, long long nr, long long nc, int square, double *out);
+SG_API int sg_dm_cols(int device, void *stream, const float *x, long long nr, long long nc, int square,
+                      const unsigned char *mask, double *out);
+
 /* Allocation-free variant for hosts that cannot tolerate (or cannot supply memory for) a device allocation while
  * they run - a packer that has split the measured free device memory into fixed windows, or a pipeline whose
  * other streams must not be stalled by cudaMalloc's device-wide synchronisation.  It has no counterpart in the

@@ -50,6 +50,17 @@ SIGNATURES = {
     "sg_qr_hist": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I]),
     "sg_qr_encode": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _Z, _P, _I]),
     "sg_qr_decode": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I]),
+    "sg_r2_hist": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P]),
+    "sg_r2_encode": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _Z, _P]),
+    "sg_r2_decode": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P]),
+    "sg_row_hash": (_I, [_I, _P, _P, _I, _I, _P]),
+    "sg_copy_rows": (_I, [_I, _P, _P, _I, _P, _I]),
+    "sg_r2_stats_scratch_bytes": (_Z, [_I, _I]),
+    "sg_r2_stats": (_I, [_I, _P, _P, _I, _I, _P, _P, _P, _P, _Z]),
+    "sg_dm_log2": (_I, [_I, _P, _P, _L, _P]),
+    "sg_dm_exp2": (_I, [_I, _P, _P, _L, _P]),
+    "sg_dm_rows": (_I, [_I, _P, _P, _L, _L, _I, _P]),
+    "sg_dm_cols": (_I, [_I, _P, _P, _L, _L, _I, _P, _P]),
     "sg_quantize_legacy_imx_static": (_I, [_I, _P, _I, _P, _I, _P, _P, ctypes.POINTER(sg_tensor), _I]),
 }
 

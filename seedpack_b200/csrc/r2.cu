@@ -1,0 +1,358 @@
+// R2: the BF16 base-model codec (context-modelled rANS over exponent, mantissa and sign of every weight) and the
+// order-fixed float64 statistics that define its contexts.
+//
+// Replaces v2_hist / v2_enc / v2_dec / row_hash (seedpack/bf16v2.py:63-155) and the statistics pass `_stats`
+// (seedpack/bf16v2.py:225-244) with its detmath kernels (seedpack/detmath.py:67-106).  Format: 15 probability bits,
+// segments of 16384 weights, three symbols per weight in decode order exponent, mantissa, sign; contexts
+//   exponent: clamp(rfi[row] + cfi[col] + 256, 0, 511)          (predicted log2 sigma in 1/8 octave)
+//   mantissa: 512 + clamp(8 * exponent - pred - 952, 0, 127)
+//   sign:     640 + scl[col]                                       (column bias class)
+// plus the tensor's role offset (656 tables per role).
+#include "api_util.h"
+#include "detmath.cuh"
+#include "rans.cuh"
+
+namespace sg {
+namespace r2 {
+
+constexpr int PB = 15;
+constexpr int TPB = 64;
+
+struct TB { long long doff; int rowlen, rowbase, colbase, tab, rmap, pad; };       // bf16v2.py:158
+struct SG { int t, n; long long i0; };                                             // bf16v2.py:159
+
+SG_DEVINL int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+struct Ctx {
+    const short* rfi; const short* cfi; const signed char* scl; const int* rowmap;
+};
+
+// position of a lane inside its tensor: compact row rc (after duplicate-row removal), column j, original row
+struct Cursor {
+    TB T; int rc, j, orow; const unsigned short* w;
+    SG_DEVINL void seek(const unsigned char* dev, const TB& t, long long i, const int* rowmap) {
+        T = t; rc = (int)(i / T.rowlen); j = (int)(i % T.rowlen);
+        orow = T.rmap >= 0 ? rowmap[T.rmap + rc] : rc;
+        w = reinterpret_cast<const unsigned short*>(dev + T.doff) + (size_t)orow * T.rowlen;
+    }
+    SG_DEVINL void row(const unsigned char* dev, const int* rowmap) {
+        orow = T.rmap >= 0 ? rowmap[T.rmap + rc] : rc;
+        w = reinterpret_cast<const unsigned short*>(dev + T.doff) + (size_t)orow * T.rowlen;
+    }
+};
+
+SG_DEVINL void contexts(const Ctx& c, const TB& T, int orow, int j, int& pred, int& pe, int& sc) {
+    pred = c.rfi[T.rowbase + orow] + c.cfi[T.colbase + j];
+    pe = clampi(pred + 256, 0, 511);
+    sc = c.scl[T.colbase + j];
+}
+SG_DEVINL int mctx(int ex, int pred) { return clampi(8 * ex - pred - 1016 + 64, 0, 127); }
+
+// warp-aggregated histogram add: lanes hitting the same counter make one atomic
+SG_DEVINL void hadd(unsigned* counts, unsigned key) {
+    const unsigned m = __match_any_sync(__activemask(), key);
+    if ((threadIdx.x & 31) == (unsigned)(__ffs(m) - 1)) atomicAdd(counts + key, (unsigned)__popc(m));
+}
+
+__global__ void __launch_bounds__(TPB) k_r2_hist(const unsigned char* __restrict__ dev, const TB* __restrict__ tb, const SG* __restrict__ sg,
+                                                 int nseg, Ctx c, unsigned* __restrict__ counts) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= nseg) return;
+    const SG g = sg[s];
+    Cursor q; q.seek(dev, tb[g.t], g.i0, c.rowmap);
+    for (int k = 0; k < g.n; ++k) {
+        const unsigned u = q.w[q.j];
+        const int ex = (u >> 7) & 255, man = u & 127, sgn = u >> 15;
+        int pred, pe, sc; contexts(c, q.T, q.orow, q.j, pred, pe, sc);
+        hadd(counts, (unsigned)(q.T.tab + pe) * 256 + ex);
+        atomicAdd(counts + (size_t)(q.T.tab + 512 + mctx(ex, pred)) * 256 + man, 1u);
+        hadd(counts, (unsigned)(q.T.tab + 640 + sc) * 256 + sgn);
+        if (++q.j == q.T.rowlen) { q.j = 0; ++q.rc; if (k + 1 < g.n) q.row(dev, c.rowmap); }
+    }
+}
+
+__global__ void __launch_bounds__(TPB) k_r2_enc(const unsigned char* __restrict__ dev, const TB* __restrict__ tb, const SG* __restrict__ sg,
+                                                int nseg, Ctx c, const RansSym* __restrict__ enc, unsigned char* __restrict__ out, size_t cap,
+                                                unsigned* __restrict__ out_len) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= nseg) return;
+    const SG g = sg[s];
+    Cursor q; q.seek(dev, tb[g.t], g.i0 + g.n - 1, c.rowmap);
+    unsigned char* slot = out + (size_t)s * cap;
+    ByteWriterDown wr; wr.init(slot + cap);
+    unsigned x = RANS_L;
+    for (int k = g.n - 1; k >= 0; --k) {
+        const unsigned u = q.w[q.j];
+        const int ex = (u >> 7) & 255, man = u & 127, sgn = u >> 15;
+        int pred, pe, sc; contexts(c, q.T, q.orow, q.j, pred, pe, sc);
+        rans_put<PB>(x, wr, enc[(size_t)(q.T.tab + 640 + sc) * 256 + sgn]);
+        rans_put<PB>(x, wr, enc[(size_t)(q.T.tab + 512 + mctx(ex, pred)) * 256 + man]);
+        rans_put<PB>(x, wr, enc[(size_t)(q.T.tab + pe) * 256 + ex]);
+        if (wr.ptr() < slot + 64) { out_len[s] = 0xffffffffu; return; }
+        if (--q.j < 0) { q.j = q.T.rowlen - 1; --q.rc; if (k > 0) q.row(dev, c.rowmap); }
+    }
+    rans_flush(x, wr);
+    wr.flush(slot);
+    out_len[s] = (unsigned)(slot + cap - wr.ptr());
+}
+
+__global__ void __launch_bounds__(TPB) k_r2_dec(const unsigned char* __restrict__ in, const unsigned long long* __restrict__ in_off,
+                                                const unsigned long long* __restrict__ in_end, unsigned char* __restrict__ dev,
+                                                const TB* __restrict__ tb, const SG* __restrict__ sg, int nseg, Ctx c,
+                                                const RansSym* __restrict__ enc, const unsigned char* __restrict__ lut, int* __restrict__ status) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= nseg) return;
+    const SG g = sg[s];
+    Cursor q; q.seek(dev, tb[g.t], g.i0, c.rowmap);
+    ByteReaderUp rd; rd.init(in + in_off[s], in + in_end[s]);
+    unsigned x = rans_init(rd);
+    for (int k = 0; k < g.n; ++k) {
+        int pred, pe, sc; contexts(c, q.T, q.orow, q.j, pred, pe, sc);
+        const int t0 = q.T.tab + pe;
+        const int ex = (int)rans_get<PB>(x, rd, lut + ((size_t)t0 << PB), enc + (size_t)t0 * 256);
+        const int t1 = q.T.tab + 512 + mctx(ex, pred);
+        const int man = (int)rans_get<PB>(x, rd, lut + ((size_t)t1 << PB), enc + (size_t)t1 * 256);
+        const int t2 = q.T.tab + 640 + sc;
+        const int sgn = (int)rans_get<PB>(x, rd, lut + ((size_t)t2 << PB), enc + (size_t)t2 * 256);
+        const_cast<unsigned short*>(q.w)[q.j] = (unsigned short)((sgn << 15) | (ex << 7) | man);
+        if (rd.over) break;
+        if (++q.j == q.T.rowlen) { q.j = 0; ++q.rc; if (k + 1 < g.n) q.row(dev, c.rowmap); }
+    }
+    if (rd.over || x != RANS_L || rd.p != rd.end) atomicOr(status, SG_ST_CORRUPT);
+}
+
+// 64-bit row fingerprints for duplicate-row detection (bf16v2.py:148-155): an order-dependent integer recurrence, one
+// lane per row
+__global__ void __launch_bounds__(128) k_row_hash(const unsigned short* __restrict__ w, int nrows, int rowlen, unsigned long long* __restrict__ h) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= nrows) return;
+    unsigned long long a = 1469598103934665603ull;
+    const unsigned short* p = w + (size_t)r * rowlen;
+    for (int j = 0; j < rowlen; ++j) { a ^= p[j]; a *= 1099511628211ull; a ^= a >> 29; }
+    h[r] = a;
+}
+
+// duplicate rows copied from their source rows after decoding (bf16v2.py:475-480): pairs = (dup row, source row)
+__global__ void __launch_bounds__(256) k_copy_rows(unsigned short* __restrict__ w, int rowlen, const long long* __restrict__ pairs, int npairs) {
+    const int p = blockIdx.x;
+    if (p >= npairs) return;
+    unsigned short* d = w + (size_t)pairs[2 * p] * rowlen;
+    const unsigned short* s = w + (size_t)pairs[2 * p + 1] * rowlen;
+    for (int j = threadIdx.x; j < rowlen; j += blockDim.x) d[j] = s[j];
+}
+
+// ---- statistics ----------------------------------------------------------------------------------------------------
+// rfi[r] = rint(8 log2 rms(row r)), and rfa[r] = (float) 2^(log2 rms) used to normalise the row in the column pass.
+// One warp per row; the float64 sum of squares runs in column order (lane 0 extends the chain over staged squares).
+__global__ void __launch_bounds__(128) k_r2_rowstat(const unsigned short* __restrict__ w, int nrows, int rowlen, short* __restrict__ rfi,
+                                                    float* __restrict__ rfa) {
+    __shared__ double sq[4][256];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 4 + warp;
+    if (r >= nrows) return;
+    const unsigned short* p = w + (size_t)r * rowlen;
+    double s = 0.0;
+    for (int c0 = 0; c0 < rowlen; c0 += 256) {
+        const int n = min(256, rowlen - c0);
+        for (int i = lane; i < n; i += 32) { const double v = (double)__uint_as_float((unsigned)p[c0 + i] << 16); sq[warp][i] = v * v; }
+        __syncwarp();
+        if (lane == 0) for (int i = 0; i < n; ++i) s = s + sq[warp][i];
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const double rf = dm::log2v(sqrt(s / (double)rowlen) + 1e-30);
+        rfa[r] = (float)dm::exp2v(rf);
+        rfi[r] = (short)fmin(fmax(rint(rf * 8.0), -32768.0), 32767.0);
+    }
+}
+// per (row chunk, column): float64 sums of v^2 and v over the chunk's rows in row order, v = weight / rfa[row] in float32
+__global__ void __launch_bounds__(256) k_r2_colpart(const unsigned short* __restrict__ w, int nrows, int rowlen, int step,
+                                                    const float* __restrict__ rfa, double* __restrict__ part) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int q = blockIdx.y;
+    if (c >= rowlen) return;
+    const int r0 = q * step, r1 = min(nrows, r0 + step);
+    double s2 = 0.0, s1 = 0.0;
+    for (int r = r0; r < r1; ++r) {
+        const float f = __fdiv_rn(__uint_as_float((unsigned)w[(size_t)r * rowlen + c] << 16), rfa[r]);
+        const double v = (double)f;
+        s2 = s2 + v * v;
+        s1 = s1 + v;
+    }
+    part[((size_t)q * rowlen + c) * 2] = s2;
+    part[((size_t)q * rowlen + c) * 2 + 1] = s1;
+}
+__global__ void __launch_bounds__(256) k_r2_colfinal(const double* __restrict__ part, int nchunks, int nrows, int rowlen,
+                                                     short* __restrict__ cfi, signed char* __restrict__ scl) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= rowlen) return;
+    double s2 = 0.0, s1 = 0.0;
+    for (int q = 0; q < nchunks; ++q) { s2 = s2 + part[((size_t)q * rowlen + c) * 2]; s1 = s1 + part[((size_t)q * rowlen + c) * 2 + 1]; }
+    const double cf = dm::log2v(sqrt(s2 / (double)nrows) + 1e-30);
+    const double ci = fmin(fmax(rint(cf * 8.0), -32768.0), 32767.0);
+    cfi[c] = (short)ci;
+    const double bias = (s1 / (double)nrows) / dm::exp2v((double)(short)ci / 8.0);
+    scl[c] = (signed char)fmin(fmax(floor(bias * 16.0) + 8.0, 0.0), 15.0);
+}
+
+// ---- generic detmath entry points (seedpack/detmath.py:67-106) --------------------------------------------------------
+__global__ void k_dm_log2(const double* x, long long n, double* y) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = dm::log2v(x[i]);
+}
+__global__ void k_dm_exp2(const double* x, long long n, double* y) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = dm::exp2v(x[i]);
+}
+__global__ void k_dm_rows(const float* x, long long nr, long long nc, int sq, double* out) {
+    const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= nr) return;
+    const float* p = x + r * nc;
+    double s = 0.0;
+    if (sq) for (long long j = 0; j < nc; ++j) { const double v = p[j]; s = s + v * v; }
+    else for (long long j = 0; j < nc; ++j) s = s + (double)p[j];
+    out[r] = s;
+}
+__global__ void k_dm_cols(const float* x, long long nr, long long nc, int sq, const unsigned char* mask, double* out) {
+    const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= nc) return;
+    double s = 0.0;
+    for (long long r = 0; r < nr; ++r) {
+        if (mask && !mask[r]) continue;
+        const double v = x[r * nc + c];
+        s = s + (sq ? v * v : v);
+    }
+    out[c] = s;
+}
+
+}  // namespace r2
+}  // namespace sg
+
+using namespace sg;
+using namespace sg::r2;
+
+static int r2_common(const void* dev, const void* tb, const void* sgp, int nseg, const void* rfi, const void* cfi, const void* scl) {
+    if (!dev || !tb || !sgp || !rfi || !cfi || !scl || nseg < 0) return SG_ERR_ARG;
+    return SG_OK;
+}
+
+extern "C" int sg_r2_hist(int device, void* stream, const unsigned char* dev, const void* tb, const void* sgp, int nseg, const short* rfi,
+                          const short* cfi, const signed char* scl, const int* rowmap, unsigned* counts) {
+    int rc = r2_common(dev, tb, sgp, nseg, rfi, cfi, scl);
+    if (rc != SG_OK || !counts) return rc != SG_OK ? rc : SG_ERR_ARG;
+    if (nseg == 0) return SG_OK;
+    rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    Ctx c = {rfi, cfi, scl, rowmap};
+    k_r2_hist<<<(nseg + TPB - 1) / TPB, TPB, 0, (cudaStream_t)stream>>>(dev, (const TB*)tb, (const SG*)sgp, nseg, c, counts);
+    return cuda_ok(cudaGetLastError());
+}
+
+extern "C" int sg_r2_encode(int device, void* stream, const unsigned char* dev, const void* tb, const void* sgp, int nseg, const short* rfi,
+                            const short* cfi, const signed char* scl, const int* rowmap, const void* enc_tab, unsigned char* slots,
+                            size_t cap, unsigned* out_len) {
+    int rc = r2_common(dev, tb, sgp, nseg, rfi, cfi, scl);
+    if (rc != SG_OK) return rc;
+    if (!enc_tab || !slots || !out_len) return SG_ERR_ARG;
+    if (cap < 128 || cap % 16 || (uintptr_t)slots % 16) return SG_ERR_ALIGN;
+    if (nseg == 0) return SG_OK;
+    rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    Ctx c = {rfi, cfi, scl, rowmap};
+    k_r2_enc<<<(nseg + TPB - 1) / TPB, TPB, 0, (cudaStream_t)stream>>>(dev, (const TB*)tb, (const SG*)sgp, nseg, c, (const RansSym*)enc_tab,
+                                                                       slots, cap, out_len);
+    return cuda_ok(cudaGetLastError());
+}
+
+extern "C" int sg_r2_decode(int device, void* stream, const unsigned char* in, const unsigned long long* in_off,
+                            const unsigned long long* in_end, unsigned char* dev, const void* tb, const void* sgp, int nseg, const short* rfi,
+                            const short* cfi, const signed char* scl, const int* rowmap, const void* enc_tab, const unsigned char* lut) {
+    int rc = r2_common(dev, tb, sgp, nseg, rfi, cfi, scl);
+    if (rc != SG_OK) return rc;
+    if (!in || !in_off || !in_end || !enc_tab || !lut) return SG_ERR_ARG;
+    if ((uintptr_t)in % 16) return SG_ERR_ALIGN;
+    if (nseg == 0) return SG_OK;
+    rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    Ctx c = {rfi, cfi, scl, rowmap};
+    k_r2_dec<<<(nseg + TPB - 1) / TPB, TPB, 0, (cudaStream_t)stream>>>(in, in_off, in_end, dev, (const TB*)tb, (const SG*)sgp, nseg, c,
+                                                                       (const RansSym*)enc_tab, lut, status_word(device));
+    return cuda_ok(cudaGetLastError());
+}
+
+extern "C" int sg_row_hash(int device, void* stream, const void* w, int nrows, int rowlen, unsigned long long* h) {
+    if (!w || !h || nrows < 0 || rowlen <= 0) return SG_ERR_ARG;
+    if (nrows == 0) return SG_OK;
+    int rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    k_row_hash<<<(nrows + 127) / 128, 128, 0, (cudaStream_t)stream>>>((const unsigned short*)w, nrows, rowlen, h);
+    return cuda_ok(cudaGetLastError());
+}
+
+extern "C" int sg_copy_rows(int device, void* stream, void* w, int rowlen, const long long* pairs, int npairs) {
+    if (!w || !pairs || npairs < 0 || rowlen <= 0) return SG_ERR_ARG;
+    if (npairs == 0) return SG_OK;
+    int rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    k_copy_rows<<<npairs, 256, 0, (cudaStream_t)stream>>>((unsigned short*)w, rowlen, pairs, npairs);
+    return cuda_ok(cudaGetLastError());
+}
+
+static int r2_step(int rowlen) { const int s = (16 << 20) / rowlen; return s < 1 ? 1 : s; }
+
+extern "C" size_t sg_r2_stats_scratch_bytes(int nrows, int rowlen) {
+    if (nrows <= 0 || rowlen <= 0) return 0;
+    const int step = r2_step(rowlen), nchunks = (nrows + step - 1) / step;
+    return ((size_t)nrows * 4 + 255) / 256 * 256 + (size_t)nchunks * rowlen * 16;
+}
+
+extern "C" int sg_r2_stats(int device, void* stream, const void* w, int nrows, int rowlen, short* rfi, short* cfi, signed char* scl,
+                           void* scratch, size_t scratch_bytes) {
+    if (!w || !rfi || !cfi || !scl || nrows <= 0 || rowlen <= 0) return SG_ERR_ARG;
+    if (!scratch || scratch_bytes < sg_r2_stats_scratch_bytes(nrows, rowlen) || (uintptr_t)scratch % 16) return SG_ERR_SCRATCH;
+    int rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int step = r2_step(rowlen), nchunks = (nrows + step - 1) / step;
+    if (nchunks > 65535) return SG_ERR_LIMIT;
+    float* rfa = (float*)scratch;
+    double* part = (double*)((unsigned char*)scratch + ((size_t)nrows * 4 + 255) / 256 * 256);
+    k_r2_rowstat<<<(nrows + 3) / 4, 128, 0, st>>>((const unsigned short*)w, nrows, rowlen, rfi, rfa);
+    k_r2_colpart<<<dim3((rowlen + 255) / 256, nchunks), 256, 0, st>>>((const unsigned short*)w, nrows, rowlen, step, rfa, part);
+    k_r2_colfinal<<<(rowlen + 255) / 256, 256, 0, st>>>(part, nchunks, nrows, rowlen, cfi, scl);
+    return cuda_ok(cudaGetLastError());
+}
+
+extern "C" int sg_dm_log2(int device, void* stream, const double* x, long long n, double* y) {
+    if (n < 0 || (n && (!x || !y))) return SG_ERR_ARG;
+    if (n == 0) return SG_OK;
+    int rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    k_dm_log2<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, n, y);
+    return cuda_ok(cudaGetLastError());
+}
+extern "C" int sg_dm_exp2(int device, void* stream, const double* x, long long n, double* y) {
+    if (n < 0 || (n && (!x || !y))) return SG_ERR_ARG;
+    if (n == 0) return SG_OK;
+    int rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    k_dm_exp2<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, n, y);
+    return cuda_ok(cudaGetLastError());
+}
+extern "C" int sg_dm_rows(int device, void* stream, const float* x, long long nr, long long nc, int square, double* out) {
+    if (nr < 0 || nc < 0 || (nr && (!x || !out))) return SG_ERR_ARG;
+    if (nr == 0) return SG_OK;
+    int rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    k_dm_rows<<<(unsigned)((nr + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, nr, nc, square, out);
+    return cuda_ok(cudaGetLastError());
+}
+extern "C" int sg_dm_cols(int device, void* stream, const float* x, long long nr, long long nc, int square, const unsigned char* mask,
+                          double* out) {
+    if (nr < 0 || nc < 0 || (nc && (!x || !out))) return SG_ERR_ARG;
+    if (nc == 0) return SG_OK;
+    int rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    k_dm_cols<<<(unsigned)((nc + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, nr, nc, square, mask, out);
+    return cuda_ok(cudaGetLastError());
+}
