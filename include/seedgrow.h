@@ -126,6 +126,14 @@ SG_API int sg_quantize_tensors(int device, void *stream, int ggml_type, int vari
                         const sg_tensor *h_tensors, int n_tensors,
                         void *scratch, size_t scratch_bytes);
 
+/* Dequantise n_weights weights of ggml type T (a multiple of its block size) to float32 with the arithmetic of
+ * dequantize_row_<type>; replaces k_dq_<type> (seedpack/gpuquant.py:215-219).  Lattice types need sg_tables_install. */
+SG_API int sg_dequantize(int device, void *stream, int T, const unsigned char *y, float *x, long long n_weights);
+/* BF16 / F16 / F32 (SG_DT_*) to any of the three; to BF16 rounds to nearest even on the bits, to F16 IEEE round to
+ * nearest; replaces M28RepoGPU._float_dev (seedpack/repo3.py:673-689) */
+SG_API int sg_convert_float(int device, void *stream, const void *src, int src_dtype, void *dst, int dst_dtype,
+                            long long n);
+
 /* ---- per-block residual ------------------------------------------------------------------------------
  * Replaces the host-side NumPy helpers _xor_async / _diff_async / _count_diff / _xor3 (seedpack/repo3.py:456-510),
  * which need a device-to-host copy of every prediction first.

@@ -40,6 +40,8 @@ SIGNATURES = {
     "sg_tables_host": (_I, [_I, _I, ctypes.POINTER(_P), ctypes.POINTER(_Z)]),
     "sg_quantize_scratch_bytes": (_Z, [_I, ctypes.POINTER(sg_tensor), _I]),
     "sg_quantize_tensors": (_I, [_I, _P, _I, _I, _P, _I, _P, _P, ctypes.POINTER(sg_tensor), _I, _P, _Z]),
+    "sg_dequantize": (_I, [_I, _P, _I, _P, _P, _L]),
+    "sg_convert_float": (_I, [_I, _P, _P, _I, _P, _I, _L]),
     "sg_residual_xor": (_I, [_I, _P, _P, _P, _P, _P, _Z, _P]),
     "sg_residual_blocks": (_I, [_I, _P, _P, _P, _I, _L, _P, _P]),
     "sg_rans_hist": (_I, [_I, _P, _P, _P, _I, _L, _P]),

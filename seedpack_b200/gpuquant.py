@@ -130,3 +130,25 @@ class GPUQuant:
         """quantise several tensors of one type in one launch.  xs: list of 2-D device tensors
         (nrows, n_per_row); returns device uint8 tensors (seedpack/gpuquant.py:424-430)."""
         return self.quantize_tensors(ttype, [(x.reshape(-1), x.shape[-1]) for x in xs], imatrices, variant, device=True)
+
+    def dequantize(self, ttype, y, npr=None, out=None):
+        """quantised bytes of a tensor (device uint8) -> float32 device tensor (or into `out`) with llama.cpp's own
+        dequantize_row_<type> (seedpack/gpuquant.py:413-422); `npr` is accepted for compatibility (rows do not matter)"""
+        _, qk, bs = QFUN[ttype]
+        y = y.view(torch.uint8).reshape(-1)
+        n = y.numel() // bs * qk
+        x = torch.empty(n, dtype=torch.float32, device=self.device) if out is None else out
+        rc = self.lib.sg_dequantize(self.device.index, self._stream(), ttype, ctypes.c_void_p(y.data_ptr()), ctypes.c_void_p(x.data_ptr()), n)
+        _lib.check(rc, f"sg_dequantize(type {ttype})")
+        return x
+
+    def convert_float(self, src, dst_dtype):
+        """BF16 / F16 / F32 tensor -> torch.bfloat16 / float16 / float32 (seedpack/repo3.py:673-689 `_float_dev`)"""
+        sd = _DT[src.dtype][0]
+        dd = {torch.bfloat16: _lib.DT_BF16, torch.float16: _lib.DT_F16, torch.float32: _lib.DT_F32}[dst_dtype]
+        src = src.contiguous()
+        dst = torch.empty(src.numel(), dtype=dst_dtype, device=self.device)
+        rc = self.lib.sg_convert_float(self.device.index, self._stream(), ctypes.c_void_p(src.data_ptr()), sd, ctypes.c_void_p(dst.data_ptr()),
+                                       dd, src.numel())
+        _lib.check(rc, "sg_convert_float")
+        return dst

@@ -111,3 +111,32 @@ def test_quantize_matches_golden_vectors(gq):
         got = gq.quantize_tensors(int(t), [(x, bits.shape[1])], [imx if use == "imx" else None], variant=int(v[1:]))[0]
         assert np.array_equal(got, gold[key]), key
     assert gq.status() == 0
+
+
+@pytest.mark.parametrize("t", TYPES)
+def test_dequantize_matches_reference(gq, t):
+    """dequantised floats equal the reference's dequantize_row_<type> bit for bit (blocks = quantiser output)"""
+    import torch
+    if not ref.available():
+        pytest.skip("oracle/_ref not built")
+    nrows, npr = 12, 1024
+    bits = synth.weights(nrows, npr, seed=40 + t)
+    imx = synth.imatrix(npr, seed=t)
+    y = ref.quantize(t, synth.bf16_bits_to_f32(bits).reshape(nrows, npr), imx)
+    want = ref.dequantize(t, y, nrows * npr)
+    got = gq.dequantize(t, torch.from_numpy(y).cuda()).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_convert_float(gq):
+    import torch
+    rng = np.random.default_rng(1)
+    x = np.concatenate([rng.normal(0, 1, 5000), rng.normal(0, 1e-6, 1000), [0.0, -0.0, 65504.0, 1e-8, 3.0e38]]).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    b = gq.convert_float(xd, torch.bfloat16)
+    assert np.array_equal(b.view(torch.int16).cpu().numpy().view(np.uint16), synth.f32_to_bf16_bits(x))
+    h = gq.convert_float(xd, torch.float16)
+    with np.errstate(over="ignore"):
+        assert np.array_equal(h.view(torch.int16).cpu().numpy().view(np.uint16), x.astype(np.float16).view(np.uint16))
+    back = gq.convert_float(b, torch.float32)
+    assert np.array_equal(back.cpu().numpy(), synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(x)))
