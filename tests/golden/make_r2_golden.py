@@ -39,7 +39,7 @@ codec = bf16v2.BF16v2(group_bytes=150_000)            # several groups
 buf = codec.compress(data)
 assert bytes(codec.decompress(buf)) == data
 ch = unpack(buf)
-out = {"data": np.frombuffer(data, np.uint8)}
+out = {"data": np.frombuffer(data, np.uint8), "counts": np.asarray(codec.last_counts)}
 for k in ("meta", "side", "tables", "lens", "stream"):
     out["part_" + k] = np.frombuffer(bytes(ch[k]), np.uint8)
 x = np.concatenate([rng.normal(0, 1, 500), np.exp(rng.normal(0, 20, 500)), [0.0, 1.0, 2.0, 1e-310, 4.9e-324, np.inf]])
