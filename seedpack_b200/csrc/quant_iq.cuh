@@ -12,6 +12,8 @@
 // 3915-4351 (IQ3_XXS/S), 4444-4671 (IQ1_S), 4693-4916 (IQ1_M); the IQ1_M variant 1 is the direct-sum
 // split search of the pre-f95b0d9539 llama.cpp sources.
 #pragma once
+#include <type_traits>
+
 #include "api_util.h"
 #include "quant_k.cuh"
 
@@ -22,6 +24,9 @@ struct GridTable {
     const void* grid;            // uint64 (IQ2 family, 8 int8 per point) or uint32 (IQ3 family, 4 int8)
     const int* map;              // >= 0: grid index, < 0: -(offset into neighbours) - 1
     const uint16_t* neighbours;  // [count, indices...] lists
+    const uint16_t* keys;        // per point: its levels packed as a map index (2 bits x 8 or 3 bits x 4)
+    const uint16_t* nbkeys;      // the neighbour lists with keys in place of point indices, padded by 64 entries
+    int nb_size, map_size;       // entries of neighbours / map
 };
 // index: 0 IQ2_XXS (256), 1 IQ2_XS (512), 2 IQ1_S/IQ1_M (2048), 3 IQ2_S (1024), 4 IQ3_XXS (256), 5 IQ3_S (512)
 struct IqTables { GridTable t[6]; };
@@ -166,11 +171,12 @@ template <bool XS> struct IQ4 {
 };
 
 // ==================================================================================================
-// Lattice types.  Per-thread arrays in shared memory, [element][thread].
-template <int BLK> struct IqSmem {
-    float xval[BLK][IQ_TPB];
-    float wgt[BLK][IQ_TPB];
-    float waux[BLK][IQ_TPB];
+// Lattice types.  Values that are indexed dynamically live in shared memory as [element][thread]; TPB is the
+// CTA size of the kernel that owns the storage.
+template <int BLK, int TPB, int NTAB> struct IqSmem {
+    float xval[BLK][TPB];         // sign-folded values
+    float waux[BLK][TPB];         // sqrt(weight): the weights of the neighbour search
+    float tab[NTAB][32];          // per lane group: distance terms of the list being searched (cooperative search)
 };
 
 // codes of up to 8 groups, 16 bits per group (the group's map index u)
@@ -185,71 +191,148 @@ struct Codes {
     }
 };
 
-// TYPE-specific constants of the five lattice quantisers
+// TYPE-specific constants of the five lattice quantisers.  W: lanes that share one neighbour list in the
+// cooperative search (0 = every lane walks its own lists, tables in shared memory).
 template <int TYPE> struct Lat;
-template <> struct Lat<SG_IQ2_XXS> { static constexpr int BLK = 32, G = 8, CB = 2, KMAXQ = 3, TAB = 0, BS = 66, IS0 = -6, IS1 = 6; static constexpr bool PARITY = true; };
-template <> struct Lat<SG_IQ2_XS>  { static constexpr int BLK = 16, G = 8, CB = 2, KMAXQ = 3, TAB = 1, BS = 74, IS0 = -9, IS1 = 9; static constexpr bool PARITY = true; };
-template <> struct Lat<SG_IQ2_S>   { static constexpr int BLK = 16, G = 8, CB = 2, KMAXQ = 3, TAB = 3, BS = 82, IS0 = -9, IS1 = 9; static constexpr bool PARITY = false; };
-template <> struct Lat<SG_IQ3_XXS> { static constexpr int BLK = 32, G = 4, CB = 3, KMAXQ = 8, TAB = 4, BS = 98, IS0 = -15, IS1 = 15; static constexpr bool PARITY = true; };
-template <> struct Lat<SG_IQ3_S>   { static constexpr int BLK = 32, G = 4, CB = 3, KMAXQ = 8, TAB = 5, BS = 110, IS0 = -9, IS1 = 9; static constexpr bool PARITY = false; };
+template <> struct Lat<SG_IQ2_XXS> { static constexpr int W = 16, BLK = 32, G = 8, CB = 2, KMAXQ = 3, TAB = 0, BS = 66, IS0 = -6, IS1 = 6; static constexpr bool PARITY = true; };
+template <> struct Lat<SG_IQ2_XS>  { static constexpr int W = 16, BLK = 16, G = 8, CB = 2, KMAXQ = 3, TAB = 1, BS = 74, IS0 = -9, IS1 = 9; static constexpr bool PARITY = true; };
+template <> struct Lat<SG_IQ2_S>   { static constexpr int W = 8, BLK = 16, G = 8, CB = 2, KMAXQ = 3, TAB = 3, BS = 82, IS0 = -9, IS1 = 9; static constexpr bool PARITY = false; };
+template <> struct Lat<SG_IQ3_XXS> { static constexpr int W = 0, BLK = 32, G = 4, CB = 3, KMAXQ = 8, TAB = 4, BS = 98, IS0 = -15, IS1 = 15; static constexpr bool PARITY = true; };
+template <> struct Lat<SG_IQ3_S>   { static constexpr int W = 0, BLK = 32, G = 4, CB = 3, KMAXQ = 8, TAB = 5, BS = 110, IS0 = -9, IS1 = 9; static constexpr bool PARITY = false; };
 
-template <int G> SG_DEVINL void grid_point(const GridTable& t, int idx, int (&pg)[G]) {
-    if (G == 8) {
-        const unsigned long long v = __ldg(static_cast<const unsigned long long*>(t.grid) + idx);
+// what a search reads: tuple -> point index or list, and the lists themselves.  MapT is int (tables in global
+// memory) or int16_t (the IQ3 tables copied into shared memory; their offsets fit 15 bits).
+template <class MapT> struct TabView {
+    const MapT* map;
+    const uint16_t* nbk;
+    unsigned key0;               // levels of point 0: what a search that found nothing falls back to
+};
+
+// exact float of a small non-negative integer without the conversion pipe: 0x4b000000 is 8388608.0f
+SG_DEVINL float small_to_float(unsigned v) { return fsub(__int_as_float(0x4b000000u | v), 8388608.f); }
+
+// weighted squared distance of the point with packed levels `key` from the G values xv at `scale`, added up in
+// index order as iq2_find_best_neighbour / iq3_find_best_neighbour do (ggml-quants.c:3271-3293, 3915-3937)
+template <int G, int CB>
+SG_DEVINL float point_dist2(unsigned key, float scale, const float (&xv)[G], const float (&wv)[G]) {
+    float d2 = 0.f;
 #pragma unroll
-        for (int i = 0; i < G; ++i) pg[i] = (int)(int8_t)(v >> (8 * i));
-    } else {
-        const unsigned v = __ldg(static_cast<const unsigned*>(t.grid) + idx);
-#pragma unroll
-        for (int i = 0; i < G; ++i) pg[i] = (int)(int8_t)(v >> (8 * i));
+    for (int i = 0; i < G; ++i) {
+        const float q = small_to_float(2 * ((key >> (CB * i)) & ((1u << CB) - 1)) + 1);
+        const float diff = fsub(fmul(scale, q), xv[i]);
+        d2 = fadd(d2, fmul(fmul(wv[i], diff), diff));
     }
+    return d2;
 }
 
-// iq2_find_best_neighbour / iq3_find_best_neighbour (ggml-quants.c:3271-3293, 3915-3937): first strictly
-// smaller weighted distance wins.  Returns the grid index, and the point's codes packed as a map index.
-template <int G, int CB, int BLK>
-SG_DEVINL int best_neighbour(const GridTable& t, int list, const IqSmem<BLK>& sm, int tid, int e0, float scale, unsigned& u_out, int* status) {
-    const uint16_t* nb = t.neighbours + list;
-    const int n = __ldg(nb);
-    float best_d2 = 3.402823466e+38F;
-    int grid_index = -1;
+// One lane walks one list: four entries at a time (independent distance chains), compared in list order so that
+// the first strictly smaller distance wins as in the C loop.  Reads up to three entries past the list's end,
+// which the padding of the key lists allows.
+template <int G, int CB, int BLK, int TPB, int NTAB, class MapT>
+SG_DEVINL unsigned own_neighbour(const TabView<MapT>& t, int list, float scale, int e0, const IqSmem<BLK, TPB, NTAB>& sm, int tid, int* status) {
+    const uint16_t* nb = t.nbk + list;
+    const int n = nb[0];
     float xv[G], wv[G];
 #pragma unroll
     for (int i = 0; i < G; ++i) { xv[i] = sm.xval[e0 + i][tid]; wv[i] = sm.waux[e0 + i][tid]; }
+    float best = 3.402823466e+38F;
+    unsigned bu = 0xffffffffu;
 #pragma unroll 1
-    for (int j = 1; j <= n; ++j) {
-        const int gi = __ldg(nb + j);
-        int pg[G];
-        grid_point<G>(t, gi, pg);
-        float d2 = 0.f;
+    for (int j = 0; j < n; j += 4) {
+        unsigned key[4];
+        float d[4];
 #pragma unroll
-        for (int i = 0; i < G; ++i) {
-            const float diff = fsub(fmul(scale, (float)pg[i]), xv[i]);
-            d2 = fadd(d2, fmul(fmul(wv[i], diff), diff));
-        }
-        if (d2 < best_d2) { best_d2 = d2; grid_index = gi; }
+        for (int q = 0; q < 4; ++q) key[q] = nb[1 + j + q];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) d[q] = point_dist2<G, CB>(key[q], scale, xv, wv);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (j + q < n && d[q] < best) { best = d[q]; bu = key[q]; }
     }
-    if (grid_index < 0) { atomicOr(status, SG_ST_OFFGRID); grid_index = 0; }
-    int pg[G];
-    grid_point<G>(t, grid_index, pg);
-    unsigned u = 0;
+    if (bu == 0xffffffffu) { atomicOr(status, SG_ST_OFFGRID); bu = t.key0; }
+    return bu;
+}
+
+// The same search for a whole warp at once, for the lattices whose lists run to hundreds of entries.  Each lane may
+// hold one group of 8 weights that fell off the lattice (`off`, neighbour list `list`, candidate `scale`); the W
+// lanes of a lane group take the group's lists one after the other: lane s looks at entries s, s + W, ..., and a
+// butterfly picks the smallest distance, the earliest entry among equals.  The owner's values are read from its
+// column of shared memory.  With three levels per weight the 24 possible terms w * (scale * q - x)^2 are tabulated
+// once per list; a distance is then 8 dependent adds of looked-up terms, in index order as in the C code.
+// Returns u, replaced for owners by the chosen point's packed levels.
+template <int W, int BLK, int TPB, int NTAB>
+SG_DEVINL unsigned coop_neighbour(const TabView<int>& t, bool off, int list, float scale, unsigned u, int e0, IqSmem<BLK, TPB, NTAB>& sm, int* status) {
+    const int lane = threadIdx.x & 31, sub = lane & (W - 1), gbase = lane & ~(W - 1);
+    const int col0 = threadIdx.x & ~31;
+    float* tab = sm.tab[threadIdx.x / W];
+    const int rot = W == 16 ? ((threadIdx.x / W) & 1) * 16 : 0;      // the two lane groups of a warp use disjoint banks
+    unsigned mine = (__ballot_sync(SG_FULL, off) >> gbase) & ((1u << W) - 1);
+    while (__any_sync(SG_FULL, mine != 0)) {
+        const bool has = mine != 0;
+        const int o = has ? __ffs(mine) - 1 : 0;
+        mine &= mine - 1;
+        const int src = gbase + o;
+        const int olist = __shfl_sync(SG_FULL, list, src);
+        const float osc = __shfl_sync(SG_FULL, scale, src);
+        const int col = col0 + src;
+        const uint16_t* nb = t.nbk + (has ? olist : 0);
+        const int n = has ? (int)__ldg(nb) : 0;
+        unsigned k0 = __ldg(nb + 1 + sub), k1 = __ldg(nb + 1 + sub + W);       // first entries, before n is known
+        {
+            __syncwarp();
+            const int i = sub & 7;
+            const float x = sm.xval[e0 + i][col], w = sm.waux[e0 + i][col];
+            if (W == 8 || sub < 8) {
+                const float d0 = fsub(osc, x), d1 = fsub(fmul(osc, 3.f), x);
+                tab[(4 * i + rot) & 31] = fmul(fmul(w, d0), d0);
+                tab[(4 * i + 1 + rot) & 31] = fmul(fmul(w, d1), d1);
+            }
+            if (W == 8 || sub >= 8) {
+                const float d2 = fsub(fmul(osc, 5.f), x);
+                tab[(4 * i + 2 + rot) & 31] = fmul(fmul(w, d2), d2);
+            }
+            __syncwarp();
+        }
+        const int nmax = (int)__reduce_max_sync(SG_FULL, (unsigned)n);
+        float best = 3.402823466e+38F;
+        int bj = 0x7fffffff;
+#pragma unroll 1
+        for (int j = sub; j < nmax; j += 2 * W) {
+            float da = 0.f, db = 0.f;
 #pragma unroll
-    for (int i = 0; i < G; ++i) u |= (unsigned)((pg[i] - 1) / 2) << (CB * i);
-    u_out = u;
-    return grid_index;
+            for (int i = 0; i < 8; ++i) {
+                da = fadd(da, tab[(4 * i + (int)((k0 >> (2 * i)) & 3u) + rot) & 31]);
+                db = fadd(db, tab[(4 * i + (int)((k1 >> (2 * i)) & 3u) + rot) & 31]);
+            }
+            if (j < n && da < best) { best = da; bj = j; }
+            if (j + W < n && db < best) { best = db; bj = j + W; }
+            if (j + 2 * W < nmax) { k0 = __ldg(nb + 1 + j + 2 * W); k1 = __ldg(nb + 1 + j + 3 * W); }
+        }
+#pragma unroll
+        for (int s = W / 2; s > 0; s >>= 1) {
+            const float ob = __shfl_xor_sync(SG_FULL, best, s);
+            const int oj = __shfl_xor_sync(SG_FULL, bj, s);
+            if (ob < best || (ob == best && oj < bj)) { best = ob; bj = oj; }
+        }
+        if (has && sub == o) {
+            if (bj == 0x7fffffff) { atomicOr(status, SG_ST_OFFGRID); u = t.key0; }
+            else u = __ldg(nb + 1 + bj);
+        }
+    }
+    return u;
 }
 
 // sumqx / sumq2 over the block in index order with q = 2*L + 1
-template <int BLK, int G, int CB>
-SG_DEVINL void block_sums(const Codes& c, const IqSmem<BLK>& sm, int tid, float& sumqx, float& sumq2) {
+template <int BLK, int G, int CB, class SM>
+SG_DEVINL void block_sums(const Codes& c, const float (&wgt)[BLK], const SM& sm, int tid, float& sumqx, float& sumq2) {
     sumqx = 0.f; sumq2 = 0.f;
 #pragma unroll
     for (int k = 0; k < BLK / G; ++k) {
         const unsigned u = c.get(k);
 #pragma unroll
         for (int i = 0; i < G; ++i) {
-            const float q = (float)(2 * (int)((u >> (CB * i)) & ((1u << CB) - 1)) + 1);
-            const float w = sm.wgt[k * G + i][tid];
+            const float q = small_to_float(2 * ((u >> (CB * i)) & ((1u << CB) - 1)) + 1);
+            const float w = wgt[k * G + i];
             sumqx = fadd(sumqx, fmul(fmul(w, sm.xval[k * G + i][tid]), q));
             sumq2 = fadd(sumq2, fmul(fmul(w, q), q));
         }
@@ -260,12 +343,21 @@ template <int TYPE> struct Lattice {
     using P = Lat<TYPE>;
     static constexpr int SLAB = 256, SUB = P::BLK, LANES = 256 / P::BLK, QK = 256, BS = P::BS;
     static constexpr int BLK = P::BLK, G = P::G, CB = P::CB, NG = BLK / G, KMAXQ = P::KMAXQ;
-    using Smem = IqSmem<BLK>;
+    static constexpr int W = P::W, TYPE_ID = TYPE;
+    using MapT = typename std::conditional<W == 0, int16_t, int>::type;
+    using View = TabView<MapT>;
 
-    template <int DT, bool IMX>
-    static SG_DEVINL void run(const Job& job, const Slab& sl, int sub, bool valid, const IqTables& tabs, IqSmem<BLK>& sm) {
-        const GridTable& T = tabs.t[P::TAB];
+    // nearest lattice point of an off-lattice group: cooperative over lane groups, or every lane for itself
+    template <class SM>
+    static SG_DEVINL unsigned search(const View& T, bool off, int list, float scale, unsigned u, int e0, SM& sm, int* status) {
+        if constexpr (W == 0) return off ? own_neighbour<G, CB>(T, list, scale, e0, sm, (int)threadIdx.x, status) : u;
+        else return coop_neighbour<W>(T, off, list, scale, u, e0, sm, status);
+    }
+
+    template <int DT, bool IMX, class SM>
+    static SG_DEVINL void run(const Job& job, const Slab& sl, int sub, bool valid, const View& T, SM& sm) {
         const int tid = threadIdx.x;
+        float wgt[BLK];
         float scale = 0.f;                 // scales[ib]
         Codes L;
         unsigned signs[4] = {0, 0, 0, 0};  // block_signs[k], per group of 8 weights
@@ -284,7 +376,7 @@ template <int TYPE> struct Lattice {
                 if (IMX) w = fmul(qw[i], fsqrt(fadd(sigma2, fmul(x[i], x[i]))));
                 else if (TYPE == SG_IQ2_S) w = fadd(fmul(0.25f, sigma2), fmul(x[i], x[i]));
                 else w = fmul(x[i], x[i]);
-                sm.wgt[i][tid] = w;
+                wgt[i] = w;
                 sm.waux[i][tid] = fsqrt(w);
             }
             // sign folding (ggml-quants.c:3341-3362): groups of 8; with PARITY an odd number of flips is repaired
@@ -303,10 +395,10 @@ template <int TYPE> struct Lattice {
                 if (P::PARITY) {
                     if (nflip & 1) {
                         int imin = 0;
-                        float mn = fmul(fmul(sm.wgt[8 * k][tid], x[8 * k]), x[8 * k]);
+                        float mn = fmul(fmul(wgt[8 * k], x[8 * k]), x[8 * k]);
 #pragma unroll
                         for (int i = 1; i < 8; ++i) {
-                            const float ax = fmul(fmul(sm.wgt[8 * k + i][tid], x[8 * k + i]), x[8 * k + i]);
+                            const float ax = fmul(fmul(wgt[8 * k + i], x[8 * k + i]), x[8 * k + i]);
                             if (ax < mn) { mn = ax; imin = i; }
                         }
 #pragma unroll
@@ -326,77 +418,83 @@ template <int TYPE> struct Lattice {
         const float eps = TYPE == SG_IQ3_XXS ? 1e-8f : TYPE == SG_IQ2_S ? 1e-8f : SG_GROUP_MAX_EPS;
         const bool dead = TYPE == SG_IQ3_S ? !(mx != 0.f) : (mx < eps);
         const float c2k1 = (float)(2 * KMAXQ - 1);
-        if (!dead) {
-            bool go = true;
-            float best = 0.f;
-            float rng;                       // denominator of the candidate inverse scales
-            unsigned ongrid = TYPE == SG_IQ3_S ? 0u : 0xffu;
+        // Every lane runs the candidate loop, because the neighbour search inside it is a warp-wide collective;
+        // `act` marks the lanes whose block is really being searched.
+        bool act = !dead;
+        float best = 0.f;
+        float rng = 1.f;                     // denominator of the candidate inverse scales
+        unsigned ongrid = TYPE == SG_IQ3_S ? 0u : 0xffu;
+        if (act) {
             if (TYPE == SG_IQ2_XXS) {
                 float xv[32], wv[32];
                 int Lq[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) { xv[i] = sm.xval[i][tid]; wv[i] = sm.wgt[i][tid]; }
+                for (int i = 0; i < 32; ++i) { xv[i] = sm.xval[i][tid]; wv[i] = wgt[i]; }
                 scale = make_qp_quants<32>(KMAXQ + 1, xv, Lq, wv);
                 rng = fmul(scale, (float)KMAXQ);       // eff_max
-                if (rng <= 0.f) go = false;
+                if (rng <= 0.f) act = false;
             } else {
                 rng = mx;
                 scale = fdiv(mx, TYPE == SG_IQ2_XS || TYPE == SG_IQ2_S ? c_div[DIV_5] : c_div[DIV_15]);
             }
-            if (go) {
-                const float step = (TYPE == SG_IQ3_XXS || TYPE == SG_IQ3_S) ? 0.2f : 0.1f;
+        }
+        {
+            const float step = (TYPE == SG_IQ3_XXS || TYPE == SG_IQ3_S) ? 0.2f : 0.1f;
 #pragma unroll 1
-                for (int is = P::IS0; is <= P::IS1; ++is) {
-                    const float id = fdiv(fadd(c2k1, fmul((float)is, step)), rng);
-                    const float this_scale = frcp(id);
-                    Codes aux;
-                    unsigned og = 0;
+            for (int is = P::IS0; is <= P::IS1; ++is) {
+                const float id = fdiv(fadd(c2k1, fmul((float)is, step)), rng);
+                const float this_scale = frcp(id);
+                Codes aux;
+                unsigned og = 0;
 #pragma unroll 1
-                    for (int k = 0; k < NG; ++k) {
-                        unsigned u = 0;
+                for (int k = 0; k < NG; ++k) {
+                    unsigned u = 0;
 #pragma unroll
-                        for (int i = 0; i < G; ++i) {
-                            const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
-                            u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
-                        }
-                        const int gi = __ldg(T.map + u);
-                        if (gi < 0) best_neighbour<G, CB, BLK>(T, -gi - 1, sm, tid, G * k, this_scale, u, job.status);
-                        else og |= 1u << k;
-                        aux.set(k, u);
+                    for (int i = 0; i < G; ++i) {
+                        const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
+                        u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
                     }
-                    float sumqx, sumq2;
-                    block_sums<BLK, G, CB>(aux, sm, tid, sumqx, sumq2);
-                    if (sumq2 > 0.f && fmul(sumqx, sumqx) > fmul(best, sumq2)) {
-                        scale = fdiv(sumqx, sumq2); best = fmul(scale, sumqx);
-                        L = aux; ongrid = og;
-                    }
+                    const int gi = T.map[u];
+                    if (gi >= 0) og |= 1u << k;
+                    u = search(T, act && gi < 0, -gi - 1, this_scale, u, G * k, sm, job.status);
+                    aux.set(k, u);
                 }
-                // second pass at the winning scale
-                bool refit;
-                if (TYPE == SG_IQ2_XXS) refit = scale > 0.f;
-                else {
-                    const unsigned all = (1u << NG) - 1;
-                    refit = (ongrid & all) != all && scale > 0.f;
+                float sumqx, sumq2;
+                block_sums<BLK, G, CB>(aux, wgt, sm, tid, sumqx, sumq2);
+                if (act && sumq2 > 0.f && fmul(sumqx, sumqx) > fmul(best, sumq2)) {
+                    scale = fdiv(sumqx, sumq2); best = fmul(scale, sumqx);
+                    L = aux; ongrid = og;
+                }
+            }
+            // second pass at the winning scale
+            bool refit;
+            if (TYPE == SG_IQ2_XXS) refit = act && scale > 0.f;
+            else {
+                const unsigned all = (1u << NG) - 1;
+                refit = act && (ongrid & all) != all && scale > 0.f;
+            }
+            if (__any_sync(SG_FULL, refit)) {
+                const float id = frcp(scale);
+#pragma unroll 1
+                for (int k = 0; k < NG; ++k) {
+                    const bool skip = !refit || ((TYPE == SG_IQ2_XS || TYPE == SG_IQ2_S || TYPE == SG_IQ3_XXS) && ((ongrid >> k) & 1));
+                    unsigned u = 0;
+#pragma unroll
+                    for (int i = 0; i < G; ++i) {
+                        const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
+                        u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
+                    }
+                    const int gi = T.map[u];
+                    u = search(T, !skip && gi < 0, -gi - 1, scale, u, G * k, sm, job.status);
+                    if (!skip) L.set(k, u);           // on the grid the codes ARE the grid point
                 }
                 if (refit) {
-                    const float id = frcp(scale);
-#pragma unroll 1
-                    for (int k = 0; k < NG; ++k) {
-                        if ((TYPE == SG_IQ2_XS || TYPE == SG_IQ2_S || TYPE == SG_IQ3_XXS) && ((ongrid >> k) & 1)) continue;
-                        unsigned u = 0;
-#pragma unroll
-                        for (int i = 0; i < G; ++i) {
-                            const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
-                            u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
-                        }
-                        const int gi = __ldg(T.map + u);
-                        if (gi < 0) best_neighbour<G, CB, BLK>(T, -gi - 1, sm, tid, G * k, scale, u, job.status);
-                        L.set(k, u);           // on the grid the codes ARE the grid point
-                    }
                     float sumqx, sumq2;
-                    block_sums<BLK, G, CB>(L, sm, tid, sumqx, sumq2);
+                    block_sums<BLK, G, CB>(L, wgt, sm, tid, sumqx, sumq2);
                     if (sumq2 > 0.f) scale = fdiv(sumqx, sumq2);
                 }
+            }
+            if (act) {
                 if (scale < 0.f) {
                     scale = -scale;
                     if (P::PARITY) {
@@ -415,7 +513,7 @@ template <int TYPE> struct Lattice {
         unsigned gidx[NG];
 #pragma unroll
         for (int k = 0; k < NG; ++k) {
-            int gi = wrote ? __ldg(T.map + L.get(k)) : 0;
+            int gi = wrote ? (int)T.map[L.get(k)] : 0;
             if (gi < 0) { atomicOr(job.status, SG_ST_OFFGRID); gi = 0; }
             gidx[k] = (unsigned)gi;
         }
@@ -507,6 +605,18 @@ template <int BLK, int NPS> struct Iq1Smem {
     uint8_t idx[BLK][IQ_TPB];     // sorted position -> element
     uint8_t L[BLK][IQ_TPB];       // ternary codes 0,1,2
 };
+
+template <int G> SG_DEVINL void grid_point(const GridTable& t, int idx, int (&pg)[G]) {
+    if (G == 8) {
+        const unsigned long long v = __ldg(static_cast<const unsigned long long*>(t.grid) + idx);
+#pragma unroll
+        for (int i = 0; i < G; ++i) pg[i] = (int)(int8_t)(v >> (8 * i));
+    } else {
+        const unsigned v = __ldg(static_cast<const unsigned*>(t.grid) + idx);
+#pragma unroll
+        for (int i = 0; i < G; ++i) pg[i] = (int)(int8_t)(v >> (8 * i));
+    }
+}
 
 // iq1_find_best_neighbour2 (ggml-quants.c:4444-4499).  The exhaustive fall-back of the C code is only
 // reachable when every distance is NaN; that case sets SG_ST_OFFGRID instead.
@@ -856,6 +966,51 @@ __global__ void __launch_bounds__(IQ_TPB) k_quant_iq(const __grid_constant__ Job
     T::template run<DT, IMX>(job, sl, sub, valid, tabs, sm);
 }
 
+// lattice types with a cooperative search: 64-thread CTAs, tables read from global memory (they stay in L2)
+template <class T, int DT, bool IMX>
+__global__ void __launch_bounds__(IQ_TPB) k_quant_lat(const __grid_constant__ Job job, const __grid_constant__ GridTable tab) {
+    __shared__ IqSmem<T::BLK, IQ_TPB, IQ_TPB / 8> sm;
+    constexpr int LANES = T::LANES;
+    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long s = g / LANES;
+    const int sub = (int)(g - s * LANES);
+    const bool valid = s < job.nslabs;
+    if (!valid) s = job.nslabs - 1;
+    const Slab sl = locate<T::SLAB>(job, s);
+    typename T::View view;
+    view.map = tab.map; view.nbk = tab.nbkeys; view.key0 = __ldg(tab.keys);
+    T::template run<DT, IMX>(job, sl, sub, valid, view, sm);
+}
+
+// IQ3_XXS / IQ3_S: their tables are small (map 4096 entries, lists < 29 K entries), so each CTA copies them into
+// shared memory once and then walks over tiles of LAT3_TPB blocks; every lane searches its own lists there.
+constexpr int LAT3_TPB = 512;
+template <class T> struct Lat3Smem {
+    IqSmem<T::BLK, LAT3_TPB, 1> v;
+    int16_t map[4096];
+    uint16_t nbk[1];              // nb_size + 64 entries follow
+};
+template <class T, int DT, bool IMX>
+__global__ void __launch_bounds__(LAT3_TPB) k_quant_lat3(const __grid_constant__ Job job, const __grid_constant__ GridTable tab, long long ntiles) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    Lat3Smem<T>& sm = *reinterpret_cast<Lat3Smem<T>*>(raw);
+    for (int i = threadIdx.x; i < 4096; i += LAT3_TPB) sm.map[i] = (int16_t)__ldg(tab.map + i);
+    for (int i = threadIdx.x; i < tab.nb_size + 64; i += LAT3_TPB) sm.nbk[i] = __ldg(tab.nbkeys + i);
+    __syncthreads();
+    typename T::View view;
+    view.map = sm.map; view.nbk = sm.nbk; view.key0 = __ldg(tab.keys);
+    constexpr int LANES = T::LANES;
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const long long g = tile * LAT3_TPB + threadIdx.x;
+        long long s = g / LANES;
+        const int sub = (int)(g - s * LANES);
+        const bool valid = s < job.nslabs;
+        if (!valid) s = job.nslabs - 1;
+        const Slab sl = locate<T::SLAB>(job, s);
+        T::template run<DT, IMX>(job, sl, sub, valid, view, sm.v);
+    }
+}
+
 template <class T, int DT, bool IMX>
 __global__ void __launch_bounds__(128) k_quant_iq4(const __grid_constant__ Job job) {
     constexpr int LANES = T::LANES;
@@ -885,6 +1040,44 @@ static int launch_iq(const Job& job, int dt, cudaStream_t st, const IqTables& ta
     return cuda_ok(cudaGetLastError());
 }
 template <class T, bool IMX>
+static int launch_lat(const Job& job, int dt, cudaStream_t st, const IqTables& tabs) {
+    const GridTable& tab = tabs.t[Lat<T::TYPE_ID>::TAB];
+    const long long threads = job.nslabs * T::LANES;
+    if (threads == 0) return SG_OK;
+    if constexpr (T::W != 0) {
+        const unsigned grid = (unsigned)((threads + IQ_TPB - 1) / IQ_TPB);
+        switch (dt) {
+            case SG_DT_BF16: k_quant_lat<T, SG_DT_BF16, IMX><<<grid, IQ_TPB, 0, st>>>(job, tab); break;
+            case SG_DT_F16:  k_quant_lat<T, SG_DT_F16, IMX><<<grid, IQ_TPB, 0, st>>>(job, tab); break;
+            case SG_DT_F32:  k_quant_lat<T, SG_DT_F32, IMX><<<grid, IQ_TPB, 0, st>>>(job, tab); break;
+            default: return SG_ERR_ARG;
+        }
+    } else {
+        if (tab.map_size != 4096 || tab.nb_size > 32767) return SG_ERR_TABLES;
+        const size_t smem = sizeof(Lat3Smem<T>) + (size_t)(tab.nb_size + 64) * sizeof(uint16_t);
+        const long long ntiles = (threads + LAT3_TPB - 1) / LAT3_TPB;
+        int dev = 0, sms = 0;
+        int rc = cuda_ok(cudaGetDevice(&dev));
+        if (rc == SG_OK) rc = cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        if (rc != SG_OK) return rc;
+        const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);
+        auto go = [&](auto kern) -> int {
+            int r = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            if (r != SG_OK) return r;
+            kern<<<grid, LAT3_TPB, smem, st>>>(job, tab, ntiles);
+            return SG_OK;
+        };
+        switch (dt) {
+            case SG_DT_BF16: rc = go(k_quant_lat3<T, SG_DT_BF16, IMX>); break;
+            case SG_DT_F16:  rc = go(k_quant_lat3<T, SG_DT_F16, IMX>); break;
+            case SG_DT_F32:  rc = go(k_quant_lat3<T, SG_DT_F32, IMX>); break;
+            default: return SG_ERR_ARG;
+        }
+        if (rc != SG_OK) return rc;
+    }
+    return cuda_ok(cudaGetLastError());
+}
+template <class T, bool IMX>
 static int launch_iq4(const Job& job, int dt, cudaStream_t st) {
     const long long threads = job.nslabs * T::LANES;
     const unsigned grid = (unsigned)((threads + 127) / 128);
@@ -905,11 +1098,11 @@ static int dispatch_iq(int type, int variant, bool imx, int device, const Job& j
     if (!tp) return SG_ERR_TABLES;
     const IqTables& tabs = *tp;
     switch (type) {
-        case SG_IQ2_XXS: return imx ? launch_iq<Lattice<SG_IQ2_XXS>, true>(job, dt, st, tabs) : SG_ERR_IMATRIX;
-        case SG_IQ2_XS:  return imx ? launch_iq<Lattice<SG_IQ2_XS>, true>(job, dt, st, tabs) : SG_ERR_IMATRIX;
-        case SG_IQ2_S:   return imx ? launch_iq<Lattice<SG_IQ2_S>, true>(job, dt, st, tabs) : launch_iq<Lattice<SG_IQ2_S>, false>(job, dt, st, tabs);
-        case SG_IQ3_XXS: return imx ? launch_iq<Lattice<SG_IQ3_XXS>, true>(job, dt, st, tabs) : launch_iq<Lattice<SG_IQ3_XXS>, false>(job, dt, st, tabs);
-        case SG_IQ3_S:   return imx ? launch_iq<Lattice<SG_IQ3_S>, true>(job, dt, st, tabs) : launch_iq<Lattice<SG_IQ3_S>, false>(job, dt, st, tabs);
+        case SG_IQ2_XXS: return imx ? launch_lat<Lattice<SG_IQ2_XXS>, true>(job, dt, st, tabs) : SG_ERR_IMATRIX;
+        case SG_IQ2_XS:  return imx ? launch_lat<Lattice<SG_IQ2_XS>, true>(job, dt, st, tabs) : SG_ERR_IMATRIX;
+        case SG_IQ2_S:   return imx ? launch_lat<Lattice<SG_IQ2_S>, true>(job, dt, st, tabs) : launch_lat<Lattice<SG_IQ2_S>, false>(job, dt, st, tabs);
+        case SG_IQ3_XXS: return imx ? launch_lat<Lattice<SG_IQ3_XXS>, true>(job, dt, st, tabs) : launch_lat<Lattice<SG_IQ3_XXS>, false>(job, dt, st, tabs);
+        case SG_IQ3_S:   return imx ? launch_lat<Lattice<SG_IQ3_S>, true>(job, dt, st, tabs) : launch_lat<Lattice<SG_IQ3_S>, false>(job, dt, st, tabs);
         case SG_IQ1_S:   return imx ? launch_iq<IQ1<false, 0>, true>(job, dt, st, tabs) : SG_ERR_IMATRIX;
         case SG_IQ1_M:
             if (variant == 1) return imx ? launch_iq<IQ1<true, 1>, true>(job, dt, st, tabs) : launch_iq<IQ1<true, 1>, false>(job, dt, st, tabs);

@@ -150,11 +150,22 @@ extern "C" int sg_tables_install(int device, void* stream) {
     const HostTable* h = host_tables();
     cudaStream_t st = (cudaStream_t)stream;
     // one allocation holds every table, each part 256-byte aligned
-    size_t off = 0, offs[6][4];
+    // part 4: the neighbour lists once more with every point index replaced by the point's packed levels (what a
+    // search needs to measure a distance, and what it returns), padded so that vector reads may overrun a list
+    constexpr size_t NBK_PAD = 64;
+    size_t off = 0, offs[6][5];
+    std::vector<uint16_t> nbk[6];
     for (int i = 0; i < 6; ++i) {
-        const size_t sz[4] = {h[i].dim == 8 ? h[i].grid64.size() * 8 : h[i].grid32.size() * 4, h[i].map.size() * 4, h[i].nb.size() * 2,
-                              (size_t)SPEC[i].n * 2};
-        for (int k = 0; k < 4; ++k) { offs[i][k] = off; off += (sz[k] + 255) / 256 * 256; }
+        nbk[i].assign(h[i].nb.size() + NBK_PAD, 0);
+        for (size_t pos = 0; pos < h[i].nb.size();) {
+            const size_t n = h[i].nb[pos];
+            nbk[i][pos] = (uint16_t)n;
+            for (size_t j = 1; j <= n; ++j) nbk[i][pos + j] = SPEC[i].packed[h[i].nb[pos + j]];
+            pos += n + 1;
+        }
+        const size_t sz[5] = {h[i].dim == 8 ? h[i].grid64.size() * 8 : h[i].grid32.size() * 4, h[i].map.size() * 4, h[i].nb.size() * 2,
+                              (size_t)SPEC[i].n * 2, nbk[i].size() * 2};
+        for (int k = 0; k < 5; ++k) { offs[i][k] = off; off += (sz[k] + 255) / 256 * 256; }
     }
     uint8_t* base = nullptr;
     rc = cuda_ok(cudaMalloc(&base, off));
@@ -166,10 +177,15 @@ extern "C" int sg_tables_install(int device, void* stream) {
         for (int k = 0; k < 3 && rc == SG_OK; ++k)
             rc = cuda_ok(cudaMemcpyAsync(base + offs[i][k], src[k], sz[k], cudaMemcpyHostToDevice, st));
         if (rc == SG_OK) rc = cuda_ok(cudaMemcpyAsync(base + offs[i][3], SPEC[i].packed, (size_t)SPEC[i].n * 2, cudaMemcpyHostToDevice, st));
+        if (rc == SG_OK) rc = cuda_ok(cudaMemcpyAsync(base + offs[i][4], nbk[i].data(), nbk[i].size() * 2, cudaMemcpyHostToDevice, st));
         g_keys[device][i] = (const uint16_t*)(base + offs[i][3]);
+        t->t[i].nbkeys = (const uint16_t*)(base + offs[i][4]);
+        t->t[i].nb_size = (int)h[i].nb.size();
+        t->t[i].map_size = SPEC[i].map_size;
         t->t[i].grid = base + offs[i][0];
         t->t[i].map = (const int*)(base + offs[i][1]);
         t->t[i].neighbours = (const uint16_t*)(base + offs[i][2]);
+        t->t[i].keys = g_keys[device][i];
     }
     if (rc == SG_OK) rc = cuda_ok(cudaStreamSynchronize(st));
     if (rc != SG_OK) { cudaFree(base); delete t; for (int i = 0; i < 6; ++i) g_keys[device][i] = nullptr; return rc; }
