@@ -174,9 +174,9 @@ template <bool XS> struct IQ4 {
 // Lattice types.  Values that are indexed dynamically live in shared memory as [element][thread]; TPB is the
 // CTA size of the kernel that owns the storage.
 template <int BLK, int TPB, int NTAB> struct IqSmem {
+    alignas(128) float2 ptab[NTAB][4][16];   // per lane group: distance terms of the list being searched (cooperative search)
     float xval[BLK][TPB];         // sign-folded values
     float waux[BLK][TPB];         // sqrt(weight): the weights of the neighbour search
-    float tab[NTAB][32];          // per lane group: distance terms of the list being searched (cooperative search)
 };
 
 // codes of up to 8 groups, 16 bits per group (the group's map index u)
@@ -196,7 +196,7 @@ struct Codes {
 template <int TYPE> struct Lat;
 template <> struct Lat<SG_IQ2_XXS> { static constexpr int W = 16, BLK = 32, G = 8, CB = 2, KMAXQ = 3, TAB = 0, BS = 66, IS0 = -6, IS1 = 6; static constexpr bool PARITY = true; };
 template <> struct Lat<SG_IQ2_XS>  { static constexpr int W = 16, BLK = 16, G = 8, CB = 2, KMAXQ = 3, TAB = 1, BS = 74, IS0 = -9, IS1 = 9; static constexpr bool PARITY = true; };
-template <> struct Lat<SG_IQ2_S>   { static constexpr int W = 8, BLK = 16, G = 8, CB = 2, KMAXQ = 3, TAB = 3, BS = 82, IS0 = -9, IS1 = 9; static constexpr bool PARITY = false; };
+template <> struct Lat<SG_IQ2_S>   { static constexpr int W = 16, BLK = 16, G = 8, CB = 2, KMAXQ = 3, TAB = 3, BS = 82, IS0 = -9, IS1 = 9; static constexpr bool PARITY = false; };
 template <> struct Lat<SG_IQ3_XXS> { static constexpr int W = 0, BLK = 32, G = 4, CB = 3, KMAXQ = 8, TAB = 4, BS = 98, IS0 = -15, IS1 = 15; static constexpr bool PARITY = true; };
 template <> struct Lat<SG_IQ3_S>   { static constexpr int W = 0, BLK = 32, G = 4, CB = 3, KMAXQ = 8, TAB = 5, BS = 110, IS0 = -9, IS1 = 9; static constexpr bool PARITY = false; };
 
@@ -207,6 +207,17 @@ template <class MapT> struct TabView {
     const uint16_t* nbk;
     unsigned key0;               // levels of point 0: what a search that found nothing falls back to
 };
+
+// Work queue of a CTA whose lanes search their own lists (W == 0): the off-lattice groups of all blocks of the CTA
+// for one candidate scale, sorted by list length class so that the lanes of a warp walk lists of equal length.
+template <int TPB> struct QueueSmem {
+    uint16_t u[8][TPB];           // codes of every block's groups for the current candidate
+    uint16_t rank[8][TPB];        // class << 12 | position inside the class, 0xffff = nothing to search
+    uint16_t item[8 * TPB];       // sorted queue: thread << 3 | group
+    float scale[TPB];             // the candidate scale of each block
+    int count[16], base[16], total;
+};
+struct NoQueue {};
 
 // exact float of a small non-negative integer without the conversion pipe: 0x4b000000 is 8388608.0f
 SG_DEVINL float small_to_float(unsigned v) { return fsub(__int_as_float(0x4b000000u | v), 8388608.f); }
@@ -260,64 +271,127 @@ SG_DEVINL unsigned own_neighbour(const TabView<MapT>& t, int list, float scale, 
 // column of shared memory.  With three levels per weight the 24 possible terms w * (scale * q - x)^2 are tabulated
 // once per list; a distance is then 8 dependent adds of looked-up terms, in index order as in the C code.
 // Returns u, replaced for owners by the chosen point's packed levels.
+template <int W> struct ListFetch {
+    const uint16_t* nb;
+    int n, o;
+    float scale;
+    bool has;
+    unsigned k[4];                // entries sub, sub + W, sub + 2W, sub + 3W, read before n is known
+};
+// next list of the lane group: pop its owner from `mine`, fetch the owner's list id and scale, start the loads
+template <int W>
+SG_DEVINL ListFetch<W> fetch_list(const uint16_t* nbk, unsigned& mine, int list, float scale, int gbase, int sub) {
+    ListFetch<W> f;
+    f.has = mine != 0;
+    f.o = f.has ? __ffs(mine) - 1 : 0;
+    mine &= mine - 1;
+    const int olist = __shfl_sync(SG_FULL, list, gbase + f.o);
+    f.scale = __shfl_sync(SG_FULL, scale, gbase + f.o);
+    f.nb = nbk + (f.has ? olist : 0);
+    f.n = f.has ? (int)__ldg(f.nb) : 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) f.k[q] = __ldg(f.nb + 1 + sub + q * W);
+    return f;
+}
+
+// order-preserving image of a float in the unsigned integers (for integer min reductions)
+SG_DEVINL unsigned float_order(float f) {
+    const unsigned b = __float_as_uint(f);
+    return b ^ ((unsigned)((int)b >> 31) | 0x80000000u);
+}
+
+// d += the two terms of weight pair P of the point `key`, looked up in the lane group's table at shared address pbase
+template <int P> SG_DEVINL void pair_terms(unsigned pbase, unsigned key, float& d) {
+    const unsigned a = pbase | ((P == 0 ? key << 3 : key >> (4 * P - 3)) & 0x78u);
+    float t0, t1;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2+%3];" : "=f"(t0), "=f"(t1) : "r"(a), "n"(128 * P) : "memory");
+    d = fadd(fadd(d, t0), t1);
+}
+
+// Cooperative search, continued.  The tabulated terms are stored in pairs: entry [p][c0 + 4 c1] holds the terms of
+// weights 2p and 2p + 1 at levels c0 and c1, so one 8-byte load indexed by a nibble of the key brings two terms
+// and a distance costs four loads and eight adds (added in index order: t0, t1, ... t7).
 template <int W, int BLK, int TPB, int NTAB>
 SG_DEVINL unsigned coop_neighbour(const TabView<int>& t, bool off, int list, float scale, unsigned u, int e0, IqSmem<BLK, TPB, NTAB>& sm, int* status) {
     const int lane = threadIdx.x & 31, sub = lane & (W - 1), gbase = lane & ~(W - 1);
     const int col0 = threadIdx.x & ~31;
-    float* tab = sm.tab[threadIdx.x / W];
-    const int rot = W == 16 ? ((threadIdx.x / W) & 1) * 16 : 0;      // the two lane groups of a warp use disjoint banks
+    const unsigned gmask = W == 32 ? SG_FULL : (((1u << W) - 1) << gbase);
+    float2 (*ptab)[16] = sm.ptab[threadIdx.x / W];
+    const unsigned pbase = (unsigned)__cvta_generic_to_shared(ptab);
     unsigned mine = (__ballot_sync(SG_FULL, off) >> gbase) & ((1u << W) - 1);
-    while (__any_sync(SG_FULL, mine != 0)) {
-        const bool has = mine != 0;
-        const int o = has ? __ffs(mine) - 1 : 0;
-        mine &= mine - 1;
-        const int src = gbase + o;
-        const int olist = __shfl_sync(SG_FULL, list, src);
-        const float osc = __shfl_sync(SG_FULL, scale, src);
-        const int col = col0 + src;
-        const uint16_t* nb = t.nbk + (has ? olist : 0);
-        const int n = has ? (int)__ldg(nb) : 0;
-        unsigned k0 = __ldg(nb + 1 + sub), k1 = __ldg(nb + 1 + sub + W);       // first entries, before n is known
+    if (!__any_sync(SG_FULL, mine != 0)) return u;
+    ListFetch<W> cur = fetch_list<W>(t.nbk, mine, list, scale, gbase, sub);
+    while (true) {
+        // the next list's loads are in flight while this one is searched
+        const bool more = __any_sync(SG_FULL, mine != 0);
+        ListFetch<W> nxt;
+        if (more) nxt = fetch_list<W>(t.nbk, mine, list, scale, gbase, sub);
         {
+            const int col = col0 + gbase + cur.o;
+            const float s3 = fmul(cur.scale, 3.f), s5 = fmul(cur.scale, 5.f);
+            auto term = [&](float x, float w, float sq) { const float d = fsub(sq, x); return fmul(fmul(w, d), d); };
             __syncwarp();
-            const int i = sub & 7;
-            const float x = sm.xval[e0 + i][col], w = sm.waux[e0 + i][col];
-            if (W == 8 || sub < 8) {
-                const float d0 = fsub(osc, x), d1 = fsub(fmul(osc, 3.f), x);
-                tab[(4 * i + rot) & 31] = fmul(fmul(w, d0), d0);
-                tab[(4 * i + 1 + rot) & 31] = fmul(fmul(w, d1), d1);
-            }
-            if (W == 8 || sub >= 8) {
-                const float d2 = fsub(fmul(osc, 5.f), x);
-                tab[(4 * i + 2 + rot) & 31] = fmul(fmul(w, d2), d2);
+            if (W == 16) {
+                // lane (p, c0): the term of weight 2p at level c0 against the three terms of weight 2p + 1
+                const int pr = sub >> 2, c0 = sub & 3;
+                const float xa = sm.xval[e0 + 2 * pr][col], wa = sm.waux[e0 + 2 * pr][col];
+                const float xb = sm.xval[e0 + 2 * pr + 1][col], wb = sm.waux[e0 + 2 * pr + 1][col];
+                const float ta = term(xa, wa, c0 == 0 ? cur.scale : c0 == 1 ? s3 : s5);
+                ptab[pr][c0] = make_float2(ta, term(xb, wb, cur.scale));
+                ptab[pr][c0 + 4] = make_float2(ta, term(xb, wb, s3));
+                ptab[pr][c0 + 8] = make_float2(ta, term(xb, wb, s5));
+            } else {
+                // lane (p, h): h = 0 writes the entries with c0 = 0, 1, h = 1 those with c0 = 2
+                const int pr = sub >> 1, h = sub & 1;
+                const float xa = sm.xval[e0 + 2 * pr][col], wa = sm.waux[e0 + 2 * pr][col];
+                const float xb = sm.xval[e0 + 2 * pr + 1][col], wb = sm.waux[e0 + 2 * pr + 1][col];
+                const float b0 = term(xb, wb, cur.scale), b1 = term(xb, wb, s3), b2 = term(xb, wb, s5);
+                const float a0 = term(xa, wa, h ? s5 : cur.scale);
+                const int c0 = h ? 2 : 0;
+                ptab[pr][c0] = make_float2(a0, b0); ptab[pr][c0 + 4] = make_float2(a0, b1); ptab[pr][c0 + 8] = make_float2(a0, b2);
+                if (!h) {
+                    const float a1 = term(xa, wa, s3);
+                    ptab[pr][1] = make_float2(a1, b0); ptab[pr][5] = make_float2(a1, b1); ptab[pr][9] = make_float2(a1, b2);
+                }
             }
             __syncwarp();
         }
+        const int n = cur.n;
         const int nmax = (int)__reduce_max_sync(SG_FULL, (unsigned)n);
         float best = 3.402823466e+38F;
         int bj = 0x7fffffff;
+        auto dist = [&](unsigned key) {
+            float d = 0.f;
+            pair_terms<0>(pbase, key, d); pair_terms<1>(pbase, key, d); pair_terms<2>(pbase, key, d); pair_terms<3>(pbase, key, d);
+            return d;
+        };
+        {
+            const float da = dist(cur.k[0]), db = dist(cur.k[1]);
+            if (sub < n && da < best) { best = da; bj = sub; }
+            if (sub + W < n && db < best) { best = db; bj = sub + W; }
+        }
+        if (nmax > 2 * W) {
+            const float da = dist(cur.k[2]), db = dist(cur.k[3]);
+            if (sub + 2 * W < n && da < best) { best = da; bj = sub + 2 * W; }
+            if (sub + 3 * W < n && db < best) { best = db; bj = sub + 3 * W; }
 #pragma unroll 1
-        for (int j = sub; j < nmax; j += 2 * W) {
-            float da = 0.f, db = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                da = fadd(da, tab[(4 * i + (int)((k0 >> (2 * i)) & 3u) + rot) & 31]);
-                db = fadd(db, tab[(4 * i + (int)((k1 >> (2 * i)) & 3u) + rot) & 31]);
+            for (int j = sub + 4 * W; j < nmax; j += 2 * W) {
+                const unsigned k0 = j < n ? __ldg(cur.nb + 1 + j) : 0u, k1 = j + W < n ? __ldg(cur.nb + 1 + j + W) : 0u;
+                const float ea = dist(k0), eb = dist(k1);
+                if (j < n && ea < best) { best = ea; bj = j; }
+                if (j + W < n && eb < best) { best = eb; bj = j + W; }
             }
-            if (j < n && da < best) { best = da; bj = j; }
-            if (j + W < n && db < best) { best = db; bj = j + W; }
-            if (j + 2 * W < nmax) { k0 = __ldg(nb + 1 + j + 2 * W); k1 = __ldg(nb + 1 + j + 3 * W); }
         }
-#pragma unroll
-        for (int s = W / 2; s > 0; s >>= 1) {
-            const float ob = __shfl_xor_sync(SG_FULL, best, s);
-            const int oj = __shfl_xor_sync(SG_FULL, bj, s);
-            if (ob < best || (ob == best && oj < bj)) { best = ob; bj = oj; }
-        }
-        if (has && sub == o) {
+        // smallest distance of the lane group, earliest entry among equals
+        const unsigned mb = float_order(fadd(best, 0.f));
+        const unsigned m = __reduce_min_sync(gmask, mb);
+        bj = (int)__reduce_min_sync(gmask, mb == m ? (unsigned)bj : 0x7fffffffu);
+        if (cur.has && sub == cur.o) {
             if (bj == 0x7fffffff) { atomicOr(status, SG_ST_OFFGRID); u = t.key0; }
-            else u = __ldg(nb + 1 + bj);
+            else u = __ldg(cur.nb + 1 + bj);
         }
+        if (!more) break;
+        cur = nxt;
     }
     return u;
 }
@@ -354,8 +428,67 @@ template <int TYPE> struct Lattice {
         else return coop_neighbour<W>(T, off, list, scale, u, e0, sm, status);
     }
 
-    template <int DT, bool IMX, class SM>
-    static SG_DEVINL void run(const Job& job, const Slab& sl, int sub, bool valid, const View& T, SM& sm) {
+    // One candidate scale for every block of the CTA (W == 0): all groups are rounded and looked up; those that fell
+    // off the lattice and are wanted (`want`, one bit per group) go into the CTA's queue ordered by list length
+    // (longest first), the CTA's threads search the queue side by side, and each thread reads its block's codes back.
+    template <class SM, class Q>
+    static SG_DEVINL void queue_round(const View& T, const SM& sm, Q& q, float id, float sc, unsigned want, Codes& aux, unsigned& og, int* status) {
+        const int tid = threadIdx.x, lane = tid & 31, tpb = blockDim.x;
+        q.scale[tid] = sc;
+        og = 0;
+#pragma unroll 1
+        for (int k = 0; k < NG; ++k) {
+            unsigned u = 0;
+#pragma unroll
+            for (int i = 0; i < G; ++i) {
+                const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
+                u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
+            }
+            const int gi = T.map[u];
+            q.u[k][tid] = (uint16_t)u;
+            if (gi >= 0) og |= 1u << k;
+            const bool off = ((want >> k) & 1) && gi < 0;
+            int cls = -1;
+            if (off) { cls = ((int)T.nbk[-gi - 1] + 3) >> 2; cls = cls > 15 ? 15 : cls; }
+            const unsigned peers = __match_any_sync(SG_FULL, cls);
+            unsigned r = 0xffffu;
+            if (off) {
+                const int leader = __ffs(peers) - 1;
+                int b = 0;
+                if (lane == leader) b = atomicAdd(&q.count[cls], __popc(peers));
+                b = __shfl_sync(peers, b, leader);
+                r = (unsigned)cls << 12 | (unsigned)(b + __popc(peers & ((1u << lane) - 1)));
+            }
+            q.rank[k][tid] = (uint16_t)r;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int acc = 0;
+            for (int c = 15; c >= 0; --c) { q.base[c] = acc; acc += q.count[c]; q.count[c] = 0; }
+            q.total = acc;
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int k = 0; k < NG; ++k) {
+            const unsigned r = q.rank[k][tid];
+            if (r != 0xffffu) q.item[q.base[r >> 12] + (int)(r & 4095u)] = (uint16_t)(tid << 3 | k);
+        }
+        __syncthreads();
+        const int total = q.total;
+#pragma unroll 1
+        for (int p = tid; p < total; p += tpb) {
+            const unsigned it = q.item[p];
+            const int t2 = (int)(it >> 3), k = (int)(it & 7);
+            const int list = -(int)T.map[q.u[k][t2]] - 1;
+            q.u[k][t2] = (uint16_t)own_neighbour<G, CB>(T, list, q.scale[t2], G * k, sm, t2, status);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < NG; ++k) aux.set(k, q.u[k][tid]);
+    }
+
+    template <int DT, bool IMX, class SM, class Q>
+    static SG_DEVINL void run(const Job& job, const Slab& sl, int sub, bool valid, const View& T, SM& sm, Q& q) {
         const int tid = threadIdx.x;
         float wgt[BLK];
         float scale = 0.f;                 // scales[ib]
@@ -446,18 +579,42 @@ template <int TYPE> struct Lattice {
                 const float this_scale = frcp(id);
                 Codes aux;
                 unsigned og = 0;
-#pragma unroll 1
-                for (int k = 0; k < NG; ++k) {
-                    unsigned u = 0;
+                if constexpr (W == 0) {
+                    queue_round(T, sm, q, id, this_scale, act ? 0xffu : 0u, aux, og, job.status);
+                } else if constexpr (NG <= 2) {
+                    // all map lookups of the block first (they miss L1 often), then the searches
+                    unsigned uk[NG];
+                    int gk[NG];
 #pragma unroll
-                    for (int i = 0; i < G; ++i) {
-                        const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
-                        u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
+                    for (int k = 0; k < NG; ++k) {
+                        unsigned u = 0;
+#pragma unroll
+                        for (int i = 0; i < G; ++i) {
+                            const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
+                            u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
+                        }
+                        uk[k] = u;
+                        gk[k] = __ldg(T.map + u);
                     }
-                    const int gi = T.map[u];
-                    if (gi >= 0) og |= 1u << k;
-                    u = search(T, act && gi < 0, -gi - 1, this_scale, u, G * k, sm, job.status);
-                    aux.set(k, u);
+#pragma unroll
+                    for (int k = 0; k < NG; ++k) {
+                        if (gk[k] >= 0) og |= 1u << k;
+                        aux.set(k, search(T, act && gk[k] < 0, -gk[k] - 1, this_scale, uk[k], G * k, sm, job.status));
+                    }
+                } else {
+#pragma unroll 1
+                    for (int k = 0; k < NG; ++k) {
+                        unsigned u = 0;
+#pragma unroll
+                        for (int i = 0; i < G; ++i) {
+                            const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
+                            u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
+                        }
+                        const int gi = T.map[u];
+                        if (gi >= 0) og |= 1u << k;
+                        u = search(T, act && gi < 0, -gi - 1, this_scale, u, G * k, sm, job.status);
+                        aux.set(k, u);
+                    }
                 }
                 float sumqx, sumq2;
                 block_sums<BLK, G, CB>(aux, wgt, sm, tid, sumqx, sumq2);
@@ -473,7 +630,22 @@ template <int TYPE> struct Lattice {
                 const unsigned all = (1u << NG) - 1;
                 refit = act && (ongrid & all) != all && scale > 0.f;
             }
-            if (__any_sync(SG_FULL, refit)) {
+            if constexpr (W == 0) {
+                if (__syncthreads_or(refit)) {
+                    unsigned want = 0;
+                    if (refit) want = TYPE == SG_IQ3_XXS ? ~ongrid & 0xffu : 0xffu;
+                    Codes aux;
+                    unsigned og;
+                    queue_round(T, sm, q, frcp(scale), scale, want, aux, og, job.status);
+#pragma unroll
+                    for (int k = 0; k < NG; ++k) if ((want >> k) & 1) L.set(k, aux.get(k));
+                    if (refit) {
+                        float sumqx, sumq2;
+                        block_sums<BLK, G, CB>(L, wgt, sm, tid, sumqx, sumq2);
+                        if (sumq2 > 0.f) scale = fdiv(sumqx, sumq2);
+                    }
+                }
+            } else if (__any_sync(SG_FULL, refit)) {
                 const float id = frcp(scale);
 #pragma unroll 1
                 for (int k = 0; k < NG; ++k) {
@@ -979,7 +1151,8 @@ __global__ void __launch_bounds__(IQ_TPB) k_quant_lat(const __grid_constant__ Jo
     const Slab sl = locate<T::SLAB>(job, s);
     typename T::View view;
     view.map = tab.map; view.nbk = tab.nbkeys; view.key0 = __ldg(tab.keys);
-    T::template run<DT, IMX>(job, sl, sub, valid, view, sm);
+    NoQueue nq;
+    T::template run<DT, IMX>(job, sl, sub, valid, view, sm, nq);
 }
 
 // IQ3_XXS / IQ3_S: their tables are small (map 4096 entries, lists < 29 K entries), so each CTA copies them into
@@ -987,15 +1160,17 @@ __global__ void __launch_bounds__(IQ_TPB) k_quant_lat(const __grid_constant__ Jo
 constexpr int LAT3_TPB = 512;
 template <class T> struct Lat3Smem {
     IqSmem<T::BLK, LAT3_TPB, 1> v;
+    QueueSmem<LAT3_TPB> q;
     int16_t map[4096];
     uint16_t nbk[1];              // nb_size + 64 entries follow
 };
 template <class T, int DT, bool IMX>
 __global__ void __launch_bounds__(LAT3_TPB) k_quant_lat3(const __grid_constant__ Job job, const __grid_constant__ GridTable tab, long long ntiles) {
-    extern __shared__ __align__(16) unsigned char raw[];
+    extern __shared__ __align__(128) unsigned char raw[];
     Lat3Smem<T>& sm = *reinterpret_cast<Lat3Smem<T>*>(raw);
     for (int i = threadIdx.x; i < 4096; i += LAT3_TPB) sm.map[i] = (int16_t)__ldg(tab.map + i);
     for (int i = threadIdx.x; i < tab.nb_size + 64; i += LAT3_TPB) sm.nbk[i] = __ldg(tab.nbkeys + i);
+    if (threadIdx.x < 16) sm.q.count[threadIdx.x] = 0;
     __syncthreads();
     typename T::View view;
     view.map = sm.map; view.nbk = sm.nbk; view.key0 = __ldg(tab.keys);
@@ -1007,7 +1182,7 @@ __global__ void __launch_bounds__(LAT3_TPB) k_quant_lat3(const __grid_constant__
         const bool valid = s < job.nslabs;
         if (!valid) s = job.nslabs - 1;
         const Slab sl = locate<T::SLAB>(job, s);
-        T::template run<DT, IMX>(job, sl, sub, valid, view, sm.v);
+        T::template run<DT, IMX>(job, sl, sub, valid, view, sm.v, sm.q);
     }
 }
 
