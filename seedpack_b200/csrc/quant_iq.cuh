@@ -173,10 +173,10 @@ template <bool XS> struct IQ4 {
 // ==================================================================================================
 // Lattice types.  Values that are indexed dynamically live in shared memory as [element][thread]; TPB is the
 // CTA size of the kernel that owns the storage.
-template <int BLK, int TPB, int NTAB> struct IqSmem {
-    alignas(128) float2 ptab[NTAB][4][16];   // per lane group: distance terms of the list being searched (cooperative search)
+template <int BLK, int TPB, int NTERM> struct IqSmem {
     float xval[BLK][TPB];         // sign-folded values
     float waux[BLK][TPB];         // sqrt(weight): the weights of the neighbour search
+    float term[NTERM][TPB];       // three-level lattices: the list walker's distance terms, [4 * weight + level]
 };
 
 // codes of up to 8 groups, 16 bits per group (the group's map index u)
@@ -191,61 +191,89 @@ struct Codes {
     }
 };
 
-// TYPE-specific constants of the five lattice quantisers.  W: lanes that share one neighbour list in the
-// cooperative search (0 = every lane walks its own lists, tables in shared memory).
+// TYPE-specific constants of the five lattice quantisers
 template <int TYPE> struct Lat;
-template <> struct Lat<SG_IQ2_XXS> { static constexpr int W = 16, BLK = 32, G = 8, CB = 2, KMAXQ = 3, TAB = 0, BS = 66, IS0 = -6, IS1 = 6; static constexpr bool PARITY = true; };
-template <> struct Lat<SG_IQ2_XS>  { static constexpr int W = 16, BLK = 16, G = 8, CB = 2, KMAXQ = 3, TAB = 1, BS = 74, IS0 = -9, IS1 = 9; static constexpr bool PARITY = true; };
-template <> struct Lat<SG_IQ2_S>   { static constexpr int W = 16, BLK = 16, G = 8, CB = 2, KMAXQ = 3, TAB = 3, BS = 82, IS0 = -9, IS1 = 9; static constexpr bool PARITY = false; };
-template <> struct Lat<SG_IQ3_XXS> { static constexpr int W = 0, BLK = 32, G = 4, CB = 3, KMAXQ = 8, TAB = 4, BS = 98, IS0 = -15, IS1 = 15; static constexpr bool PARITY = true; };
-template <> struct Lat<SG_IQ3_S>   { static constexpr int W = 0, BLK = 32, G = 4, CB = 3, KMAXQ = 8, TAB = 5, BS = 110, IS0 = -9, IS1 = 9; static constexpr bool PARITY = false; };
+template <> struct Lat<SG_IQ2_XXS> { static constexpr int BLK = 32, G = 8, CB = 2, KMAXQ = 3, TAB = 0, BS = 66, IS0 = -6, IS1 = 6; static constexpr bool PARITY = true; };
+template <> struct Lat<SG_IQ2_XS>  { static constexpr int BLK = 16, G = 8, CB = 2, KMAXQ = 3, TAB = 1, BS = 74, IS0 = -9, IS1 = 9; static constexpr bool PARITY = true; };
+template <> struct Lat<SG_IQ2_S>   { static constexpr int BLK = 16, G = 8, CB = 2, KMAXQ = 3, TAB = 3, BS = 82, IS0 = -9, IS1 = 9; static constexpr bool PARITY = false; };
+template <> struct Lat<SG_IQ3_XXS> { static constexpr int BLK = 32, G = 4, CB = 3, KMAXQ = 8, TAB = 4, BS = 98, IS0 = -15, IS1 = 15; static constexpr bool PARITY = true; };
+template <> struct Lat<SG_IQ3_S>   { static constexpr int BLK = 32, G = 4, CB = 3, KMAXQ = 8, TAB = 5, BS = 110, IS0 = -9, IS1 = 9; static constexpr bool PARITY = false; };
 
-// what a search reads: tuple -> point index or list, and the lists themselves.  MapT is int (tables in global
-// memory) or int16_t (the IQ3 tables copied into shared memory; their offsets fit 15 bits).
+// what a search reads: tuple -> point index or list, and the lists themselves (keys in place of point indices).
+// MapT is int (tables in global memory) or int16_t (the IQ3 tables copied into shared memory; their offsets fit).
 template <class MapT> struct TabView {
     const MapT* map;
     const uint16_t* nbk;
     unsigned key0;               // levels of point 0: what a search that found nothing falls back to
 };
 
-// Work queue of a CTA whose lanes search their own lists (W == 0): the off-lattice groups of all blocks of the CTA
-// for one candidate scale, sorted by list length class so that the lanes of a warp walk lists of equal length.
-template <int TPB> struct QueueSmem {
-    uint16_t u[8][TPB];           // codes of every block's groups for the current candidate
-    uint16_t rank[8][TPB];        // class << 12 | position inside the class, 0xffff = nothing to search
-    uint16_t item[8 * TPB];       // sorted queue: thread << 3 | group
-    float scale[TPB];             // the candidate scale of each block
-    int count[16], base[16], total;
+// Work queue of a CTA.  Neighbour lists run from one entry to a few hundred, so a warp whose lanes each walked the
+// list of their own block would wait for its longest list.  Instead every thread registers the groups of its block
+// that fell off the lattice, the queue is ordered by list length (a counting sort over length classes, longest
+// first), and the CTA's threads then take queue entries side by side: the lanes of a warp walk lists of equal
+// length, whichever blocks they belong to.  Results go back through u[][].
+constexpr int ilog2_ce(int v) { return v <= 1 ? 0 : 1 + ilog2_ce(v / 2); }
+template <int TPB, int NG> struct WorkQueue {
+    static constexpr int RANK_BITS = ilog2_ce(TPB * NG), CLS_BITS = 16 - RANK_BITS;
+    static constexpr int NCLS = CLS_BITS >= 5 ? 32 : (1 << CLS_BITS);
+    uint16_t u[NG][TPB];          // codes of every block's groups
+    uint16_t rank[NG][TPB];       // class << RANK_BITS | position inside the class; 0xffff = nothing to search
+    uint16_t item[NG * TPB];      // the ordered queue: thread * NG + group
+    float scale[TPB];             // the scale each block is searched at
+    int count[32], base[32], total;
+
+    // every lane of the warp calls this once per group k; off: the group needs a search of a list of n entries,
+    // lists of up to 2^cshift entries more or less count as equally long
+    SG_DEVINL void put(int k, unsigned codes, bool off, int n, int cshift) {
+        const int tid = threadIdx.x, lane = tid & 31;
+        u[k][tid] = (uint16_t)codes;
+        int cls = -1;
+        if (off) { cls = (n + (1 << cshift) - 1) >> cshift; cls = cls > NCLS - 2 ? NCLS - 2 : cls; }
+        const unsigned peers = __match_any_sync(SG_FULL, cls);
+        unsigned r = 0xffffu;
+        if (off) {
+            const int leader = __ffs(peers) - 1;
+            int b = 0;
+            if (lane == leader) b = atomicAdd(&count[cls], __popc(peers));
+            b = __shfl_sync(peers, b, leader);
+            r = (unsigned)cls << RANK_BITS | (unsigned)(b + __popc(peers & ((1u << lane) - 1)));
+        }
+        rank[k][tid] = (uint16_t)r;
+    }
+    // all threads of the CTA, after their puts: orders the queue, returns its length
+    SG_DEVINL int sort() {
+        const int tid = threadIdx.x;
+        __syncthreads();
+        if (tid == 0) {
+            int acc = 0;
+            for (int c = NCLS - 1; c >= 0; --c) { base[c] = acc; acc += count[c]; count[c] = 0; }
+            total = acc;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < NG; ++k) {
+            const unsigned r = rank[k][tid];
+            if (r != 0xffffu) item[base[r >> RANK_BITS] + (int)(r & ((1u << RANK_BITS) - 1))] = (uint16_t)(tid * NG + k);
+        }
+        __syncthreads();
+        return total;
+    }
 };
-struct NoQueue {};
 
 // exact float of a small non-negative integer without the conversion pipe: 0x4b000000 is 8388608.0f
 SG_DEVINL float small_to_float(unsigned v) { return fsub(__int_as_float(0x4b000000u | v), 8388608.f); }
 
-// weighted squared distance of the point with packed levels `key` from the G values xv at `scale`, added up in
-// index order as iq2_find_best_neighbour / iq3_find_best_neighbour do (ggml-quants.c:3271-3293, 3915-3937)
-template <int G, int CB>
-SG_DEVINL float point_dist2(unsigned key, float scale, const float (&xv)[G], const float (&wv)[G]) {
-    float d2 = 0.f;
-#pragma unroll
-    for (int i = 0; i < G; ++i) {
-        const float q = small_to_float(2 * ((key >> (CB * i)) & ((1u << CB) - 1)) + 1);
-        const float diff = fsub(fmul(scale, q), xv[i]);
-        d2 = fadd(d2, fmul(fmul(wv[i], diff), diff));
-    }
-    return d2;
-}
-
-// One lane walks one list: four entries at a time (independent distance chains), compared in list order so that
-// the first strictly smaller distance wins as in the C loop.  Reads up to three entries past the list's end,
-// which the padding of the key lists allows.
-template <int G, int CB, int BLK, int TPB, int NTAB, class MapT>
-SG_DEVINL unsigned own_neighbour(const TabView<MapT>& t, int list, float scale, int e0, const IqSmem<BLK, TPB, NTAB>& sm, int tid, int* status) {
-    const uint16_t* nb = t.nbk + list;
+// iq3_find_best_neighbour (ggml-quants.c:3915-3937) over a list of keys in shared memory, for the group of 4 weights
+// of thread column t2 that starts at element e0.  Four entries at a time (independent distance chains, each added
+// up in index order), compared in list order so that the first strictly smaller distance wins as in the C loop.
+// Reads up to three entries past the list's end, which the padding of the key lists allows.
+template <int BLK, int TPB, int NTERM>
+SG_DEVINL unsigned search_list4(const uint16_t* nbk, int list, float scale, int e0, const IqSmem<BLK, TPB, NTERM>& sm, int t2, unsigned key0, int* status) {
+    const uint16_t* nb = nbk + list;
     const int n = nb[0];
-    float xv[G], wv[G];
+    float xv[4], wv[4];
 #pragma unroll
-    for (int i = 0; i < G; ++i) { xv[i] = sm.xval[e0 + i][tid]; wv[i] = sm.waux[e0 + i][tid]; }
+    for (int i = 0; i < 4; ++i) { xv[i] = sm.xval[e0 + i][t2]; wv[i] = sm.waux[e0 + i][t2]; }
     float best = 3.402823466e+38F;
     unsigned bu = 0xffffffffu;
 #pragma unroll 1
@@ -255,145 +283,69 @@ SG_DEVINL unsigned own_neighbour(const TabView<MapT>& t, int list, float scale, 
 #pragma unroll
         for (int q = 0; q < 4; ++q) key[q] = nb[1 + j + q];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) d[q] = point_dist2<G, CB>(key[q], scale, xv, wv);
+        for (int q = 0; q < 4; ++q) {
+            float d2 = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float lv = small_to_float(2 * ((key[q] >> (3 * i)) & 7u) + 1);
+                const float diff = fsub(fmul(scale, lv), xv[i]);
+                d2 = fadd(d2, fmul(fmul(wv[i], diff), diff));
+            }
+            d[q] = d2;
+        }
 #pragma unroll
         for (int q = 0; q < 4; ++q)
             if (j + q < n && d[q] < best) { best = d[q]; bu = key[q]; }
     }
-    if (bu == 0xffffffffu) { atomicOr(status, SG_ST_OFFGRID); bu = t.key0; }
+    if (bu == 0xffffffffu) { atomicOr(status, SG_ST_OFFGRID); bu = key0; }
     return bu;
 }
 
-// The same search for a whole warp at once, for the lattices whose lists run to hundreds of entries.  Each lane may
-// hold one group of 8 weights that fell off the lattice (`off`, neighbour list `list`, candidate `scale`); the W
-// lanes of a lane group take the group's lists one after the other: lane s looks at entries s, s + W, ..., and a
-// butterfly picks the smallest distance, the earliest entry among equals.  The owner's values are read from its
-// column of shared memory.  With three levels per weight the 24 possible terms w * (scale * q - x)^2 are tabulated
-// once per list; a distance is then 8 dependent adds of looked-up terms, in index order as in the C code.
-// Returns u, replaced for owners by the chosen point's packed levels.
-template <int W> struct ListFetch {
-    const uint16_t* nb;
-    int n, o;
-    float scale;
-    bool has;
-    unsigned k[4];                // entries sub, sub + W, sub + 2W, sub + 3W, read before n is known
-};
-// next list of the lane group: pop its owner from `mine`, fetch the owner's list id and scale, start the loads
-template <int W>
-SG_DEVINL ListFetch<W> fetch_list(const uint16_t* nbk, unsigned& mine, int list, float scale, int gbase, int sub) {
-    ListFetch<W> f;
-    f.has = mine != 0;
-    f.o = f.has ? __ffs(mine) - 1 : 0;
-    mine &= mine - 1;
-    const int olist = __shfl_sync(SG_FULL, list, gbase + f.o);
-    f.scale = __shfl_sync(SG_FULL, scale, gbase + f.o);
-    f.nb = nbk + (f.has ? olist : 0);
-    f.n = f.has ? (int)__ldg(f.nb) : 0;
+// iq2_find_best_neighbour (ggml-quants.c:3271-3293) and iq1_find_best_neighbour2 (4444-4499) over a list of keys in
+// global memory, for 8 weights with three levels each.  xs / ws: the group's values and weights, [8][TPB], column
+// t2; sq[c]: scale times the value of level c.  The 24 possible terms w * (sq[c] - x)^2 go into the calling
+// thread's own column of `term` first; a distance is then 8 looked-up terms added in index order.
+template <int TPB>
+SG_DEVINL unsigned search_list8(const uint16_t* __restrict__ nbk, int list, const float (&sq)[3], const float (*xs)[TPB], const float (*ws)[TPB],
+                                int t2, float (*term)[TPB], unsigned key0, int* status) {
+    const int tid = threadIdx.x;
+    const uint16_t* nb = nbk + list;
+    const int n = __ldg(nb);
+    unsigned key[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) f.k[q] = __ldg(f.nb + 1 + sub + q * W);
-    return f;
-}
-
-// order-preserving image of a float in the unsigned integers (for integer min reductions)
-SG_DEVINL unsigned float_order(float f) {
-    const unsigned b = __float_as_uint(f);
-    return b ^ ((unsigned)((int)b >> 31) | 0x80000000u);
-}
-
-// d += the two terms of weight pair P of the point `key`, looked up in the lane group's table at shared address pbase
-template <int P> SG_DEVINL void pair_terms(unsigned pbase, unsigned key, float& d) {
-    const unsigned a = pbase | ((P == 0 ? key << 3 : key >> (4 * P - 3)) & 0x78u);
-    float t0, t1;
-    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2+%3];" : "=f"(t0), "=f"(t1) : "r"(a), "n"(128 * P) : "memory");
-    d = fadd(fadd(d, t0), t1);
-}
-
-// Cooperative search, continued.  The tabulated terms are stored in pairs: entry [p][c0 + 4 c1] holds the terms of
-// weights 2p and 2p + 1 at levels c0 and c1, so one 8-byte load indexed by a nibble of the key brings two terms
-// and a distance costs four loads and eight adds (added in index order: t0, t1, ... t7).
-template <int W, int BLK, int TPB, int NTAB>
-SG_DEVINL unsigned coop_neighbour(const TabView<int>& t, bool off, int list, float scale, unsigned u, int e0, IqSmem<BLK, TPB, NTAB>& sm, int* status) {
-    const int lane = threadIdx.x & 31, sub = lane & (W - 1), gbase = lane & ~(W - 1);
-    const int col0 = threadIdx.x & ~31;
-    const unsigned gmask = W == 32 ? SG_FULL : (((1u << W) - 1) << gbase);
-    float2 (*ptab)[16] = sm.ptab[threadIdx.x / W];
-    const unsigned pbase = (unsigned)__cvta_generic_to_shared(ptab);
-    unsigned mine = (__ballot_sync(SG_FULL, off) >> gbase) & ((1u << W) - 1);
-    if (!__any_sync(SG_FULL, mine != 0)) return u;
-    ListFetch<W> cur = fetch_list<W>(t.nbk, mine, list, scale, gbase, sub);
-    while (true) {
-        // the next list's loads are in flight while this one is searched
-        const bool more = __any_sync(SG_FULL, mine != 0);
-        ListFetch<W> nxt;
-        if (more) nxt = fetch_list<W>(t.nbk, mine, list, scale, gbase, sub);
-        {
-            const int col = col0 + gbase + cur.o;
-            const float s3 = fmul(cur.scale, 3.f), s5 = fmul(cur.scale, 5.f);
-            auto term = [&](float x, float w, float sq) { const float d = fsub(sq, x); return fmul(fmul(w, d), d); };
-            __syncwarp();
-            if (W == 16) {
-                // lane (p, c0): the term of weight 2p at level c0 against the three terms of weight 2p + 1
-                const int pr = sub >> 2, c0 = sub & 3;
-                const float xa = sm.xval[e0 + 2 * pr][col], wa = sm.waux[e0 + 2 * pr][col];
-                const float xb = sm.xval[e0 + 2 * pr + 1][col], wb = sm.waux[e0 + 2 * pr + 1][col];
-                const float ta = term(xa, wa, c0 == 0 ? cur.scale : c0 == 1 ? s3 : s5);
-                ptab[pr][c0] = make_float2(ta, term(xb, wb, cur.scale));
-                ptab[pr][c0 + 4] = make_float2(ta, term(xb, wb, s3));
-                ptab[pr][c0 + 8] = make_float2(ta, term(xb, wb, s5));
-            } else {
-                // lane (p, h): h = 0 writes the entries with c0 = 0, 1, h = 1 those with c0 = 2
-                const int pr = sub >> 1, h = sub & 1;
-                const float xa = sm.xval[e0 + 2 * pr][col], wa = sm.waux[e0 + 2 * pr][col];
-                const float xb = sm.xval[e0 + 2 * pr + 1][col], wb = sm.waux[e0 + 2 * pr + 1][col];
-                const float b0 = term(xb, wb, cur.scale), b1 = term(xb, wb, s3), b2 = term(xb, wb, s5);
-                const float a0 = term(xa, wa, h ? s5 : cur.scale);
-                const int c0 = h ? 2 : 0;
-                ptab[pr][c0] = make_float2(a0, b0); ptab[pr][c0 + 4] = make_float2(a0, b1); ptab[pr][c0 + 8] = make_float2(a0, b2);
-                if (!h) {
-                    const float a1 = term(xa, wa, s3);
-                    ptab[pr][1] = make_float2(a1, b0); ptab[pr][5] = make_float2(a1, b1); ptab[pr][9] = make_float2(a1, b2);
-                }
-            }
-            __syncwarp();
+    for (int q = 0; q < 4; ++q) key[q] = __ldg(nb + 1 + q);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float x = xs[i][t2], w = ws[i][t2];
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+            const float d = fsub(sq[c], x);
+            term[4 * i + c][tid] = fmul(fmul(w, d), d);
         }
-        const int n = cur.n;
-        const int nmax = (int)__reduce_max_sync(SG_FULL, (unsigned)n);
-        float best = 3.402823466e+38F;
-        int bj = 0x7fffffff;
-        auto dist = [&](unsigned key) {
-            float d = 0.f;
-            pair_terms<0>(pbase, key, d); pair_terms<1>(pbase, key, d); pair_terms<2>(pbase, key, d); pair_terms<3>(pbase, key, d);
-            return d;
-        };
-        {
-            const float da = dist(cur.k[0]), db = dist(cur.k[1]);
-            if (sub < n && da < best) { best = da; bj = sub; }
-            if (sub + W < n && db < best) { best = db; bj = sub + W; }
-        }
-        if (nmax > 2 * W) {
-            const float da = dist(cur.k[2]), db = dist(cur.k[3]);
-            if (sub + 2 * W < n && da < best) { best = da; bj = sub + 2 * W; }
-            if (sub + 3 * W < n && db < best) { best = db; bj = sub + 3 * W; }
-#pragma unroll 1
-            for (int j = sub + 4 * W; j < nmax; j += 2 * W) {
-                const unsigned k0 = j < n ? __ldg(cur.nb + 1 + j) : 0u, k1 = j + W < n ? __ldg(cur.nb + 1 + j + W) : 0u;
-                const float ea = dist(k0), eb = dist(k1);
-                if (j < n && ea < best) { best = ea; bj = j; }
-                if (j + W < n && eb < best) { best = eb; bj = j + W; }
-            }
-        }
-        // smallest distance of the lane group, earliest entry among equals
-        const unsigned mb = float_order(fadd(best, 0.f));
-        const unsigned m = __reduce_min_sync(gmask, mb);
-        bj = (int)__reduce_min_sync(gmask, mb == m ? (unsigned)bj : 0x7fffffffu);
-        if (cur.has && sub == cur.o) {
-            if (bj == 0x7fffffff) { atomicOr(status, SG_ST_OFFGRID); u = t.key0; }
-            else u = __ldg(cur.nb + 1 + bj);
-        }
-        if (!more) break;
-        cur = nxt;
     }
-    return u;
+    float best = 3.402823466e+38F;
+    unsigned bu = 0xffffffffu;
+#pragma unroll 1
+    for (int j = 0; j < n; j += 4) {
+        float d[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float d2 = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) d2 = fadd(d2, term[4 * i + (int)((key[q] >> (2 * i)) & 3u)][tid]);
+            d[q] = d2;
+        }
+        unsigned nk[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) nk[q] = __ldg(nb + 5 + j + q);          // the padding covers the overrun
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (j + q < n && d[q] < best) { best = d[q]; bu = key[q]; }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) key[q] = nk[q];
+    }
+    if (bu == 0xffffffffu) { atomicOr(status, SG_ST_OFFGRID); bu = key0; }
+    return bu;
 }
 
 // sumqx / sumq2 over the block in index order with q = 2*L + 1
@@ -417,23 +369,19 @@ template <int TYPE> struct Lattice {
     using P = Lat<TYPE>;
     static constexpr int SLAB = 256, SUB = P::BLK, LANES = 256 / P::BLK, QK = 256, BS = P::BS;
     static constexpr int BLK = P::BLK, G = P::G, CB = P::CB, NG = BLK / G, KMAXQ = P::KMAXQ;
-    static constexpr int W = P::W, TYPE_ID = TYPE;
-    using MapT = typename std::conditional<W == 0, int16_t, int>::type;
+    static constexpr int TYPE_ID = TYPE;
+    static constexpr bool SMEM_TABLES = G == 4;      // IQ3: map 4096 entries, lists < 29 K entries
+    static constexpr int TPB = SMEM_TABLES ? 512 : 256, NTERM = G == 8 ? 32 : 1;
+    using MapT = typename std::conditional<SMEM_TABLES, int16_t, int>::type;
     using View = TabView<MapT>;
+    using SM = IqSmem<BLK, TPB, NTERM>;
+    using Q = WorkQueue<TPB, NG>;
 
-    // nearest lattice point of an off-lattice group: cooperative over lane groups, or every lane for itself
-    template <class SM>
-    static SG_DEVINL unsigned search(const View& T, bool off, int list, float scale, unsigned u, int e0, SM& sm, int* status) {
-        if constexpr (W == 0) return off ? own_neighbour<G, CB>(T, list, scale, e0, sm, (int)threadIdx.x, status) : u;
-        else return coop_neighbour<W>(T, off, list, scale, u, e0, sm, status);
-    }
-
-    // One candidate scale for every block of the CTA (W == 0): all groups are rounded and looked up; those that fell
-    // off the lattice and are wanted (`want`, one bit per group) go into the CTA's queue ordered by list length
-    // (longest first), the CTA's threads search the queue side by side, and each thread reads its block's codes back.
-    template <class SM, class Q>
-    static SG_DEVINL void queue_round(const View& T, const SM& sm, Q& q, float id, float sc, unsigned want, Codes& aux, unsigned& og, int* status) {
-        const int tid = threadIdx.x, lane = tid & 31, tpb = blockDim.x;
+    // One candidate scale for every block of the CTA: all groups are rounded (inverse scale id) and looked up; those
+    // that fell off the lattice and are wanted (`want`, one bit per group) are searched through the CTA's queue at
+    // scale sc; each thread then reads its block's codes back into aux.  og: the groups that were on the lattice.
+    static SG_DEVINL void queue_round(const View& T, SM& sm, Q& q, float id, float sc, unsigned want, Codes& aux, unsigned& og, int* status) {
+        const int tid = threadIdx.x;
         q.scale[tid] = sc;
         og = 0;
 #pragma unroll 1
@@ -445,49 +393,31 @@ template <int TYPE> struct Lattice {
                 u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
             }
             const int gi = T.map[u];
-            q.u[k][tid] = (uint16_t)u;
             if (gi >= 0) og |= 1u << k;
             const bool off = ((want >> k) & 1) && gi < 0;
-            int cls = -1;
-            if (off) { cls = ((int)T.nbk[-gi - 1] + 3) >> 2; cls = cls > 15 ? 15 : cls; }
-            const unsigned peers = __match_any_sync(SG_FULL, cls);
-            unsigned r = 0xffffu;
-            if (off) {
-                const int leader = __ffs(peers) - 1;
-                int b = 0;
-                if (lane == leader) b = atomicAdd(&q.count[cls], __popc(peers));
-                b = __shfl_sync(peers, b, leader);
-                r = (unsigned)cls << 12 | (unsigned)(b + __popc(peers & ((1u << lane) - 1)));
-            }
-            q.rank[k][tid] = (uint16_t)r;
+            q.put(k, u, off, off ? (int)T.nbk[-gi - 1] : 0, G == 4 ? 2 : 3);
         }
-        __syncthreads();
-        if (tid == 0) {
-            int acc = 0;
-            for (int c = 15; c >= 0; --c) { q.base[c] = acc; acc += q.count[c]; q.count[c] = 0; }
-            q.total = acc;
-        }
-        __syncthreads();
+        const int total = q.sort();
 #pragma unroll 1
-        for (int k = 0; k < NG; ++k) {
-            const unsigned r = q.rank[k][tid];
-            if (r != 0xffffu) q.item[q.base[r >> 12] + (int)(r & 4095u)] = (uint16_t)(tid << 3 | k);
-        }
-        __syncthreads();
-        const int total = q.total;
-#pragma unroll 1
-        for (int p = tid; p < total; p += tpb) {
+        for (int p = tid; p < total; p += TPB) {
             const unsigned it = q.item[p];
-            const int t2 = (int)(it >> 3), k = (int)(it & 7);
+            const int t2 = (int)(it / NG), k = (int)(it % NG);
             const int list = -(int)T.map[q.u[k][t2]] - 1;
-            q.u[k][t2] = (uint16_t)own_neighbour<G, CB>(T, list, q.scale[t2], G * k, sm, t2, status);
+            const float s1 = q.scale[t2];
+            unsigned r;
+            if constexpr (G == 4) r = search_list4(T.nbk, list, s1, G * k, sm, t2, T.key0, status);
+            else {
+                const float sq[3] = {s1, fmul(s1, 3.f), fmul(s1, 5.f)};
+                r = search_list8<TPB>(T.nbk, list, sq, &sm.xval[G * k], &sm.waux[G * k], t2, sm.term, T.key0, status);
+            }
+            q.u[k][t2] = (uint16_t)r;
         }
         __syncthreads();
 #pragma unroll
         for (int k = 0; k < NG; ++k) aux.set(k, q.u[k][tid]);
     }
 
-    template <int DT, bool IMX, class SM, class Q>
+    template <int DT, bool IMX>
     static SG_DEVINL void run(const Job& job, const Slab& sl, int sub, bool valid, const View& T, SM& sm, Q& q) {
         const int tid = threadIdx.x;
         float wgt[BLK];
@@ -551,8 +481,8 @@ template <int TYPE> struct Lattice {
         const float eps = TYPE == SG_IQ3_XXS ? 1e-8f : TYPE == SG_IQ2_S ? 1e-8f : SG_GROUP_MAX_EPS;
         const bool dead = TYPE == SG_IQ3_S ? !(mx != 0.f) : (mx < eps);
         const float c2k1 = (float)(2 * KMAXQ - 1);
-        // Every lane runs the candidate loop, because the neighbour search inside it is a warp-wide collective;
-        // `act` marks the lanes whose block is really being searched.
+        // Every thread runs the candidate loop, because the neighbour searches inside it go through the CTA's queue;
+        // `act` marks the threads whose block is really being searched.
         bool act = !dead;
         float best = 0.f;
         float rng = 1.f;                     // denominator of the candidate inverse scales
@@ -579,43 +509,7 @@ template <int TYPE> struct Lattice {
                 const float this_scale = frcp(id);
                 Codes aux;
                 unsigned og = 0;
-                if constexpr (W == 0) {
-                    queue_round(T, sm, q, id, this_scale, act ? 0xffu : 0u, aux, og, job.status);
-                } else if constexpr (NG <= 2) {
-                    // all map lookups of the block first (they miss L1 often), then the searches
-                    unsigned uk[NG];
-                    int gk[NG];
-#pragma unroll
-                    for (int k = 0; k < NG; ++k) {
-                        unsigned u = 0;
-#pragma unroll
-                        for (int i = 0; i < G; ++i) {
-                            const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
-                            u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
-                        }
-                        uk[k] = u;
-                        gk[k] = __ldg(T.map + u);
-                    }
-#pragma unroll
-                    for (int k = 0; k < NG; ++k) {
-                        if (gk[k] >= 0) og |= 1u << k;
-                        aux.set(k, search(T, act && gk[k] < 0, -gk[k] - 1, this_scale, uk[k], G * k, sm, job.status));
-                    }
-                } else {
-#pragma unroll 1
-                    for (int k = 0; k < NG; ++k) {
-                        unsigned u = 0;
-#pragma unroll
-                        for (int i = 0; i < G; ++i) {
-                            const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
-                            u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
-                        }
-                        const int gi = T.map[u];
-                        if (gi >= 0) og |= 1u << k;
-                        u = search(T, act && gi < 0, -gi - 1, this_scale, u, G * k, sm, job.status);
-                        aux.set(k, u);
-                    }
-                }
+                queue_round(T, sm, q, id, this_scale, act ? 0xffu : 0u, aux, og, job.status);
                 float sumqx, sumq2;
                 block_sums<BLK, G, CB>(aux, wgt, sm, tid, sumqx, sumq2);
                 if (act && sumq2 > 0.f && fmul(sumqx, sumqx) > fmul(best, sumq2)) {
@@ -630,36 +524,14 @@ template <int TYPE> struct Lattice {
                 const unsigned all = (1u << NG) - 1;
                 refit = act && (ongrid & all) != all && scale > 0.f;
             }
-            if constexpr (W == 0) {
-                if (__syncthreads_or(refit)) {
-                    unsigned want = 0;
-                    if (refit) want = TYPE == SG_IQ3_XXS ? ~ongrid & 0xffu : 0xffu;
-                    Codes aux;
-                    unsigned og;
-                    queue_round(T, sm, q, frcp(scale), scale, want, aux, og, job.status);
+            if (__syncthreads_or(refit)) {
+                unsigned want = 0;
+                if (refit) want = (TYPE == SG_IQ2_XS || TYPE == SG_IQ2_S || TYPE == SG_IQ3_XXS) ? ~ongrid & ((1u << NG) - 1) : (1u << NG) - 1;
+                Codes aux;
+                unsigned og;
+                queue_round(T, sm, q, frcp(scale), scale, want, aux, og, job.status);
 #pragma unroll
-                    for (int k = 0; k < NG; ++k) if ((want >> k) & 1) L.set(k, aux.get(k));
-                    if (refit) {
-                        float sumqx, sumq2;
-                        block_sums<BLK, G, CB>(L, wgt, sm, tid, sumqx, sumq2);
-                        if (sumq2 > 0.f) scale = fdiv(sumqx, sumq2);
-                    }
-                }
-            } else if (__any_sync(SG_FULL, refit)) {
-                const float id = frcp(scale);
-#pragma unroll 1
-                for (int k = 0; k < NG; ++k) {
-                    const bool skip = !refit || ((TYPE == SG_IQ2_XS || TYPE == SG_IQ2_S || TYPE == SG_IQ3_XXS) && ((ongrid >> k) & 1));
-                    unsigned u = 0;
-#pragma unroll
-                    for (int i = 0; i < G; ++i) {
-                        const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
-                        u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
-                    }
-                    const int gi = T.map[u];
-                    u = search(T, !skip && gi < 0, -gi - 1, scale, u, G * k, sm, job.status);
-                    if (!skip) L.set(k, u);           // on the grid the codes ARE the grid point
-                }
+                for (int k = 0; k < NG; ++k) if ((want >> k) & 1) L.set(k, aux.get(k));     // on the grid the codes ARE the grid point
                 if (refit) {
                     float sumqx, sumq2;
                     block_sums<BLK, G, CB>(L, wgt, sm, tid, sumqx, sumq2);
@@ -1138,45 +1010,33 @@ __global__ void __launch_bounds__(IQ_TPB) k_quant_iq(const __grid_constant__ Job
     T::template run<DT, IMX>(job, sl, sub, valid, tabs, sm);
 }
 
-// lattice types with a cooperative search: 64-thread CTAs, tables read from global memory (they stay in L2)
-template <class T, int DT, bool IMX>
-__global__ void __launch_bounds__(IQ_TPB) k_quant_lat(const __grid_constant__ Job job, const __grid_constant__ GridTable tab) {
-    __shared__ IqSmem<T::BLK, IQ_TPB, IQ_TPB / 8> sm;
-    constexpr int LANES = T::LANES;
-    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    long long s = g / LANES;
-    const int sub = (int)(g - s * LANES);
-    const bool valid = s < job.nslabs;
-    if (!valid) s = job.nslabs - 1;
-    const Slab sl = locate<T::SLAB>(job, s);
-    typename T::View view;
-    view.map = tab.map; view.nbk = tab.nbkeys; view.key0 = __ldg(tab.keys);
-    NoQueue nq;
-    T::template run<DT, IMX>(job, sl, sub, valid, view, sm, nq);
-}
-
-// IQ3_XXS / IQ3_S: their tables are small (map 4096 entries, lists < 29 K entries), so each CTA copies them into
-// shared memory once and then walks over tiles of LAT3_TPB blocks; every lane searches its own lists there.
-constexpr int LAT3_TPB = 512;
-template <class T> struct Lat3Smem {
-    IqSmem<T::BLK, LAT3_TPB, 1> v;
-    QueueSmem<LAT3_TPB> q;
-    int16_t map[4096];
-    uint16_t nbk[1];              // nb_size + 64 entries follow
+// Lattice kernels: CTAs of T::TPB threads, one block of 16 / 32 weights per thread, walking over tiles of T::TPB
+// blocks.  The IQ3 tables are small, so each CTA copies them into shared memory first; the IQ2 tables stay in global
+// memory (they are L2-resident).
+template <class T> struct LatSmem {
+    typename T::SM v;
+    typename T::Q q;
+    int16_t map[T::SMEM_TABLES ? 4096 : 1];
+    uint16_t nbk[1];              // SMEM_TABLES: nb_size + 64 entries follow
 };
 template <class T, int DT, bool IMX>
-__global__ void __launch_bounds__(LAT3_TPB) k_quant_lat3(const __grid_constant__ Job job, const __grid_constant__ GridTable tab, long long ntiles) {
-    extern __shared__ __align__(128) unsigned char raw[];
-    Lat3Smem<T>& sm = *reinterpret_cast<Lat3Smem<T>*>(raw);
-    for (int i = threadIdx.x; i < 4096; i += LAT3_TPB) sm.map[i] = (int16_t)__ldg(tab.map + i);
-    for (int i = threadIdx.x; i < tab.nb_size + 64; i += LAT3_TPB) sm.nbk[i] = __ldg(tab.nbkeys + i);
-    if (threadIdx.x < 16) sm.q.count[threadIdx.x] = 0;
-    __syncthreads();
+__global__ void __launch_bounds__(T::TPB, T::TPB == 256 ? 2 : 1) k_quant_lat(const __grid_constant__ Job job, const __grid_constant__ GridTable tab, long long ntiles) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    LatSmem<T>& sm = *reinterpret_cast<LatSmem<T>*>(raw);
+    constexpr int TPB = T::TPB, LANES = T::LANES;
     typename T::View view;
-    view.map = sm.map; view.nbk = sm.nbk; view.key0 = __ldg(tab.keys);
-    constexpr int LANES = T::LANES;
+    view.key0 = __ldg(tab.keys);
+    if constexpr (T::SMEM_TABLES) {
+        for (int i = threadIdx.x; i < 4096; i += TPB) sm.map[i] = (int16_t)__ldg(tab.map + i);
+        for (int i = threadIdx.x; i < tab.nb_size + 64; i += TPB) sm.nbk[i] = __ldg(tab.nbkeys + i);
+        view.map = sm.map; view.nbk = sm.nbk;
+    } else {
+        view.map = tab.map; view.nbk = tab.nbkeys;
+    }
+    if (threadIdx.x < 32) sm.q.count[threadIdx.x] = 0;
+    __syncthreads();
     for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        const long long g = tile * LAT3_TPB + threadIdx.x;
+        const long long g = tile * TPB + threadIdx.x;
         long long s = g / LANES;
         const int sub = (int)(g - s * LANES);
         const bool valid = s < job.nslabs;
@@ -1219,37 +1079,33 @@ static int launch_lat(const Job& job, int dt, cudaStream_t st, const IqTables& t
     const GridTable& tab = tabs.t[Lat<T::TYPE_ID>::TAB];
     const long long threads = job.nslabs * T::LANES;
     if (threads == 0) return SG_OK;
-    if constexpr (T::W != 0) {
-        const unsigned grid = (unsigned)((threads + IQ_TPB - 1) / IQ_TPB);
-        switch (dt) {
-            case SG_DT_BF16: k_quant_lat<T, SG_DT_BF16, IMX><<<grid, IQ_TPB, 0, st>>>(job, tab); break;
-            case SG_DT_F16:  k_quant_lat<T, SG_DT_F16, IMX><<<grid, IQ_TPB, 0, st>>>(job, tab); break;
-            case SG_DT_F32:  k_quant_lat<T, SG_DT_F32, IMX><<<grid, IQ_TPB, 0, st>>>(job, tab); break;
-            default: return SG_ERR_ARG;
-        }
-    } else {
+    size_t smem = sizeof(LatSmem<T>);
+    if (T::SMEM_TABLES) {
         if (tab.map_size != 4096 || tab.nb_size > 32767) return SG_ERR_TABLES;
-        const size_t smem = sizeof(Lat3Smem<T>) + (size_t)(tab.nb_size + 64) * sizeof(uint16_t);
-        const long long ntiles = (threads + LAT3_TPB - 1) / LAT3_TPB;
-        int dev = 0, sms = 0;
-        int rc = cuda_ok(cudaGetDevice(&dev));
-        if (rc == SG_OK) rc = cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        if (rc != SG_OK) return rc;
-        const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);
-        auto go = [&](auto kern) -> int {
-            int r = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            if (r != SG_OK) return r;
-            kern<<<grid, LAT3_TPB, smem, st>>>(job, tab, ntiles);
-            return SG_OK;
-        };
-        switch (dt) {
-            case SG_DT_BF16: rc = go(k_quant_lat3<T, SG_DT_BF16, IMX>); break;
-            case SG_DT_F16:  rc = go(k_quant_lat3<T, SG_DT_F16, IMX>); break;
-            case SG_DT_F32:  rc = go(k_quant_lat3<T, SG_DT_F32, IMX>); break;
-            default: return SG_ERR_ARG;
-        }
-        if (rc != SG_OK) return rc;
+        smem += (size_t)(tab.nb_size + 64) * sizeof(uint16_t);
     }
+    const long long ntiles = (threads + T::TPB - 1) / T::TPB;
+    int dev = 0, sms = 0;
+    int rc = cuda_ok(cudaGetDevice(&dev));
+    if (rc == SG_OK) rc = cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (rc != SG_OK) return rc;
+    auto go = [&](auto kern) -> int {
+        int r = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        int per_sm = 0;
+        if (r == SG_OK) r = cuda_ok(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, T::TPB, smem));
+        if (r != SG_OK) return r;
+        if (per_sm < 1) return SG_ERR_LIMIT;
+        const long long resident = (long long)sms * per_sm;
+        kern<<<(unsigned)(ntiles < resident ? ntiles : resident), T::TPB, smem, st>>>(job, tab, ntiles);
+        return SG_OK;
+    };
+    switch (dt) {
+        case SG_DT_BF16: rc = go(k_quant_lat<T, SG_DT_BF16, IMX>); break;
+        case SG_DT_F16:  rc = go(k_quant_lat<T, SG_DT_F16, IMX>); break;
+        case SG_DT_F32:  rc = go(k_quant_lat<T, SG_DT_F32, IMX>); break;
+        default: return SG_ERR_ARG;
+    }
+    if (rc != SG_OK) return rc;
     return cuda_ok(cudaGetLastError());
 }
 template <class T, bool IMX>
