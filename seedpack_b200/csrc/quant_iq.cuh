@@ -213,16 +213,16 @@ template <class MapT> struct TabView {
 // first), and the CTA's threads then take queue entries side by side: the lanes of a warp walk lists of equal
 // length, whichever blocks they belong to.  Results go back through u[][].
 constexpr int ilog2_ce(int v) { return v <= 1 ? 0 : 1 + ilog2_ce(v / 2); }
-template <int TPB, int NG> struct WorkQueue {
-    static constexpr int RANK_BITS = ilog2_ce(TPB * NG), CLS_BITS = 16 - RANK_BITS;
+template <int TPB, int NS, int R> struct WorkQueue {
+    static constexpr int RANK_BITS = ilog2_ce(TPB * NS), CLS_BITS = 16 - RANK_BITS;
     static constexpr int NCLS = CLS_BITS >= 5 ? 32 : (1 << CLS_BITS);
-    uint16_t u[NG][TPB];          // codes of every block's groups
-    uint16_t rank[NG][TPB];       // class << RANK_BITS | position inside the class; 0xffff = nothing to search
-    uint16_t item[NG * TPB];      // the ordered queue: thread * NG + group
-    float scale[TPB];             // the scale each block is searched at
+    uint16_t u[NS][TPB];          // codes of every block's groups, one slot per (candidate scale, group)
+    uint16_t rank[NS][TPB];       // class << RANK_BITS | position inside the class; 0xffff = nothing to search
+    uint16_t item[NS * TPB];      // the ordered queue: thread * NS + slot
+    float scale[R][TPB];          // the candidate scales each block is searched at
     int count[32], base[32], total;
 
-    // every lane of the warp calls this once per group k; off: the group needs a search of a list of n entries,
+    // every lane of the warp calls this once per slot k; off: the group needs a search of a list of n entries,
     // lists of up to 2^cshift entries more or less count as equally long
     SG_DEVINL void put(int k, unsigned codes, bool off, int n, int cshift) {
         const int tid = threadIdx.x, lane = tid & 31;
@@ -240,8 +240,8 @@ template <int TPB, int NG> struct WorkQueue {
         }
         rank[k][tid] = (uint16_t)r;
     }
-    // all threads of the CTA, after their puts: orders the queue, returns its length
-    SG_DEVINL int sort() {
+    // all threads of the CTA, after their puts into slots 0 .. ns-1: orders the queue, returns its length
+    SG_DEVINL int sort(int ns) {
         const int tid = threadIdx.x;
         __syncthreads();
         if (tid == 0) {
@@ -250,10 +250,10 @@ template <int TPB, int NG> struct WorkQueue {
             total = acc;
         }
         __syncthreads();
-#pragma unroll
-        for (int k = 0; k < NG; ++k) {
+#pragma unroll 1
+        for (int k = 0; k < ns; ++k) {
             const unsigned r = rank[k][tid];
-            if (r != 0xffffu) item[base[r >> RANK_BITS] + (int)(r & ((1u << RANK_BITS) - 1))] = (uint16_t)(tid * NG + k);
+            if (r != 0xffffu) item[base[r >> RANK_BITS] + (int)(r & ((1u << RANK_BITS) - 1))] = (uint16_t)(tid * NS + k);
         }
         __syncthreads();
         return total;
@@ -375,46 +375,57 @@ template <int TYPE> struct Lattice {
     using MapT = typename std::conditional<SMEM_TABLES, int16_t, int>::type;
     using View = TabView<MapT>;
     using SM = IqSmem<BLK, TPB, NTERM>;
-    using Q = WorkQueue<TPB, NG>;
+    static constexpr int R = 8 / NG;                 // candidate scales searched per pass over the queue (8 slots a block)
+    using Q = WorkQueue<TPB, 8, R>;
 
-    // One candidate scale for every block of the CTA: all groups are rounded (inverse scale id) and looked up; those
-    // that fell off the lattice and are wanted (`want`, one bit per group) are searched through the CTA's queue at
-    // scale sc; each thread then reads its block's codes back into aux.  og: the groups that were on the lattice.
-    static SG_DEVINL void queue_round(const View& T, SM& sm, Q& q, float id, float sc, unsigned want, Codes& aux, unsigned& og, int* status) {
+    // nr candidate scales for every block of the CTA.  cand(r, id, sc, want) describes candidate r of a block: all
+    // its groups are rounded with inverse scale id and looked up; those that fell off the lattice and are wanted
+    // (`want`, one bit per group) are searched through the CTA's queue at scale sc; each thread then reads its
+    // block's codes back into aux[r].  on: bit r * NG + k is set where group k of candidate r was on the lattice.
+    template <class F>
+    static SG_DEVINL void queue_round(const View& T, SM& sm, Q& q, int nr, F cand, Codes (&aux)[R], unsigned& on, int* status) {
         const int tid = threadIdx.x;
-        q.scale[tid] = sc;
-        og = 0;
+        on = 0;
 #pragma unroll 1
-        for (int k = 0; k < NG; ++k) {
-            unsigned u = 0;
+        for (int r = 0; r < nr; ++r) {
+            float id, sc;
+            unsigned want;
+            cand(r, id, sc, want);
+            q.scale[r][tid] = sc;
+#pragma unroll 1
+            for (int k = 0; k < NG; ++k) {
+                unsigned u = 0;
 #pragma unroll
-            for (int i = 0; i < G; ++i) {
-                const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
-                u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
+                for (int i = 0; i < G; ++i) {
+                    const int l = nearest_int(fmul(0.5f, fsub(fmul(id, sm.xval[G * k + i][tid]), 1.f)));
+                    u |= (unsigned)clampi(l, 0, KMAXQ - 1) << (CB * i);
+                }
+                const int gi = T.map[u];
+                if (gi >= 0) on |= 1u << (r * NG + k);
+                const bool off = ((want >> k) & 1) && gi < 0;
+                q.put(r * NG + k, u, off, off ? (int)T.nbk[-gi - 1] : 0, G == 4 ? 2 : 3);
             }
-            const int gi = T.map[u];
-            if (gi >= 0) og |= 1u << k;
-            const bool off = ((want >> k) & 1) && gi < 0;
-            q.put(k, u, off, off ? (int)T.nbk[-gi - 1] : 0, G == 4 ? 2 : 3);
         }
-        const int total = q.sort();
+        const int total = q.sort(nr * NG);
 #pragma unroll 1
         for (int p = tid; p < total; p += TPB) {
             const unsigned it = q.item[p];
-            const int t2 = (int)(it / NG), k = (int)(it % NG);
-            const int list = -(int)T.map[q.u[k][t2]] - 1;
-            const float s1 = q.scale[t2];
-            unsigned r;
-            if constexpr (G == 4) r = search_list4(T.nbk, list, s1, G * k, sm, t2, T.key0, status);
+            const int t2 = (int)(it >> 3), slot = (int)(it & 7), k = slot % NG;
+            const int list = -(int)T.map[q.u[slot][t2]] - 1;
+            const float s1 = q.scale[slot / NG][t2];
+            unsigned res;
+            if constexpr (G == 4) res = search_list4(T.nbk, list, s1, G * k, sm, t2, T.key0, status);
             else {
                 const float sq[3] = {s1, fmul(s1, 3.f), fmul(s1, 5.f)};
-                r = search_list8<TPB>(T.nbk, list, sq, &sm.xval[G * k], &sm.waux[G * k], t2, sm.term, T.key0, status);
+                res = search_list8<TPB>(T.nbk, list, sq, &sm.xval[G * k], &sm.waux[G * k], t2, sm.term, T.key0, status);
             }
-            q.u[k][t2] = (uint16_t)r;
+            q.u[slot][t2] = (uint16_t)res;
         }
         __syncthreads();
 #pragma unroll
-        for (int k = 0; k < NG; ++k) aux.set(k, q.u[k][tid]);
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int k = 0; k < NG; ++k) aux[r].set(k, q.u[r * NG + k][tid]);
     }
 
     template <int DT, bool IMX>
@@ -503,35 +514,43 @@ template <int TYPE> struct Lattice {
         }
         {
             const float step = (TYPE == SG_IQ3_XXS || TYPE == SG_IQ3_S) ? 0.2f : 0.1f;
+            constexpr unsigned ALL = (1u << NG) - 1;
 #pragma unroll 1
-            for (int is = P::IS0; is <= P::IS1; ++is) {
-                const float id = fdiv(fadd(c2k1, fmul((float)is, step)), rng);
-                const float this_scale = frcp(id);
-                Codes aux;
-                unsigned og = 0;
-                queue_round(T, sm, q, id, this_scale, act ? 0xffu : 0u, aux, og, job.status);
-                float sumqx, sumq2;
-                block_sums<BLK, G, CB>(aux, wgt, sm, tid, sumqx, sumq2);
-                if (act && sumq2 > 0.f && fmul(sumqx, sumqx) > fmul(best, sumq2)) {
-                    scale = fdiv(sumqx, sumq2); best = fmul(scale, sumqx);
-                    L = aux; ongrid = og;
+            for (int is0 = P::IS0; is0 <= P::IS1; is0 += R) {
+                const int nr = P::IS1 - is0 + 1 < R ? P::IS1 - is0 + 1 : R;
+                Codes aux[R];
+                unsigned on;
+                queue_round(T, sm, q, nr, [&](int r, float& id, float& sc, unsigned& want) {
+                    id = fdiv(fadd(c2k1, fmul((float)(is0 + r), step)), rng);
+                    sc = frcp(id);
+                    want = act ? ALL : 0u;
+                }, aux, on, job.status);
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    if (r >= nr) break;
+                    float sumqx, sumq2;
+                    block_sums<BLK, G, CB>(aux[r], wgt, sm, tid, sumqx, sumq2);
+                    if (act && sumq2 > 0.f && fmul(sumqx, sumqx) > fmul(best, sumq2)) {
+                        scale = fdiv(sumqx, sumq2); best = fmul(scale, sumqx);
+                        L = aux[r]; ongrid = (on >> (r * NG)) & ALL;
+                    }
                 }
             }
             // second pass at the winning scale
             bool refit;
             if (TYPE == SG_IQ2_XXS) refit = act && scale > 0.f;
             else {
-                const unsigned all = (1u << NG) - 1;
-                refit = act && (ongrid & all) != all && scale > 0.f;
+                refit = act && (ongrid & ALL) != ALL && scale > 0.f;
             }
             if (__syncthreads_or(refit)) {
-                unsigned want = 0;
-                if (refit) want = (TYPE == SG_IQ2_XS || TYPE == SG_IQ2_S || TYPE == SG_IQ3_XXS) ? ~ongrid & ((1u << NG) - 1) : (1u << NG) - 1;
-                Codes aux;
-                unsigned og;
-                queue_round(T, sm, q, frcp(scale), scale, want, aux, og, job.status);
+                unsigned want0 = 0;
+                if (refit) want0 = (TYPE == SG_IQ2_XS || TYPE == SG_IQ2_S || TYPE == SG_IQ3_XXS) ? ~ongrid & ALL : ALL;
+                Codes aux[R];
+                unsigned on;
+                const float win = scale;
+                queue_round(T, sm, q, 1, [&](int, float& id, float& sc, unsigned& want) { id = frcp(win); sc = win; want = want0; }, aux, on, job.status);
 #pragma unroll
-                for (int k = 0; k < NG; ++k) if ((want >> k) & 1) L.set(k, aux.get(k));     // on the grid the codes ARE the grid point
+                for (int k = 0; k < NG; ++k) if ((want0 >> k) & 1) L.set(k, aux[0].get(k));     // on the grid the codes ARE the grid point
                 if (refit) {
                     float sumqx, sumq2;
                     block_sums<BLK, G, CB>(L, wgt, sm, tid, sumqx, sumq2);
