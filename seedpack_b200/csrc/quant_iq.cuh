@@ -33,7 +33,6 @@ struct IqTables { GridTable t[6]; };
 
 static __constant__ int8_t c_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
 
-constexpr int IQ_TPB = 64;      // threads per CTA of the IQ kernels (bounds their shared memory)
 
 // ==================================================================================================
 // IQ4_NL / IQ4_XS
@@ -212,7 +211,7 @@ template <class MapT> struct TabView {
 // that fell off the lattice, the queue is ordered by list length (a counting sort over length classes, longest
 // first), and the CTA's threads then take queue entries side by side: the lanes of a warp walk lists of equal
 // length, whichever blocks they belong to.  Results go back through u[][].
-constexpr int ilog2_ce(int v) { return v <= 1 ? 0 : 1 + ilog2_ce(v / 2); }
+constexpr int ilog2_ce(int v) { return v <= 1 ? 0 : 1 + ilog2_ce((v + 1) / 2); }     // bits that hold 0 .. v-1
 template <int TPB, int NS, int R> struct WorkQueue {
     static constexpr int RANK_BITS = ilog2_ce(TPB * NS), CLS_BITS = 16 - RANK_BITS;
     static constexpr int NCLS = CLS_BITS >= 5 ? 32 : (1 << CLS_BITS);
@@ -220,6 +219,7 @@ template <int TPB, int NS, int R> struct WorkQueue {
     uint16_t rank[NS][TPB];       // class << RANK_BITS | position inside the class; 0xffff = nothing to search
     uint16_t item[NS * TPB];      // the ordered queue: thread * NS + slot
     float scale[R][TPB];          // the candidate scales each block is searched at
+    uint8_t flag[TPB];            // per block, for the kernel's use
     int count[32], base[32], total;
 
     // every lane of the warp calls this once per slot k; off: the group needs a search of a list of n entries,
@@ -369,7 +369,7 @@ template <int TYPE> struct Lattice {
     using P = Lat<TYPE>;
     static constexpr int SLAB = 256, SUB = P::BLK, LANES = 256 / P::BLK, QK = 256, BS = P::BS;
     static constexpr int BLK = P::BLK, G = P::G, CB = P::CB, NG = BLK / G, KMAXQ = P::KMAXQ;
-    static constexpr int TYPE_ID = TYPE;
+    static constexpr int TYPE_ID = TYPE, TAB = P::TAB;
     static constexpr bool SMEM_TABLES = G == 4;      // IQ3: map 4096 entries, lists < 29 K entries
     static constexpr int TPB = SMEM_TABLES ? 512 : 256, NTERM = G == 8 ? 32 : 1;
     using MapT = typename std::conditional<SMEM_TABLES, int16_t, int>::type;
@@ -660,61 +660,14 @@ template <int TYPE> struct Lattice {
 
 // ==================================================================================================
 // IQ1_S / IQ1_M
-template <int BLK, int NPS> struct Iq1Smem {
-    float xb[BLK][IQ_TPB];
-    float wgt[BLK][IQ_TPB];
-    float pa[NPS][IQ_TPB];        // prefix sums of weight * x in sorted order
-    float pb[NPS][IQ_TPB];        // prefix sums of weight
-    uint8_t idx[BLK][IQ_TPB];     // sorted position -> element
-    uint8_t L[BLK][IQ_TPB];       // ternary codes 0,1,2
+template <int BLK, int NPS, int TPB> struct Iq1Smem {
+    float xb[BLK][TPB];
+    float wgt[BLK][TPB];
+    float pa[NPS][TPB];           // prefix sums of weight * x in sorted order; later the list walker's 32 distance terms
+    float pb[NPS][TPB];           // prefix sums of weight
+    uint8_t idx[BLK][TPB];        // sorted position -> element
+    uint8_t L[BLK][TPB];          // ternary codes 0,1,2
 };
-
-template <int G> SG_DEVINL void grid_point(const GridTable& t, int idx, int (&pg)[G]) {
-    if (G == 8) {
-        const unsigned long long v = __ldg(static_cast<const unsigned long long*>(t.grid) + idx);
-#pragma unroll
-        for (int i = 0; i < G; ++i) pg[i] = (int)(int8_t)(v >> (8 * i));
-    } else {
-        const unsigned v = __ldg(static_cast<const unsigned*>(t.grid) + idx);
-#pragma unroll
-        for (int i = 0; i < G; ++i) pg[i] = (int)(int8_t)(v >> (8 * i));
-    }
-}
-
-// iq1_find_best_neighbour2 (ggml-quants.c:4444-4499).  The exhaustive fall-back of the C code is only
-// reachable when every distance is NaN; that case sets SG_ST_OFFGRID instead.
-template <class SM>
-SG_DEVINL int best_neighbour_iq1(const GridTable& t, int list, SM& sm, int tid, int e0, float scale,
-                                 const float (&xg)[3], int* status) {
-    const uint16_t* nb = t.neighbours + list;
-    const int n = __ldg(nb);
-    float best = 3.402823466e+38F;
-    int grid_index = -1;
-    float xv[8], wv[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { xv[i] = sm.xb[e0 + i][tid]; wv[i] = sm.wgt[e0 + i][tid]; }
-#pragma unroll 1
-    for (int j = 1; j <= n; ++j) {
-        const int gi = __ldg(nb + j);
-        int pg[8];
-        grid_point<8>(t, gi, pg);
-        float d2 = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int c = (pg[i] - 1) / 2;
-            const float q = c == 0 ? xg[0] : c == 1 ? xg[1] : xg[2];
-            const float diff = fsub(fmul(scale, q), xv[i]);
-            d2 = fadd(d2, fmul(fmul(wv[i], diff), diff));
-        }
-        if (d2 < best) { best = d2; grid_index = gi; }
-    }
-    if (grid_index < 0) { atomicOr(status, SG_ST_OFFGRID); grid_index = 0; }
-    int pg[8];
-    grid_point<8>(t, grid_index, pg);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sm.L[e0 + i][tid] = (uint8_t)((pg[i] - 1) / 2);
-    return grid_index;
-}
 
 // stable insertion sort of (value, index) by value (seedpack/gpuquant.py:70-80 replaces qsort with exactly this)
 template <int BLK, class SM> SG_DEVINL void sort_block(SM& sm, int tid) {
@@ -738,12 +691,17 @@ template <int BLK, class SM> SG_DEVINL void sort_block(SM& sm, int tid) {
 template <bool M, int VARIANT> struct IQ1 {
     static constexpr int BLK = M ? 16 : 32, NPS = M ? 34 : 33;
     static constexpr int SLAB = 256, SUB = BLK, LANES = 256 / BLK, QK = 256, BS = M ? 56 : 50;
-    using SM = Iq1Smem<BLK, NPS>;
-    using Smem = SM;
+    static constexpr int TPB = M ? 448 : 320, NG = BLK / 8;         // CTA size: what the shared memory allows
+    static constexpr bool SMEM_TABLES = false;
+    static constexpr int TAB = 2;
+    using SM = Iq1Smem<BLK, NPS, TPB>;
+    using Q = WorkQueue<TPB, NG, 1>;
+    using View = TabView<int>;
 
+    // The grid snap (iq1_find_best_neighbour2) goes through the CTA's sorted queue like the lattice types' searches:
+    // its lists have 91 entries on average and up to 205.
     template <int DT, bool IMX>
-    static SG_DEVINL void run(const Job& job, const Slab& sl, int sub, bool valid, const IqTables& tabs, SM& sm) {
-        const GridTable& T = tabs.t[2];
+    static SG_DEVINL void run(const Job& job, const Slab& sl, int sub, bool valid, const View& T, SM& sm, Q& q) {
         const int tid = threadIdx.x;
         const float x_p[3] = {-1 + 0.125f, 0.125f, 1 + 0.125f};
         const float x_m[3] = {-1 - 0.125f, -0.125f, 1 - 0.125f};
@@ -768,12 +726,13 @@ template <bool M, int VARIANT> struct IQ1 {
         unsigned index[BLK / 8];
 #pragma unroll
         for (int k = 0; k < BLK / 8; ++k) index[k] = 0;
-        bool wrote = false;
+        bool wrote = false, found = false;
+        int best_k = M ? -1 : 0;
         if (!(mx < (M ? 1e-7f : 1e-12f))) {
             sort_block<BLK>(sm, tid);
             float best_score = -3.402823466e+38F;
             scale = mx;
-            int besti1 = -1, besti2 = -1, best_k = M ? -1 : 0;
+            int besti1 = -1, besti2 = -1;
             if (!M) {
                 sm.pa[0][tid] = 0.f; sm.pb[0][tid] = 0.f;
                 {
@@ -891,7 +850,7 @@ template <bool M, int VARIANT> struct IQ1 {
                     }
                 }
             }
-            const bool found = besti1 >= 0 && besti2 >= 0 && (M ? best_k >= 0 : best_k != 0);
+            found = besti1 >= 0 && besti2 >= 0 && (M ? best_k >= 0 : best_k != 0);
             if (found) {
 #pragma unroll 1
                 for (int j = 0; j < BLK; ++j) sm.L[sm.idx[j][tid]][tid] = (uint8_t)(j < besti1 ? 0 : j < besti2 ? 1 : 2);
@@ -901,44 +860,74 @@ template <bool M, int VARIANT> struct IQ1 {
                     scale = -scale;
                     best_k = M ? 3 - best_k : -best_k;
                 }
-                bool all_on_grid = true;
-#pragma unroll
-                for (int k = 0; k < BLK / 8; ++k) {
-                    const bool plus = M ? (k == 0 ? best_k < 2 : (best_k % 2 == 0)) : best_k == 1;
-                    const float xx[3] = {plus ? x_p[0] : x_m[0], plus ? x_p[1] : x_m[1], plus ? x_p[2] : x_m[2]};
-                    unsigned u = 0;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) u |= (unsigned)sm.L[8 * k + j][tid] << (2 * j);
-                    int gi = __ldg(T.map + u);
-                    if (gi < 0) {
-                        all_on_grid = false;
-                        gi = best_neighbour_iq1(T, -gi - 1, sm, tid, 8 * k, scale, xx, job.status);
-                    }
-                    index[k] = (unsigned)gi;
-                }
-                if (!all_on_grid) {
-                    float sumqx = 0.f, sumq2 = 0.f;
-#pragma unroll
-                    for (int k = 0; k < BLK / 8; ++k) {
-                        const bool plus = M ? (k == 0 ? best_k < 2 : (best_k % 2 == 0)) : best_k == 1;
-                        int pg[8];
-                        grid_point<8>(T, (int)index[k], pg);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const int c = (pg[j] - 1) / 2;
-                            const float q = plus ? (c == 0 ? x_p[0] : c == 1 ? x_p[1] : x_p[2]) : (c == 0 ? x_m[0] : c == 1 ? x_m[1] : x_m[2]);
-                            const float w = sm.wgt[8 * k + j][tid];
-                            sumqx = fadd(sumqx, fmul(fmul(w, q), sm.xb[8 * k + j][tid]));
-                            sumq2 = fadd(sumq2, fmul(fmul(w, q), q));
-                        }
-                    }
-                    if (sumqx > 0.f && sumq2 > 0.f) scale = fdiv(sumqx, sumq2);
-                }
-                shift = best_k;
-                wrote = true;
             } else {
                 scale = 0.f;
             }
+        }
+        // grid snap of every group of 8 through the queue
+        unsigned plusmask = 0;
+#pragma unroll
+        for (int k = 0; k < NG; ++k)
+            if (M ? (k == 0 ? best_k < 2 : (best_k % 2 == 0)) : best_k == 1) plusmask |= 1u << k;
+        q.scale[0][tid] = scale;
+        q.flag[tid] = (uint8_t)plusmask;
+        bool all_on_grid = true;
+#pragma unroll
+        for (int k = 0; k < NG; ++k) {
+            unsigned u = 0;
+            if (found) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) u |= (unsigned)sm.L[8 * k + j][tid] << (2 * j);
+            }
+            const int gi = found ? T.map[u] : 0;
+            const bool off = gi < 0;
+            if (off) all_on_grid = false;
+            q.put(k, u, off, off ? (int)T.nbk[-gi - 1] : 0, 3);
+        }
+        {
+            const int total = q.sort(NG);
+            float (*term)[TPB] = sm.pa;               // the prefix sums are dead by now
+#pragma unroll 1
+            for (int p = tid; p < total; p += TPB) {
+                const unsigned it = q.item[p];
+                const int t2 = (int)(it / NG), k = (int)(it % NG);
+                const int list = -T.map[q.u[k][t2]] - 1;
+                const float s1 = q.scale[0][t2];
+                const bool plus = (q.flag[t2] >> k) & 1;
+                const float sq[3] = {fmul(s1, plus ? x_p[0] : x_m[0]), fmul(s1, plus ? x_p[1] : x_m[1]), fmul(s1, plus ? x_p[2] : x_m[2])};
+                q.u[k][t2] = (uint16_t)search_list8<TPB>(T.nbk, list, sq, &sm.xb[8 * k], &sm.wgt[8 * k], t2, term, T.key0, job.status);
+            }
+            __syncthreads();
+        }
+        unsigned ukey[NG];                  // levels of the chosen grid points, 2 bits a weight
+#pragma unroll
+        for (int k = 0; k < NG; ++k) ukey[k] = T.key0;      // bytes that stay zero name grid point 0
+        if (found) {
+#pragma unroll
+            for (int k = 0; k < NG; ++k) {
+                ukey[k] = q.u[k][tid];
+                int gi = T.map[ukey[k]];
+                if (gi < 0) { atomicOr(job.status, SG_ST_OFFGRID); gi = 0; ukey[k] = T.key0; }
+                index[k] = (unsigned)gi;
+            }
+            if (!all_on_grid) {
+                float sumqx = 0.f, sumq2 = 0.f;
+#pragma unroll
+                for (int k = 0; k < NG; ++k) {
+                    const bool plus = (plusmask >> k) & 1;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const unsigned c = (ukey[k] >> (2 * j)) & 3u;
+                        const float qv = plus ? (c == 0 ? x_p[0] : c == 1 ? x_p[1] : x_p[2]) : (c == 0 ? x_m[0] : c == 1 ? x_m[1] : x_m[2]);
+                        const float w = sm.wgt[8 * k + j][tid];
+                        sumqx = fadd(sumqx, fmul(fmul(w, qv), sm.xb[8 * k + j][tid]));
+                        sumq2 = fadd(sumq2, fmul(fmul(w, qv), qv));
+                    }
+                }
+                if (sumqx > 0.f && sumq2 > 0.f) scale = fdiv(sumqx, sumq2);
+            }
+            shift = best_k;
+            wrote = true;
         }
         if (!wrote) { scale = 0.f; shift = M ? 0 : 1; }
         float scales[LANES];
@@ -974,11 +963,9 @@ template <bool M, int VARIANT> struct IQ1 {
 #pragma unroll
                     for (int k = 0; k < 2; ++k) {
                         const bool plus = k == 0 ? shift < 2 : (shift % 2 == 0);
-                        int pg[8];
-                        grid_point<8>(T, (int)index[k], pg);
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            const int c = (pg[j] - 1) / 2;
+                            const unsigned c = (ukey[k] >> (2 * j)) & 3u;
                             const float xx = plus ? (c == 0 ? x_p[0] : c == 1 ? x_p[1] : x_p[2]) : (c == 0 ? x_m[0] : c == 1 ? x_m[1] : x_m[2]);
                             const float q = fmul(xx, ql);
                             const float w = sm.wgt[8 * k + j][tid];
@@ -1016,21 +1003,8 @@ template <bool M, int VARIANT> struct IQ1 {
 // ---- launch ------------------------------------------------------------------------------------------
 const IqTables* device_tables(int device);     // tables.cu; null until sg_tables_install ran on the device
 
-template <class T, int DT, bool IMX>
-__global__ void __launch_bounds__(IQ_TPB) k_quant_iq(const __grid_constant__ Job job, const __grid_constant__ IqTables tabs) {
-    __shared__ typename T::Smem sm;
-    constexpr int LANES = T::LANES;
-    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    long long s = g / LANES;
-    const int sub = (int)(g - s * LANES);
-    const bool valid = s < job.nslabs;
-    if (!valid) s = job.nslabs - 1;
-    const Slab sl = locate<T::SLAB>(job, s);
-    T::template run<DT, IMX>(job, sl, sub, valid, tabs, sm);
-}
-
-// Lattice kernels: CTAs of T::TPB threads, one block of 16 / 32 weights per thread, walking over tiles of T::TPB
-// blocks.  The IQ3 tables are small, so each CTA copies them into shared memory first; the IQ2 tables stay in global
+// Lattice and ternary kernels: CTAs of T::TPB threads, one block of 16 / 32 weights per thread, walking over tiles
+// of T::TPB blocks.  The IQ3 tables are small, so each CTA copies them into shared memory first; the IQ2 tables stay in global
 // memory (they are L2-resident).
 template <class T> struct LatSmem {
     typename T::SM v;
@@ -1081,21 +1055,8 @@ __global__ void __launch_bounds__(128) k_quant_iq4(const __grid_constant__ Job j
 }
 
 template <class T, bool IMX>
-static int launch_iq(const Job& job, int dt, cudaStream_t st, const IqTables& tabs) {
-    const long long threads = job.nslabs * T::LANES;
-    const unsigned grid = (unsigned)((threads + IQ_TPB - 1) / IQ_TPB);
-    if (grid == 0) return SG_OK;
-    switch (dt) {
-        case SG_DT_BF16: k_quant_iq<T, SG_DT_BF16, IMX><<<grid, IQ_TPB, 0, st>>>(job, tabs); break;
-        case SG_DT_F16:  k_quant_iq<T, SG_DT_F16, IMX><<<grid, IQ_TPB, 0, st>>>(job, tabs); break;
-        case SG_DT_F32:  k_quant_iq<T, SG_DT_F32, IMX><<<grid, IQ_TPB, 0, st>>>(job, tabs); break;
-        default: return SG_ERR_ARG;
-    }
-    return cuda_ok(cudaGetLastError());
-}
-template <class T, bool IMX>
 static int launch_lat(const Job& job, int dt, cudaStream_t st, const IqTables& tabs) {
-    const GridTable& tab = tabs.t[Lat<T::TYPE_ID>::TAB];
+    const GridTable& tab = tabs.t[T::TAB];
     const long long threads = job.nslabs * T::LANES;
     if (threads == 0) return SG_OK;
     size_t smem = sizeof(LatSmem<T>);
@@ -1153,10 +1114,10 @@ static int dispatch_iq(int type, int variant, bool imx, int device, const Job& j
         case SG_IQ2_S:   return imx ? launch_lat<Lattice<SG_IQ2_S>, true>(job, dt, st, tabs) : launch_lat<Lattice<SG_IQ2_S>, false>(job, dt, st, tabs);
         case SG_IQ3_XXS: return imx ? launch_lat<Lattice<SG_IQ3_XXS>, true>(job, dt, st, tabs) : launch_lat<Lattice<SG_IQ3_XXS>, false>(job, dt, st, tabs);
         case SG_IQ3_S:   return imx ? launch_lat<Lattice<SG_IQ3_S>, true>(job, dt, st, tabs) : launch_lat<Lattice<SG_IQ3_S>, false>(job, dt, st, tabs);
-        case SG_IQ1_S:   return imx ? launch_iq<IQ1<false, 0>, true>(job, dt, st, tabs) : SG_ERR_IMATRIX;
+        case SG_IQ1_S:   return imx ? launch_lat<IQ1<false, 0>, true>(job, dt, st, tabs) : SG_ERR_IMATRIX;
         case SG_IQ1_M:
-            if (variant == 1) return imx ? launch_iq<IQ1<true, 1>, true>(job, dt, st, tabs) : launch_iq<IQ1<true, 1>, false>(job, dt, st, tabs);
-            return imx ? launch_iq<IQ1<true, 0>, true>(job, dt, st, tabs) : launch_iq<IQ1<true, 0>, false>(job, dt, st, tabs);
+            if (variant == 1) return imx ? launch_lat<IQ1<true, 1>, true>(job, dt, st, tabs) : launch_lat<IQ1<true, 1>, false>(job, dt, st, tabs);
+            return imx ? launch_lat<IQ1<true, 0>, true>(job, dt, st, tabs) : launch_lat<IQ1<true, 0>, false>(job, dt, st, tabs);
         default: return SG_ERR_TYPE;
     }
 }
