@@ -283,6 +283,224 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------------------
+# Coder workloads (not the default): the rANS symbol coder on BASELINE config 3's stream, the QR residual coder and the
+# R2 BF16 base codec on the config-2 tensor.  Kernel times are CUDA-event times of the library calls
+# (seedpack_b200._lib.timed); `e2e` is wall time through the Python classes with host buffers on both sides.
+def _codec_line(args, metric, workload, unit_bytes, kern_ms, e2e_s, h2d, d2h, table, roof, cpu, launches, clocks):
+    peak, peak_kind = peaks()
+    roof = dict(roof, peak=peak, peak_kind=peak_kind, unit="GB/s", frac=roof["achieved"] / peak, bound="hbm", traffic=None)
+    return {"metric": metric, "value": unit_bytes / (kern_ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": kern_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u32", "data": "synthetic", "config": {"workload": workload, "l2": "inputs larger than L2", "kernels": table},
+            "clocks": clocks, "e2e": {"value": unit_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+            "gpu_launches": int(launches), "roofline": roof, "cpu_baseline": cpu}
+
+
+def _timed_steps(args, fn):
+    """fn() once per step after the warm-up steps -> ({kernel: ms per step}, wall seconds per step, clocks)"""
+    import torch
+    from seedpack_b200 import _lib
+    for _ in range(max(args.warmup, 1)):
+        fn()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    _lib.timing_start()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fn()
+    torch.cuda.synchronize()
+    wall = (time.perf_counter() - t0) / args.steps
+    ms = {k: v / args.steps for k, v in _lib.timing_stop().items()}
+    return ms, wall, sampler.summary()
+
+
+def synth_symbols(nsym, seed, device):
+    """BASELINE config 3's stream: blocks of 32 symbols, each block with an alphabet of 4 / 5 / 6 / 8 bits and one of
+    292 context tables; 97 % zeros, the rest discrete Laplace(b = 2) folded into the alphabet"""
+    import torch
+    g = torch.Generator(device=device); g.manual_seed(seed)
+    nb = nsym // 32
+    kind = torch.randint(0, 4, (nb,), generator=g, device=device)
+    tab = (kind * 73 + torch.randint(0, 73, (nb,), generator=g, device=device)).to(torch.int16)
+    mask = torch.tensor([15, 31, 63, 255], device=device)[kind].to(torch.int32)
+    sym = torch.empty(nsym, dtype=torch.uint8, device=device)
+    step = 1 << 24
+    for a in range(0, nsym, step):
+        n = min(step, nsym - a)
+        u = torch.rand(n, generator=g, device=device)
+        mag = torch.floor(-2.0 * torch.log(torch.rand(n, generator=g, device=device).clamp_min(1e-12))).to(torch.int32)
+        sgn = torch.randint(0, 2, (n,), generator=g, device=device, dtype=torch.int32) * 2 - 1
+        v = torch.where(u < 0.97, torch.zeros_like(mag), mag * sgn) & mask[a // 32:(a + n) // 32].repeat_interleave(32)
+        sym[a:a + n] = v.to(torch.uint8)
+    return sym, tab
+
+
+def run_rans(args):
+    import torch
+    from seedpack_b200.rans import RansCodec
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    S, NTAB = args.symbols, 294
+    sym, tab = synth_symbols(S, 1, dev)
+    c = RansCodec(0)
+    state = {}
+
+    def step():
+        r = c.encode(sym, tab, 32, NTAB)
+        out = c.decode(r["stream"], r["off"], tab, 32, S, r["freq"], r["used"], NTAB)
+        state.update(r=r, out=out)
+
+    ms, _, clocks = _timed_steps(args, step)
+    assert torch.equal(state["out"], sym), "round trip failed"
+    coded = state["r"]["total"]
+    kern = sum(ms.values())
+    algo = {"rans_hist": S + S // 16, "rans_encode": S + S // 16 + coded, "scan_gather": 2 * coded, "rans_decode": coded + S // 16 + S}
+    table = {k: {"ms": round(v, 3), "algo_gbs": round(algo[k] / (v * 1e-3) / 1e9, 1)} for k, v in ms.items()}
+    dom = max(ms, key=ms.get)
+    # end to end: symbols and table ids from pinned host memory, coded stream back; then the stream in, symbols back
+    hs, ht = sym.cpu().pin_memory(), tab.cpu().pin_memory()
+    hback = torch.empty(S, dtype=torch.uint8).pin_memory()
+
+    def e2e():
+        ds, dt_ = hs.to(dev, non_blocking=True), ht.to(dev, non_blocking=True)
+        r = c.encode(ds, dt_, 32, NTAB)
+        hstream = r["stream"].cpu()                       # padded to the 16-byte windows the decoder reads
+        hoff = r["off"].cpu()
+        out = c.decode(hstream.to(dev), hoff.to(dev), dt_, 32, S, r["freq"], r["used"], NTAB)
+        hback.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e()
+    t0 = time.perf_counter(); e2e(); e2e_s = time.perf_counter() - t0
+    # CPU baseline: the plain-C restatement of the same coder, one thread, on the first 4 Mi symbols
+    cpu = None
+    try:
+        from oracle import rans as orans
+        n = min(S, 1 << 22)
+        hsym, htab = sym[:n].cpu().numpy(), tab[:n // 32].cpu().numpy().view(np.uint16)
+        from seedpack_b200.rans import normalize
+        counts = np.bincount(np.repeat(htab, 32).astype(np.int64) * 256 + hsym, minlength=NTAB * 256).reshape(NTAB, 256)
+        freq, used = normalize(counts)
+        full = np.zeros((NTAB, 256), np.uint16); full[used] = freq
+        t0 = time.perf_counter()
+        st, off = orans.encode(hsym, htab, 32, 16384, full)
+        back, _ = orans.decode(st, off, htab, 32, n, 16384, full)
+        dtc = time.perf_counter() - t0
+        assert np.array_equal(back, hsym)
+        cpu = {"value": n / dtc / 1e9, "unit": "GB/s", "cores": 1, "kind": "port", "sample": f"first {n} symbols, encode + decode"}
+    except Exception as e:
+        cpu = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+    line = _codec_line(args, "rANS symbol coder GB/s of symbols, histogram + encode + gather + decode",
+                       f"{S} symbols in blocks of 32 with one of {NTAB} tables per block, 97% zeros + Laplace(b=2) on 4/5/6/8-bit alphabets, "
+                       f"segments of 16384, 12 probability bits; coded to {coded} bytes",
+                       S, kern, e2e_s, S + S // 16 + coded, coded + S, table,
+                       {"kernel": dom, "achieved": algo[dom] / (ms[dom] * 1e-3) / 1e9}, cpu, 6, clocks)
+    print(json.dumps(line))
+
+
+def _flip_bytes(a, bs, frac, seed):
+    """one random byte XOR-flipped in `frac` of the blocks of a (BASELINE config 1's non-derivable residuals)"""
+    rng = np.random.default_rng(seed)
+    nb = len(a) // bs
+    pick = rng.choice(nb, max(1, int(nb * frac)), replace=False)
+    a = a.copy()
+    a[pick * bs + rng.integers(0, bs, len(pick))] ^= rng.integers(1, 256, len(pick)).astype(np.uint8)
+    return a
+
+
+def run_qr(args):
+    import torch
+    from seedpack_b200.gpuquant import GPUQuant
+    from seedpack_b200.qr import QRCodec, GRID_TYPES
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    gq, qc = GPUQuant(0), QRCodec(0)
+    K = args.tensors
+    tens = [synth_tensor(1 + k) for k in range(K)]
+    imx = tens[0][1]
+    seed_bytes = np.concatenate([b.view(np.uint8).reshape(-1) for b, _ in tens])
+    xs = [torch.from_numpy(b.view(np.int16)).to(dev).view(torch.bfloat16).reshape(-1) for b, _ in tens]
+    rng = np.random.default_rng(7)
+    imx2 = (imx * np.exp(rng.normal(0, 0.3, imx.shape))).astype(np.float32)      # the file was made with another matrix
+    types = [int(t) for t in args.qr_types.split(",")]
+    table, tot_bytes, tot_ms, tot_wall, launches, dom, clocks = {}, 0, 0.0, 0.0, 0, None, None
+    for T in types:
+        name, qk, bs = QFUN[T]
+        Ps = gq.quantize_tensors(T, [(x, NPR) for x in xs], [imx] * K)
+        Fs = [_flip_bytes(f, bs, 0.005, T + 100 * k) for k, f in enumerate(gq.quantize_tensors(T, [(x, NPR) for x in xs], [imx2] * K))]
+        ioff = 0 if T in GRID_TYPES else -1
+        enc_items = [(Fs[k], Ps[k], k * 2 * NROWS * NPR, 30, NPR, ioff) for k in range(K)]
+        dec_items = [(Ps[k], k * 2 * NROWS * NPR, 30, NPR, ioff) for k in range(K)]
+        F, P = np.concatenate(Fs), np.concatenate(Ps)
+        st = {}
+
+        def step():
+            buf = qc.encode(T, enc_items, seed_bytes, imx if T in GRID_TYPES else None)
+            out = qc.decode(T, buf, dec_items, seed_bytes, imx if T in GRID_TYPES else None)
+            st.update(buf=buf, out=out)
+
+        ms, wall, clocks = _timed_steps(args, step)
+        assert np.array_equal(st["out"].cpu().numpy(), F), f"type {T}: round trip failed"
+        nfile, coded = len(F), len(st["buf"])
+        nw = NROWS * NPR * K
+        algo = {"residual_blocks": 2 * nfile, "qr_hist": 2 * nfile + 2 * nw, "qr_encode": 2 * nfile + 2 * nw + coded,
+                "scan_gather": 2 * coded, "qr_decode": 2 * nfile + 2 * nw + coded}
+        kern = sum(ms.values())
+        table[name] = {"file_bytes": nfile, "coded_bytes": coded, "differing_blocks": float(np.mean(np.any((F != P).reshape(-1, bs), axis=1))),
+                       "ms": {k: round(v, 3) for k, v in ms.items()},
+                       "algo_gbs": {k: round(algo[k] / (v * 1e-3) / 1e9, 1) for k, v in ms.items()}, "e2e_s": round(wall, 4)}
+        k = max(ms, key=ms.get)
+        if dom is None or ms[k] > dom[1]:
+            dom = (f"{k} {name}", ms[k], algo[k])
+        tot_bytes += nfile; tot_ms += kern; tot_wall += wall; launches += 6
+    line = _codec_line(args, "QR residual coder GB/s of tensor bytes, block compare + histogram + encode + gather + decode",
+                       f"one coding batch per type ({', '.join(QFUN[t][0] for t in types)}) of {K} tensors of {NROWS}x{NPR}: file quantised with a "
+                       "perturbed importance matrix and 0.5% of blocks with a flipped byte, prediction with the plain matrix, BF16 seed",
+                       tot_bytes, tot_ms, tot_wall, 2 * tot_bytes + 2 * NROWS * NPR * K * len(types), tot_bytes, table,
+                       {"kernel": dom[0], "achieved": dom[2] / (dom[1] * 1e-3) / 1e9},
+                       {"value": None, "unit": "GB/s", "cores": 0, "kind": "port",
+                        "sample": "no CPU restatement of the QR model is kept; parity is pinned on the reference's own coded batches"},
+                       launches, clocks)
+    print(json.dumps(line))
+
+
+def run_r2(args):
+    import torch
+    from seedpack_b200.bf16v2 import BF16v2, R2Tensors, layout_of
+    torch.cuda.set_device(0)
+    K = args.tensors
+    data = np.concatenate([synth_tensor(1 + k)[0].view(np.uint8).reshape(-1) for k in range(K)])
+    one = len(data) // K
+    layout = layout_of([(f"blk.{k}.ffn_up.weight", k * one, one, NPR) for k in range(K)], len(data))
+    codec = BF16v2(device=0)
+    st = {}
+
+    def step():
+        parts = codec.compress_parts(data, layout)
+        r = R2Tensors(parts, 0)
+        dev, outs = r.decode(range(len(layout["t"])))
+        st.update(parts=parts, dev=dev, outs=outs)
+
+    ms, wall, clocks = _timed_steps(args, step)
+    h = st["dev"].cpu().numpy()
+    for k, (off, nb, _, _) in enumerate(layout["t"]):
+        assert np.array_equal(h[st["outs"][k]:st["outs"][k] + nb], data[off:off + nb]), "round trip failed"
+    coded = len(st["parts"]["stream"])
+    n = len(data)
+    algo = {"r2_stats": 3 * n, "row_hash": n, "r2_hist": n, "r2_encode": n + coded, "scan_gather": 2 * coded, "r2_decode": coded + n}
+    table = {k: {"ms": round(v, 3), "algo_gbs": round(algo[k] / (v * 1e-3) / 1e9, 1)} for k, v in ms.items()}
+    dom = max(ms, key=ms.get)
+    line = _codec_line(args, "R2 BF16 base codec GB/s of BF16 bytes, statistics + row hashes + histogram + encode + gather + decode",
+                       f"{K} BF16 tensors of {NROWS}x{NPR} of one role ({n} bytes), coded to {coded} stream bytes",
+                       n, sum(ms.values()), wall, n + coded, coded + n, table, {"kernel": dom, "achieved": algo[dom] / (ms[dom] * 1e-3) / 1e9},
+                       {"value": None, "unit": "GB/s", "cores": 0, "kind": "port",
+                        "sample": "no CPU restatement of the R2 codec is kept; parity is pinned on the reference's own coded parts"},
+                       8, clocks)
+    print(json.dumps(line))
+
+
 def case_name(t, use):
     return f"{QFUN[t][0]}{'+imx' if use else ''}"
 
@@ -297,6 +515,11 @@ def main():
     ap.add_argument("--ref-rows", type=int, default=0, help="rows of the tensor the CPU baseline quantises per step")
     ap.add_argument("--rows", type=int, default=NROWS, help="rows of the tensor (profiling captures use fewer)")
     ap.add_argument("--only", default="", help="comma-separated launch names to keep, e.g. q4_K+imx,iq2_xs+imx")
+    ap.add_argument("--workload", default="quant", choices=["quant", "rans", "qr", "r2"],
+                    help="quant: the quantiser sweep (the headline); rans / qr / r2: the coders, one GPU")
+    ap.add_argument("--symbols", type=int, default=1 << 30, help="rans: symbols in the stream")
+    ap.add_argument("--tensors", type=int, default=4, help="qr / r2: tensors of the benchmark shape in the batch / file")
+    ap.add_argument("--qr-types", default="8,12,14,17,18", help="qr: ggml type ids, one coding batch each")
     args = ap.parse_args()
     NROWS = args.rows
     if args.only:
@@ -305,6 +528,9 @@ def main():
         assert CASES, "no such launch"
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "quant":
+        if int(os.environ.get("RANK", "0")) == 0:
+            {"rans": run_rans, "qr": run_qr, "r2": run_r2}[args.workload](args)
     else:
         run_ours(args)
 

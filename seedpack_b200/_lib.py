@@ -84,3 +84,38 @@ def lib():
 def check(status, where):
     if status != 0:
         raise SgError(status, where)
+
+
+# ---- optional per-kernel device timing (benchmarks) ------------------------------------------------------------
+import contextlib
+
+_TIMES = None
+
+
+@contextlib.contextmanager
+def timed(name):
+    """with timing_start() active: CUDA-event time of the enclosed launches on torch's current stream, summed per name"""
+    if _TIMES is None:
+        yield
+        return
+    import torch
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    yield
+    e1.record()
+    _TIMES.setdefault(name, []).append((e0, e1))
+
+
+def timing_start():
+    global _TIMES
+    _TIMES = {}
+
+
+def timing_stop():
+    """-> {name: milliseconds} of everything timed since timing_start()"""
+    global _TIMES
+    import torch
+    torch.cuda.synchronize()
+    out = {k: sum(a.elapsed_time(b) for a, b in v) for k, v in (_TIMES or {}).items()}
+    _TIMES = None
+    return out

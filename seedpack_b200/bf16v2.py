@@ -128,15 +128,17 @@ class BF16v2:
         scl = torch.empty(rl, dtype=torch.int8, device=self.device)
         need = self.lib.sg_r2_stats_scratch_bytes(nr, rl)
         scratch = torch.empty(need + 16, dtype=torch.uint8, device=self.device)
-        _lib.check(self.lib.sg_r2_stats(self.device.index, self._st(), _p(d), nr, rl, _p(rfi), _p(cfi), _p(scl), _p(scratch), need),
-                   "sg_r2_stats")
+        with _lib.timed("r2_stats"):
+            _lib.check(self.lib.sg_r2_stats(self.device.index, self._st(), _p(d), nr, rl, _p(rfi), _p(cfi), _p(scl), _p(scratch), need),
+                       "sg_r2_stats")
         return rfi, cfi, scl
 
     def _dups(self, d, rl, host):
         """exact duplicate rows -> (rows kept (sorted), [(dup row, source row)])  (bf16v2.py:246-271)"""
         nr = d.numel() // 2 // rl
         h = torch.empty(nr, dtype=torch.int64, device=self.device)
-        _lib.check(self.lib.sg_row_hash(self.device.index, self._st(), _p(d), nr, rl, _p(h)), "sg_row_hash")
+        with _lib.timed("row_hash"):
+            _lib.check(self.lib.sg_row_hash(self.device.index, self._st(), _p(d), nr, rl, _p(h)), "sg_row_hash")
         h = h.cpu().numpy().view(np.uint64)
         order = np.argsort(h, kind="stable")
         hs = h[order]
@@ -205,8 +207,9 @@ class BF16v2:
             else:
                 rm = torch.zeros(1, dtype=torch.int32, device=self.device)
             tb_d, sg_d = _dev(tb.view(np.uint8), self.device), _dev(sg.view(np.uint8), self.device)
-            _lib.check(self.lib.sg_r2_hist(d, st, _p(dev), _p(tb_d), _p(sg_d), len(sg), _p(rfi), _p(cfi), _p(scl), _p(rm), _p(counts)),
-                       "sg_r2_hist")
+            with _lib.timed("r2_hist"):
+                _lib.check(self.lib.sg_r2_hist(d, st, _p(dev), _p(tb_d), _p(sg_d), len(sg), _p(rfi), _p(cfi), _p(scl), _p(rm), _p(counts)),
+                           "sg_r2_hist")
             devs[gi] = dev
         rowmap = _dev(np.concatenate(rmap_all), self.device) if rmap_all else torch.zeros(1, dtype=torch.int32, device=self.device)
         freq, used = normalize_gpu(counts.cpu().numpy().view(np.uint32).reshape(ntab, 256), 1 << PB)
@@ -219,15 +222,18 @@ class BF16v2:
             tb_d, sg_d = _dev(tb.view(np.uint8), self.device), _dev(sg.view(np.uint8), self.device)
             slots = torch.empty(max(nseg, 1) * cap, dtype=torch.uint8, device=self.device)
             lens = torch.zeros(max(nseg, 1), dtype=torch.int32, device=self.device)
-            _lib.check(self.lib.sg_r2_encode(d, st, _p(devs[gi]), _p(tb_d), _p(sg_d), nseg, _p(rfi), _p(cfi), _p(scl), _p(rowmap), _p(enc),
-                                             _p(slots), cap, _p(lens)), "sg_r2_encode")
+            with _lib.timed("r2_encode"):
+                _lib.check(self.lib.sg_r2_encode(d, st, _p(devs[gi]), _p(tb_d), _p(sg_d), nseg, _p(rfi), _p(cfi), _p(scl), _p(rowmap), _p(enc),
+                                                 _p(slots), cap, _p(lens)), "sg_r2_encode")
             off = torch.empty(nseg + 1, dtype=torch.int64, device=self.device)
-            _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, None, 0, _p(off)), "sg_scan_gather")
+            with _lib.timed("scan_gather"):
+                _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, None, 0, _p(off)), "sg_scan_gather")
             if self._status() & 2:
                 raise RuntimeError("rANS segment overflow")
             total = int(off[-1].item())
             dst = torch.empty(total + 32, dtype=torch.uint8, device=self.device)
-            _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, _p(dst), total, _p(off)), "sg_scan_gather")
+            with _lib.timed("scan_gather"):
+                _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, _p(dst), total, _p(off)), "sg_scan_gather")
             streams.append(dst[:total].cpu().numpy().tobytes())
             lens_all.append(lens[:nseg].cpu().numpy().view(np.uint32))
             devs[gi] = None
@@ -308,9 +314,10 @@ class R2Tensors:
             # caching allocator would be reused by the next upload
             keep = [_dev(sb, self.device), _dev(np.concatenate(in_off), self.device), _dev(np.concatenate(in_end), self.device),
                     _dev(tb.view(np.uint8), self.device), _dev(sg.view(np.uint8), self.device)]
-            _lib.check(self.lib.sg_r2_decode(d, st, _p(keep[0]), _p(keep[1]), _p(keep[2]), _p(dev), _p(keep[3]), _p(keep[4]), len(sg),
-                                             _p(self.rfi), _p(self.cfi), _p(self.scl), _p(self.rowmap), _p(self.enc), _p(self.lut)),
-                       "sg_r2_decode")
+            with _lib.timed("r2_decode"):
+                _lib.check(self.lib.sg_r2_decode(d, st, _p(keep[0]), _p(keep[1]), _p(keep[2]), _p(dev), _p(keep[3]), _p(keep[4]), len(sg),
+                                                 _p(self.rfi), _p(self.cfi), _p(self.scl), _p(self.rowmap), _p(self.enc), _p(self.lut)),
+                           "sg_r2_decode")
         for k, i in enumerate(idxs):
             if i in self.dups:
                 off, nb, rl, _ = t[i]

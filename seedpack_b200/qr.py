@@ -164,9 +164,11 @@ class QRCodec:
         seed = _dev_u8(seed_dev, self.device)
         ne = torch.empty(max(nb, 1), dtype=torch.uint8, device=self.device)
         ndiff = torch.zeros(1, dtype=torch.int64, device=self.device)
-        _lib.check(self.lib.sg_residual_blocks(d, st, _p(F), _p(P), bs, nb, _p(ne), _p(ndiff)), "sg_residual_blocks")
+        with _lib.timed("residual_blocks"):
+            _lib.check(self.lib.sg_residual_blocks(d, st, _p(F), _p(P), bs, nb, _p(ne), _p(ndiff)), "sg_residual_blocks")
         counts = torch.zeros(NTAB2 * 256, dtype=torch.int32, device=self.device)
-        _lib.check(self.lib.sg_qr_hist(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(counts), mv), "sg_qr_hist")
+        with _lib.timed("qr_hist"):
+            _lib.check(self.lib.sg_qr_hist(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(counts), mv), "sg_qr_hist")
         freq, used = normalize(counts.cpu().numpy().astype(np.uint32).reshape(NTAB2, 256))
         enc, _ = self._tables(freq, used, lut=False)
         cap = seg_blocks(T) * (3 * BS[T] if T in GRID_TYPES else (QK[T] + NSB_MAX) * 2) + 1024
@@ -174,10 +176,12 @@ class QRCodec:
         for _ in range(3):
             slots = torch.empty(max(nseg, 1) * cap, dtype=torch.uint8, device=self.device)
             lens = torch.zeros(max(nseg, 1), dtype=torch.int32, device=self.device)
-            _lib.check(self.lib.sg_qr_encode(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(enc), _p(slots),
-                                             cap, _p(lens), mv), "sg_qr_encode")
+            with _lib.timed("qr_encode"):
+                _lib.check(self.lib.sg_qr_encode(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(enc), _p(slots),
+                                                 cap, _p(lens), mv), "sg_qr_encode")
             off = torch.empty(nseg + 1, dtype=torch.int64, device=self.device)
-            _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, None, 0, _p(off)), "sg_scan_gather")
+            with _lib.timed("scan_gather"):
+                _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, None, 0, _p(off)), "sg_scan_gather")
             if not (self._status() & 2):
                 break
             cap *= 2
@@ -185,7 +189,8 @@ class QRCodec:
             raise RuntimeError("QR segment overflow")
         total = int(off[-1].item())
         dst = torch.empty(total + 32, dtype=torch.uint8, device=self.device)
-        _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, _p(dst), total, _p(off)), "sg_scan_gather")
+        with _lib.timed("scan_gather"):
+            _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, _p(dst), total, _p(off)), "sg_scan_gather")
         stream = dst[:total].cpu().numpy().tobytes()
         lens_h = lens[:nseg].cpu().numpy().view(np.uint32)
         out = {"t": store_tables(freq, used), "l": zstd.compress(lens_h.astype(np.uint32).tobytes(), 19), "s": stream}
@@ -219,8 +224,9 @@ class QRCodec:
         sd[:len(s)] = torch.from_numpy(s.copy()).to(self.device)
         F = torch.empty(nb * bs, dtype=torch.uint8, device=self.device)
         off_d = torch.from_numpy(offs.view(np.int64)).to(self.device)
-        _lib.check(self.lib.sg_qr_decode(d, st, T, _p(sd), _p(off_d), _p(P), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(enc), _p(lut), _p(F),
-                                         mv), "sg_qr_decode")
+        with _lib.timed("qr_decode"):
+            _lib.check(self.lib.sg_qr_decode(d, st, T, _p(sd), _p(off_d), _p(P), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(enc), _p(lut), _p(F),
+                                             mv), "sg_qr_decode")
         if self._status() & 4:
             raise ValueError("QR batch: corrupt stream")
         return F

@@ -58,8 +58,9 @@ class RansCodec:
 
     def hist(self, sym, block_tab, block_len, ntab):
         counts = torch.zeros(ntab * 256, dtype=torch.int32, device=self.device)
-        _lib.check(self.lib.sg_rans_hist(self.device.index, self._stream(), _p(sym), _p(block_tab), block_len, sym.numel(), _p(counts)),
-                   "sg_rans_hist")
+        with _lib.timed("rans_hist"):
+            _lib.check(self.lib.sg_rans_hist(self.device.index, self._stream(), _p(sym), _p(block_tab), block_len, sym.numel(), _p(counts)),
+                       "sg_rans_hist")
         return counts
 
     def tables(self, freq_full, lut=True):
@@ -79,18 +80,21 @@ class RansCodec:
         for _ in range(6):
             slots = torch.empty(nseg * cap, dtype=torch.uint8, device=self.device)
             lens = torch.empty(nseg, dtype=torch.int32, device=self.device)
-            _lib.check(self.lib.sg_rans_encode(self.device.index, self._stream(), _p(sym), _p(block_tab), block_len, n, seg_len, PB,
-                                               _p(enc), _p(slots), cap, _p(lens)), "sg_rans_encode")
+            with _lib.timed("rans_encode"):
+                _lib.check(self.lib.sg_rans_encode(self.device.index, self._stream(), _p(sym), _p(block_tab), block_len, n, seg_len, PB,
+                                                   _p(enc), _p(slots), cap, _p(lens)), "sg_rans_encode")
             off = torch.empty(nseg + 1, dtype=torch.int64, device=self.device)
-            _lib.check(self.lib.sg_scan_gather(self.device.index, self._stream(), _p(slots), cap, _p(lens), nseg, None, 0, _p(off)),
-                       "sg_scan_gather")
+            with _lib.timed("scan_gather"):
+                _lib.check(self.lib.sg_scan_gather(self.device.index, self._stream(), _p(slots), cap, _p(lens), nseg, None, 0, _p(off)),
+                           "sg_scan_gather")
             if self.status() & 2:                 # a slot overflowed: retry with twice the room (seedpack/qr.py:1043-1053)
                 cap *= 2
                 continue
             total = int(off[-1].item())
             dst = torch.zeros((total + 15) // 16 * 16 + 16, dtype=torch.uint8, device=self.device)
-            _lib.check(self.lib.sg_scan_gather(self.device.index, self._stream(), _p(slots), cap, _p(lens), nseg, _p(dst), total, _p(off)),
-                       "sg_scan_gather")
+            with _lib.timed("scan_gather"):
+                _lib.check(self.lib.sg_scan_gather(self.device.index, self._stream(), _p(slots), cap, _p(lens), nseg, _p(dst), total, _p(off)),
+                           "sg_scan_gather")
             return dst, off, total
         raise RuntimeError("rANS slots overflowed after 6 doublings")
 
@@ -109,6 +113,7 @@ class RansCodec:
         full[used] = freq
         enc, lut = self.tables(full, lut=True)
         out = torch.empty(nsym, dtype=torch.uint8, device=self.device)
-        _lib.check(self.lib.sg_rans_decode(self.device.index, self._stream(), _p(stream), _p(off), _p(block_tab), block_len, nsym,
-                                           seg_len, PB, _p(enc), _p(lut), _p(out)), "sg_rans_decode")
+        with _lib.timed("rans_decode"):
+            _lib.check(self.lib.sg_rans_decode(self.device.index, self._stream(), _p(stream), _p(off), _p(block_tab), block_len, nsym,
+                                               seg_len, PB, _p(enc), _p(lut), _p(out)), "sg_rans_decode")
         return out
