@@ -446,6 +446,7 @@ def run_qr(args):
         nfile, coded = len(F), len(st["buf"])
         nw = NROWS * NPR * K
         algo = {"residual_blocks": 2 * nfile, "qr_hist": 2 * nfile + 2 * nw, "qr_encode": 2 * nfile + 2 * nw + coded,
+                "qr_stage": 2 * nfile + 2 * nw, "qr_stage_hist": 2 * nfile + 2 * nw, "qr_stage_encode": 2 * nfile + 2 * nw + coded,
                 "scan_gather": 2 * coded, "qr_decode": 2 * nfile + 2 * nw + coded}
         kern = sum(ms.values())
         table[name] = {"file_bytes": nfile, "coded_bytes": coded, "differing_blocks": float(np.mean(np.any((F != P).reshape(-1, bs), axis=1))),

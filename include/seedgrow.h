@@ -202,6 +202,20 @@ SG_API int sg_qr_encode(int device, void *stream, int T, const unsigned char *F,
                         const unsigned char *ne, const unsigned char *seed, const void *tm, const void *sg, int nseg,
                         const float *imx, const void *enc_tab, unsigned char *slots, size_t cap, unsigned *out_len,
                         int mv);
+/* Encoding in two steps, for throughput: the model of a block (fields, predictions, contexts, lattice ranks) does not
+ * depend on the coder's state, so sg_qr_stage runs it once with one lane per BLOCK and writes every block's
+ * (table, symbol) pairs into `stage` (sg_qr_stage_bytes(T, nblocks) bytes, 16-byte aligned, owned by the caller);
+ * sg_qr_stage_hist counts the pairs into counts[294 * 256] (add to what is there), and sg_qr_stage_encode walks
+ * them with one rANS lane per segment.  Same bytes out as sg_qr_hist + sg_qr_encode, which run the model twice
+ * on one lane per segment.  nblocks = blocks of the whole batch.  No counterpart in the reference, which has the
+ * single-pass kernels only (seedpack/qr.py:674-758). */
+SG_API size_t sg_qr_stage_bytes(int T, long long nblocks);
+SG_API int sg_qr_stage(int device, void *stream, int T, const unsigned char *F, const unsigned char *P,
+                       const unsigned char *ne, const unsigned char *seed, const void *tm, const void *sg, int nseg,
+                       const float *imx, int mv, long long nblocks, void *stage, size_t stage_bytes);
+SG_API int sg_qr_stage_hist(int device, void *stream, int T, long long nblocks, const void *stage, unsigned *counts);
+SG_API int sg_qr_stage_encode(int device, void *stream, int T, long long nblocks, const void *stage, const void *sg,
+                              int nseg, const void *enc_tab, unsigned char *slots, size_t cap, unsigned *out_len);
 SG_API int sg_qr_decode(int device, void *stream, int T, const unsigned char *in, const unsigned long long *off,
                         const unsigned char *P, const unsigned char *seed, const void *tm, const void *sg, int nseg,
                         const float *imx, const void *enc_tab, const unsigned char *lut, unsigned char *F, int mv);

@@ -52,6 +52,10 @@ SIGNATURES = {
     "sg_qr_hist": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I]),
     "sg_qr_encode": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _Z, _P, _I]),
     "sg_qr_decode": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I]),
+    "sg_qr_stage_bytes": (_Z, [_I, _L]),
+    "sg_qr_stage": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _L, _P, _Z]),
+    "sg_qr_stage_hist": (_I, [_I, _P, _I, _L, _P, _P]),
+    "sg_qr_stage_encode": (_I, [_I, _P, _I, _L, _P, _P, _I, _P, _P, _Z, _P]),
     "sg_r2_hist": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P]),
     "sg_r2_encode": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _Z, _P]),
     "sg_r2_decode": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P]),

@@ -37,12 +37,15 @@ template <class E> SG_DEVINL void field_symbols(int kd, int any, int tv, int dl,
 
 // ---- one coder for the three passes ---------------------------------------------------------------------------
 struct Coder {
-    int mode;                       // 0 histogram, 1 encode (symbols arrive in reverse decode order), 2 decode
+    int mode;                       // 0 histogram, 1 encode (symbols arrive in reverse decode order), 2 decode,
+                                    // 3 stage: like encode, but the (table, symbol) pairs are only written down
     unsigned* counts;
+    unsigned* stage; int nstaged;
     const RansSym* enc; const uchar* lut;
     unsigned x; ByteWriterDown wr; ByteReaderUp rd; uchar* slot; bool ovf;
     SG_DEVINL void sym(int tab, int& s) {
         if (mode == 0) { atomicAdd(counts + tab * 256 + s, 1u); return; }
+        if (mode == 3) { stage[nstaged++] = (unsigned)(tab * 256 + s); return; }
         if (mode == 1) {
             if (ovf) return;
             rans_put<12>(x, wr, enc[tab * 256 + s]);
@@ -220,7 +223,7 @@ struct Args {
 // scalar-code types: the codes of one differing block, forwards (histogram, decode) or backwards (encode)
 SG_DEVINL void scalar_codes(Coder& c, int T, int mv, uchar* fb, const uchar* pb, const int* tv, const Setup& u, long long gw0) {
     const long long col0 = u.m.cols > 0 ? gw0 % u.m.cols : 0;
-    const bool fwd = c.mode != 1, dec = c.mode == 2;
+    const bool fwd = c.mode == 0 || c.mode == 2, dec = c.mode == 2;
     int tsub = -1; float ta = 0.f, tc = 0.f;
     for (int i = 0; i < u.qk; ++i) {
         const int w = fwd ? i : u.qk - 1 - i;
@@ -348,6 +351,221 @@ __global__ void __launch_bounds__(QR_TPB) k_qr_dec(const Args a, const uchar* __
     if (c.rd.over || c.x != RANS_L || c.rd.p != c.rd.end) atomicOr(status, SG_ST_CORRUPT);
 }
 
+// ---- decoder of the scalar-code types: a warp per segment ------------------------------------------------------------
+// A segment is one rANS chain, so its symbols come out one after the other; but what a block's code symbols are coded
+// WITH (context, predicted code, sign) depends only on the seed, the prediction and the block's scale fields, which
+// are decoded first.  So the warp decodes flag and fields in lockstep (every lane runs the same chain on the same
+// bytes, which costs what one lane would), then its lanes work out contexts and predictions of the block's weights
+// side by side into shared memory, the chain runs over the staged contexts, and the lanes put the codes together.
+// Table lookups for symbol 0 (by far the most frequent: cum = 0, freq from a small table in shared memory) stay off
+// global memory.
+constexpr int DW_WARPS = 4;
+struct DecWarpSmem {
+    unsigned fblk[56], pblk[56];            // the block being rebuilt / its prediction (block sizes <= 210 bytes)
+    unsigned short ctx[256];
+    short pred[256];
+    signed char sgn[256];
+    uchar sym[256];
+};
+struct WarpDec {
+    unsigned x; ByteReaderUp rd;
+    const RansSym* enc; const uchar* lut; const unsigned short* f0;
+    SG_DEVINL int get(int tab) {
+        const unsigned slot = x & 4095u, f = f0[tab];
+        if (slot < f) {                     // symbol 0
+            x = f * (x >> 12) + slot;
+#pragma unroll 1
+            for (int guard = 0; guard < 4 && x < RANS_L; ++guard) x = (x << 8) | rd.get();
+            return 0;
+        }
+        return (int)rans_get<12>(x, rd, lut + ((size_t)tab << 12), enc + tab * 256);
+    }
+};
+SG_DEVINL void or_byte(unsigned* blk, int i, unsigned v) { atomicOr(blk + (i >> 2), (v & 255u) << (8 * (i & 3))); }
+// put_code with the bits OR-ed into a zeroed block in shared memory, safe for lanes that share a byte
+SG_DEVINL void put_code_shared(int T, unsigned* blk, int w, int q) {
+    const CodeLoc L = code_loc(T, w);
+    if (T == 8) { or_byte(blk, L.lo_byte, (unsigned)q); return; }
+    if (L.hi_bits) {
+        or_byte(blk, L.lo_byte, (unsigned)((q & ((1 << L.lo_bits) - 1)) << L.lo_shift));
+        or_byte(blk, L.hi_byte, (unsigned)(((q >> L.lo_bits) & ((1 << L.hi_bits) - 1)) << L.hi_shift));
+    } else if (L.lo_bits == 2) or_byte(blk, L.lo_byte, (unsigned)((q & 3) << L.lo_shift));
+    else or_byte(blk, L.lo_byte, (unsigned)(q << L.lo_shift));
+}
+
+__global__ void __launch_bounds__(DW_WARPS * 32) k_qr_dec_warp(const Args a, const uchar* __restrict__ in, const unsigned long long* __restrict__ off,
+                                                               const RansSym* __restrict__ enc, const uchar* __restrict__ lut,
+                                                               uchar* __restrict__ F, int* __restrict__ status) {
+    __shared__ unsigned short f0[NTAB2];
+    __shared__ DecWarpSmem wsm[DW_WARPS];
+    for (int t = threadIdx.x; t < NTAB2; t += blockDim.x) f0[t] = (unsigned short)(enc[t * 256].fc & 0xffffu);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, s = blockIdx.x * DW_WARPS + (threadIdx.x >> 5);
+    if (s >= a.nseg) return;
+    DecWarpSmem& m = wsm[threadIdx.x >> 5];
+    const int T = a.T, mv = a.mv;
+    const Setup u = setup(T, a.seed, a.tm, a.sg, s);
+    WarpDec c; c.enc = enc; c.lut = lut; c.f0 = f0;
+    c.rd.init(in + off[s], in + off[s + 1]);
+    c.x = rans_init(c.rd);
+    uchar* fb = reinterpret_cast<uchar*>(m.fblk);
+    const uchar* pbs = reinterpret_cast<const uchar*>(m.pblk);
+    int prev = 1;
+    for (long long b = u.g.b0; b < u.g.b0 + u.g.nb; ++b) {
+        const uchar* pg = a.P + b * u.bs;
+        uchar* fg = F + b * u.bs;
+        const int eq = c.get(FLAG + prev);
+        prev = eq;
+        if (eq) { for (int i = lane; i < u.bs; i += 32) fg[i] = pg[i]; continue; }
+        __syncwarp();
+        for (int i = lane; i < 56; i += 32) m.fblk[i] = 0;
+        for (int i = lane; i < u.bs; i += 32) reinterpret_cast<uchar*>(m.pblk)[i] = pg[i];
+        __syncwarp();
+        int tv[MAXF], pv[MAXF];
+        unpack_fields(T, pbs, pv);
+        int any = 0;
+        for (int k = 0; k < u.nf; ++k) {
+            const int kd = fkind(T, k);
+            const int pr = fpred(T, mv, pv, k, k > 0 ? tv[0] : 0, k > 1 ? tv[1] : 0);
+            const int sym = c.get(fctx(kd, any));
+            int t;
+            if (kd < 2 && sym == 128) { const int lo = c.get(FESC_LO), hi = c.get(FESC_HI); t = lo | (hi << 8); }
+            else {
+                t = pr + (int)(signed char)sym;
+                if (kd < 2) t &= 0xffff;
+                else if (T == 14) t = (int)(signed char)(t & 255);
+            }
+            tv[k] = t; any |= t != pr;
+        }
+        if (lane == 0) pack_fields(T, fb, tv);
+        // contexts and predictions of the block's weights, side by side
+        const long long gw0 = (b - u.m.blk0) * u.qk;
+        const long long col0 = u.m.cols > 0 ? gw0 % u.m.cols : 0;
+        for (int w = lane; w < u.qk; w += 32) {
+            float ta, tc;
+            wscale(T, tv, w / u.sublen, ta, tc);
+            float xv, hv; seed_val(u.m.seed_type, u.sbase, gw0 + w, xv, hv, u.m.cols);
+            int r, sgn, ctx; predict_code(T, ta, tc, pbs, w, xv, hv, u.hboff, r, sgn, ctx, mv, pos8(col0 + w, u.m.cols));
+            m.ctx[w] = (unsigned short)ctx; m.pred[w] = (short)r; m.sgn[w] = (signed char)sgn;
+        }
+        __syncwarp();
+        for (int w = 0; w < u.qk; ++w) {
+            const int sy = c.get(m.ctx[w]);
+            if (lane == 0) m.sym[w] = (uchar)sy;
+        }
+        __syncwarp();
+        for (int w = lane; w < u.qk; w += 32) {
+            int q = m.pred[w] + m.sgn[w] * (int)(signed char)m.sym[w];
+            if (T == 8) q = (int)(signed char)(q & 255);
+            put_code_shared(T, m.fblk, w, q);
+        }
+        __syncwarp();
+        for (int i = lane; i < u.bs; i += 32) fg[i] = fb[i];
+        if (c.rd.over) break;
+    }
+    if (lane == 0 && (c.rd.over || c.x != RANS_L || c.rd.p != c.rd.end)) atomicOr(status, SG_ST_CORRUPT);
+}
+
+// ---- encoding in two steps ---------------------------------------------------------------------------------------
+// The model (fields, predictions, contexts, lattice ranks) of a block does not depend on the coder's state, only the
+// rANS walk does.  So one lane per BLOCK first writes the block's (table, symbol) pairs down in the order the encoder
+// consumes them; the histogram is a count over those pairs, and the coder proper is one lane per segment walking
+// staged pairs.  The model runs once instead of twice, on seg_blocks(T) times as many lanes.
+// Staging: cnt[b] pairs of block b at stage[b * capb ...], a pair is table * 256 + symbol.
+__global__ void __launch_bounds__(QR_TPB) k_qr_stage(const Args a, int segb, unsigned* __restrict__ stage, unsigned short* __restrict__ cnt,
+                                                     int capb) {
+    const long long lane = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int s = (int)(lane / segb), j = (int)(lane % segb);
+    if (s >= a.nseg) return;
+    const int T = a.T, mv = a.mv;
+    const Setup u = setup(T, a.seed, a.tm, a.sg, s);
+    if (j >= u.g.nb) return;
+    const long long b = u.g.b0 + j;
+    const float* im = u.m.imx_off >= 0 ? a.imx + u.m.imx_off : nullptr;
+    Coder c; c.mode = 3; c.stage = stage + (size_t)b * capb; c.nstaged = 0; c.ovf = false;
+    const int eq = !a.ne[b];
+    const int prev = j > 0 ? !a.ne[b - 1] : 1;
+    if (eq) c.put(FLAG + prev, 1);
+    else {
+        const uchar* fb = a.F + b * u.bs; const uchar* pb = a.P + b * u.bs;
+        int tv[MAXF], pv[MAXF];
+        unpack_fields(T, fb, tv); unpack_fields(T, pb, pv);
+        const long long gw0 = (b - u.m.blk0) * u.qk;
+        if (is_grid(T)) grid_code(c, T, mv, const_cast<uchar*>(fb), pb, tv, a.gk, gw0, u.m.seed_type, u.sbase, u.m.cols, im, gtab);
+        else scalar_codes(c, T, mv, const_cast<uchar*>(fb), pb, tv, u, gw0);
+        int dl[MAXF], anyk[MAXF], any = 0;
+        for (int k = 0; k < u.nf; ++k) {
+            dl[k] = tv[k] - fpred(T, mv, pv, k, tv[0], u.nf > 1 ? tv[1] : 0);
+            anyk[k] = any; any |= dl[k] != 0;
+        }
+        for (int k = u.nf - 1; k >= 0; --k) {
+            const int kd = fkind(T, k);
+            if (kd < 2 && (dl[k] < -127 || dl[k] > 127)) { c.put(FESC_HI, tv[k] >> 8); c.put(FESC_LO, tv[k] & 255); c.put(fctx(kd, anyk[k]), 128); }
+            else c.put(fctx(kd, anyk[k]), dl[k] & 255);
+        }
+        c.put(FLAG + prev, 0);
+    }
+    cnt[b] = (unsigned short)c.nstaged;
+}
+
+// counts over the staged pairs, equal pairs of a warp added once.  A warp takes 32 blocks at a time: blocks with a
+// single pair (equal to their prediction: just the flag) are counted one per lane, the others one after the other
+// by the whole warp.
+__global__ void __launch_bounds__(256) k_qr_stage_hist(long long nblocks, const unsigned* __restrict__ stage, const unsigned short* __restrict__ cnt,
+                                                        int capb, unsigned* __restrict__ counts) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    auto add = [&](unsigned e, bool live) {
+        const unsigned peers = __match_any_sync(0xffffffffu, live ? e : 0xffffffffu);
+        if (live && lane == __ffs(peers) - 1) atomicAdd(counts + e, (unsigned)__popc(peers));
+    };
+    for (long long b0 = warp * 32; b0 < nblocks; b0 += nwarps * 32) {
+        const long long b = b0 + lane;
+        const int n = b < nblocks ? cnt[b] : 0;
+        add(n == 1 ? stage[(size_t)b * capb] : 0u, n == 1);
+        unsigned many = __ballot_sync(0xffffffffu, n > 1);
+        while (many) {
+            const int src = __ffs(many) - 1;
+            many &= many - 1;
+            const int nn = __shfl_sync(0xffffffffu, n, src);
+            const unsigned* p = stage + (size_t)(b0 + src) * capb;
+            for (int i0 = 0; i0 < nn; i0 += 32) add(i0 + lane < nn ? p[i0 + lane] : 0u, i0 + lane < nn);
+        }
+    }
+}
+
+// the coder proper: one lane per segment, blocks last to first, each block's staged pairs in order
+__global__ void __launch_bounds__(QR_TPB) k_qr_stage_code(const SG* __restrict__ sg, int nseg, const unsigned* __restrict__ stage,
+                                                           const unsigned short* __restrict__ cnt, int capb, const RansSym* __restrict__ enc,
+                                                           uchar* __restrict__ out, size_t cap, unsigned* __restrict__ out_len) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= nseg) return;
+    const SG g = sg[s];
+    uchar* slot = out + (size_t)s * cap;
+    ByteWriterDown wr; wr.init(slot + cap);
+    unsigned x = RANS_L;
+    bool ovf = false;
+    for (long long b = g.b0 + g.nb - 1; b >= g.b0 && !ovf; --b) {
+        const int n = cnt[b];
+        const unsigned* p = stage + (size_t)b * capb;
+        int i = 0;
+        for (; i + 4 <= n; i += 4) {            // table entries do not depend on the coder state: four loads in flight
+            const uint4 e4 = *reinterpret_cast<const uint4*>(p + i);
+            const RansSym s0 = enc[e4.x], s1 = enc[e4.y], s2 = enc[e4.z], s3 = enc[e4.w];
+            rans_put<12>(x, wr, s0); rans_put<12>(x, wr, s1); rans_put<12>(x, wr, s2); rans_put<12>(x, wr, s3);
+            if (wr.ptr() < slot + 64) { ovf = true; break; }
+        }
+        for (; i < n && !ovf; ++i) {
+            rans_put<12>(x, wr, enc[p[i]]);
+            if (wr.ptr() < slot + 64) ovf = true;
+        }
+    }
+    if (ovf) { out_len[s] = 0xffffffffu; return; }
+    rans_flush(x, wr);
+    wr.flush(slot);
+    out_len[s] = (unsigned)(slot + cap - wr.ptr());
+}
+
 }  // namespace qr
 }  // namespace sg
 
@@ -419,7 +637,75 @@ extern "C" int sg_qr_decode(int device, void* stream, int T, const unsigned char
     if (nseg == 0) return SG_OK;
     rc = use_device(device);
     if (rc != SG_OK) return rc;
-    k_qr_dec<<<(nseg + QR_TPB - 1) / QR_TPB, QR_TPB, grid_smem(T), (cudaStream_t)stream>>>(a, in, off, (const RansSym*)enc_tab, lut, F,
-                                                                                       status_word(device));
+    if (qr::is_grid(T))
+        k_qr_dec<<<(nseg + QR_TPB - 1) / QR_TPB, QR_TPB, grid_smem(T), (cudaStream_t)stream>>>(a, in, off, (const RansSym*)enc_tab, lut, F,
+                                                                                           status_word(device));
+    else
+        k_qr_dec_warp<<<(nseg + DW_WARPS - 1) / DW_WARPS, DW_WARPS * 32, 0, (cudaStream_t)stream>>>(a, in, off, (const RansSym*)enc_tab, lut, F,
+                                                                                                 status_word(device));
+    return cuda_ok(cudaGetLastError());
+}
+
+// pairs one block can produce: flag + fields (an escaped field takes three) + codes, or for a lattice type per unit of
+// 8 weights the ranks (an escaped rank takes three), 8 signs and a shift bit; rounded up to a multiple of 4
+static int stage_capb(int T) {
+    int qk, bs;
+    if (sg_type_info(T, &qk, &bs) != SG_OK) return 0;
+    const int nf = qr::nfield(T);
+    const int n = 1 + 3 * nf + (qr::is_grid(T) ? 32 * (2 * 3 + 8 + 1) : qk);
+    return (n + 3) / 4 * 4;
+}
+static size_t stage_cnt_bytes(long long nblocks) { return ((size_t)nblocks * 2 + 255) / 256 * 256; }
+
+extern "C" size_t sg_qr_stage_bytes(int T, long long nblocks) {
+    const int capb = stage_capb(T);
+    if (!capb || nblocks < 0) return 0;
+    return stage_cnt_bytes(nblocks) + (size_t)nblocks * capb * 4;
+}
+
+extern "C" int sg_qr_stage(int device, void* stream, int T, const unsigned char* F, const unsigned char* P, const unsigned char* ne,
+                           const unsigned char* seed, const void* tm, const void* sgp, int nseg, const float* imx, int mv,
+                           long long nblocks, void* stage, size_t stage_bytes) {
+    Args a;
+    int rc = qr_args(device, a, T, F, P, ne, seed, tm, sgp, nseg, imx, mv);
+    if (rc != SG_OK) return rc;
+    if (!F || !ne || !stage || nblocks < 0) return SG_ERR_ARG;
+    if ((uintptr_t)stage % 16) return SG_ERR_ALIGN;
+    if (stage_bytes < sg_qr_stage_bytes(T, nblocks)) return SG_ERR_SCRATCH;
+    if (nseg == 0) return SG_OK;
+    rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    const int segb = 16384 / qr::qk_of(T) > 16 ? 16384 / qr::qk_of(T) : 16, capb = stage_capb(T);      // seg_blocks, qr.py:952-954
+    const long long lanes = (long long)nseg * segb;
+    k_qr_stage<<<(unsigned)((lanes + QR_TPB - 1) / QR_TPB), QR_TPB, grid_smem(T), (cudaStream_t)stream>>>(
+        a, segb, (unsigned*)((uchar*)stage + stage_cnt_bytes(nblocks)), (unsigned short*)stage, capb);
+    return cuda_ok(cudaGetLastError());
+}
+
+extern "C" int sg_qr_stage_hist(int device, void* stream, int T, long long nblocks, const void* stage, unsigned* counts) {
+    const int capb = stage_capb(T);
+    if (!capb) return SG_ERR_TYPE;
+    if (!stage || !counts || nblocks < 0) return SG_ERR_ARG;
+    if (nblocks == 0) return SG_OK;
+    int rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    const long long want = (nblocks + 255) / 256;
+    k_qr_stage_hist<<<(unsigned)(want < 148 * 8 ? want : 148 * 8), 256, 0, (cudaStream_t)stream>>>(
+        nblocks, (const unsigned*)((const uchar*)stage + stage_cnt_bytes(nblocks)), (const unsigned short*)stage, capb, counts);
+    return cuda_ok(cudaGetLastError());
+}
+
+extern "C" int sg_qr_stage_encode(int device, void* stream, int T, long long nblocks, const void* stage, const void* sgp, int nseg,
+                                  const void* enc_tab, unsigned char* slots, size_t cap, unsigned* out_len) {
+    const int capb = stage_capb(T);
+    if (!capb) return SG_ERR_TYPE;
+    if (!stage || !sgp || !enc_tab || !slots || !out_len || nseg < 0 || nblocks < 0) return SG_ERR_ARG;
+    if (cap < 128 || cap % 16 || (uintptr_t)slots % 16 || (uintptr_t)stage % 16) return SG_ERR_ALIGN;
+    if (nseg == 0) return SG_OK;
+    int rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    k_qr_stage_code<<<(nseg + QR_TPB - 1) / QR_TPB, QR_TPB, 0, (cudaStream_t)stream>>>(
+        (const SG*)sgp, nseg, (const unsigned*)((const uchar*)stage + stage_cnt_bytes(nblocks)), (const unsigned short*)stage, capb,
+        (const RansSym*)enc_tab, slots, cap, out_len);
     return cuda_ok(cudaGetLastError());
 }

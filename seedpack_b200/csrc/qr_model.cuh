@@ -55,7 +55,7 @@ SG_DEVINL int u16(const uchar* b) { return b[0] | (b[1] << 8); }
 SG_DEVINL unsigned u32(const uchar* b) { return b[0] | (b[1] << 8) | (b[2] << 16) | ((unsigned)b[3] << 24); }
 SG_DEVINL float h2f(const uchar* p) { return h2fv((unsigned)u16(p)); }
 
-SG_DEVINL int qk_of(int T) { return (T == 2 || T == 3 || T == 6 || T == 7 || T == 8 || T == 20) ? 32 : T == 42 ? 64 : 256; }
+__host__ SG_DEVINL int qk_of(int T) { return (T == 2 || T == 3 || T == 6 || T == 7 || T == 8 || T == 20) ? 32 : T == 42 ? 64 : 256; }
 SG_DEVINL int bs_of(int T) {
     switch (T) { case 2: return 18; case 3: return 20; case 6: return 22; case 7: return 24; case 8: return 34; case 10: return 84;
                  case 11: return 110; case 12: return 144; case 13: return 176; case 14: return 210; case 20: return 18;
@@ -63,7 +63,7 @@ SG_DEVINL int bs_of(int T) {
                  case 19: return 50; case 21: return 110; case 22: return 82; case 29: return 56; }
     return 1;
 }
-SG_DEVINL bool is_grid(int T) { return T == 16 || T == 17 || T == 18 || T == 19 || T == 21 || T == 22 || T == 29; }
+__host__ SG_DEVINL bool is_grid(int T) { return T == 16 || T == 17 || T == 18 || T == 19 || T == 21 || T == 22 || T == 29; }
 SG_DEVINL int qmin_of(int T) { return T == 8 ? -128 : 0; }
 SG_DEVINL int qmax_of(int T) {
     switch (T) { case 10: case 42: return 3; case 11: return 7; case 6: case 7: case 13: return 31; case 14: return 63; case 8: return 127; }
@@ -131,7 +131,7 @@ SG_DEVINL void put_code(int T, uchar* b, int w, int q) {
 // ---- scale fields ------------------------------------------------------------------------------------------
 // A block's scale fields as an integer vector: [0] fp16 scale (bits), [1] fp16 min where the type has one, then
 // the sub-block scales (and sub-block mins).  unpack_fields / pack_fields are inverse on every valid block.
-SG_DEVINL int nfield(int T) {
+__host__ SG_DEVINL int nfield(int T) {
     switch (T) { case 2: case 6: case 8: case 20: case 42: return 1; case 3: case 7: return 2; case 10: return 34;
                  case 11: case 14: return 17; case 12: case 13: return 18; case 23: return 9;
                  case 16: case 18: case 19: case 21: return 9; case 17: case 22: case 29: return 17; }

@@ -109,9 +109,12 @@ def _gather(arrs, device):
 
 
 class QRCodec:
-    def __init__(self, device=None):
+    def __init__(self, device=None, staged=True):
+        """staged: run the model once with one lane per block and code from the staged (table, symbol) pairs
+        (sg_qr_stage*); False: the single-pass kernels, one lane per segment, as the reference has them"""
         self.device = torch.device("cuda", torch.cuda.current_device() if device is None else device)
         self.lib = _lib.lib()
+        self.staged = staged
 
     def _stream(self):
         return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
@@ -167,8 +170,19 @@ class QRCodec:
         with _lib.timed("residual_blocks"):
             _lib.check(self.lib.sg_residual_blocks(d, st, _p(F), _p(P), bs, nb, _p(ne), _p(ndiff)), "sg_residual_blocks")
         counts = torch.zeros(NTAB2 * 256, dtype=torch.int32, device=self.device)
-        with _lib.timed("qr_hist"):
-            _lib.check(self.lib.sg_qr_hist(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(counts), mv), "sg_qr_hist")
+        stage = None
+        if self.staged:            # the model once, one lane per block; histogram and coder work on the staged pairs
+            nstage = self.lib.sg_qr_stage_bytes(T, nb)
+            stage = torch.empty(max(nstage, 16), dtype=torch.uint8, device=self.device)
+            with _lib.timed("qr_stage"):
+                _lib.check(self.lib.sg_qr_stage(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), mv, nb, _p(stage),
+                                                nstage), "sg_qr_stage")
+            with _lib.timed("qr_stage_hist"):
+                _lib.check(self.lib.sg_qr_stage_hist(d, st, T, nb, _p(stage), _p(counts)), "sg_qr_stage_hist")
+        else:
+            with _lib.timed("qr_hist"):
+                _lib.check(self.lib.sg_qr_hist(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(counts), mv),
+                           "sg_qr_hist")
         freq, used = normalize(counts.cpu().numpy().astype(np.uint32).reshape(NTAB2, 256))
         enc, _ = self._tables(freq, used, lut=False)
         cap = seg_blocks(T) * (3 * BS[T] if T in GRID_TYPES else (QK[T] + NSB_MAX) * 2) + 1024
@@ -176,9 +190,14 @@ class QRCodec:
         for _ in range(3):
             slots = torch.empty(max(nseg, 1) * cap, dtype=torch.uint8, device=self.device)
             lens = torch.zeros(max(nseg, 1), dtype=torch.int32, device=self.device)
-            with _lib.timed("qr_encode"):
-                _lib.check(self.lib.sg_qr_encode(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(enc), _p(slots),
-                                                 cap, _p(lens), mv), "sg_qr_encode")
+            if self.staged:
+                with _lib.timed("qr_stage_encode"):
+                    _lib.check(self.lib.sg_qr_stage_encode(d, st, T, nb, _p(stage), _p(sg_d), nseg, _p(enc), _p(slots), cap, _p(lens)),
+                               "sg_qr_stage_encode")
+            else:
+                with _lib.timed("qr_encode"):
+                    _lib.check(self.lib.sg_qr_encode(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(enc),
+                                                     _p(slots), cap, _p(lens), mv), "sg_qr_encode")
             off = torch.empty(nseg + 1, dtype=torch.int64, device=self.device)
             with _lib.timed("scan_gather"):
                 _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, None, 0, _p(off)), "sg_scan_gather")

@@ -118,3 +118,21 @@ def test_grid_decode_of_reference_batch_restores_file(T, mv):
     _, dec = _grid_items(T)
     out = c.decode(T, GG[f"B_{T}_{mv}"].tobytes(), dec, GG["seed_bits"].view(np.uint8), GG["imx"])
     assert np.array_equal(out.cpu().numpy(), GG[f"F_{T}"])
+
+
+@pytest.mark.parametrize("T", TYPES)
+def test_single_pass_and_staged_encoders_agree(T):
+    """sg_qr_hist + sg_qr_encode (one lane per segment) and sg_qr_stage* (one lane per block, then the coder) give the
+    same batch"""
+    from seedpack_b200.qr import QRCodec
+    enc, _ = _items(T)
+    seed = G["seed_bits"].view(np.uint8)
+    assert QRCodec(staged=False).encode(T, enc, seed, None, mv=2) == QRCodec(staged=True).encode(T, enc, seed, None, mv=2)
+
+
+@pytest.mark.parametrize("T", GTYPES)
+def test_grid_single_pass_and_staged_encoders_agree(T):
+    from seedpack_b200.qr import QRCodec
+    enc, _ = _grid_items(T)
+    seed = GG["seed_bits"].view(np.uint8)
+    assert QRCodec(staged=False).encode(T, enc, seed, GG["imx"], mv=2) == QRCodec(staged=True).encode(T, enc, seed, GG["imx"], mv=2)
