@@ -360,25 +360,51 @@ __global__ void __launch_bounds__(QR_TPB) k_qr_dec(const Args a, const uchar* __
 // Table lookups for symbol 0 (by far the most frequent: cum = 0, freq from a small table in shared memory) stay off
 // global memory.
 constexpr int DW_WARPS = 4;
-struct DecWarpSmem {
+struct __align__(8) DecWarpSmem {
     unsigned fblk[56], pblk[56];            // the block being rebuilt / its prediction (block sizes <= 210 bytes)
     unsigned short ctx[256];
     short pred[256];
     signed char sgn[256];
     uchar sym[256];
 };
+// the decoder's state and byte source: bytes come through a 64-bit register refilled every 8 bytes, reads past the
+// end give zeros and set `over`
 struct WarpDec {
-    unsigned x; ByteReaderUp rd;
+    unsigned x;
+    unsigned long long buf; int nbuf;
+    const uchar* p; const uchar* end; bool over;
     const RansSym* enc; const uchar* lut; const unsigned short* f0;
+    SG_DEVINL void fill() {
+        buf = 0;
+        const long long left = end - p;
+        if (left <= 0) { over = true; nbuf = 8; return; }
+        const int n = left < 8 ? (int)left : 8;
+        for (int i = 0; i < n; ++i) buf |= (unsigned long long)p[i] << (56 - 8 * i);
+        p += n; nbuf = n;
+    }
+    SG_DEVINL unsigned byte() {
+        if (nbuf == 0) fill();
+        const unsigned b = (unsigned)(buf >> 56);
+        buf <<= 8; --nbuf;
+        return b;
+    }
+    SG_DEVINL void init(const uchar* b, const uchar* e) {
+        p = b; end = e; over = false; nbuf = 0; buf = 0; x = 0;
+        for (int i = 0; i < 4; ++i) x = (x << 8) | byte();
+    }
+    SG_DEVINL bool finished() const { return !over && x == RANS_L && p - nbuf == end; }
     SG_DEVINL int get(int tab) {
         const unsigned slot = x & 4095u, f = f0[tab];
-        if (slot < f) {                     // symbol 0
-            x = f * (x >> 12) + slot;
-#pragma unroll 1
-            for (int guard = 0; guard < 4 && x < RANS_L; ++guard) x = (x << 8) | rd.get();
-            return 0;
+        int s = 0;
+        if (slot < f) x = f * (x >> 12) + slot;                  // symbol 0: cum = 0
+        else {
+            s = lut[((size_t)tab << 12) + slot];
+            const unsigned fc = enc[tab * 256 + s].fc;
+            x = (fc & 0xffffu) * (x >> 12) + slot - (fc >> 16);
         }
-        return (int)rans_get<12>(x, rd, lut + ((size_t)tab << 12), enc + tab * 256);
+#pragma unroll 1
+        for (int guard = 0; guard < 4 && x < RANS_L; ++guard) x = (x << 8) | byte();
+        return s;
     }
 };
 SG_DEVINL void or_byte(unsigned* blk, int i, unsigned v) { atomicOr(blk + (i >> 2), (v & 255u) << (8 * (i & 3))); }
@@ -393,33 +419,268 @@ SG_DEVINL void put_code_shared(int T, unsigned* blk, int w, int q) {
     else or_byte(blk, L.lo_byte, (unsigned)(q << L.lo_shift));
 }
 
+// W lanes per segment, 32 / W segments per warp.  A chain instruction issued by a warp advances 32 / W chains, so a
+// small W wastes fewer issue slots on the lockstep parts, a large W spreads the per-weight work wider.  The warp's
+// control flow is kept uniform (every segment of the warp is at its j-th block; segments whose block equals its
+// prediction, or that have ended, sit the phases out), so the lane groups stay converged.
+template <int W>
 __global__ void __launch_bounds__(DW_WARPS * 32) k_qr_dec_warp(const Args a, const uchar* __restrict__ in, const unsigned long long* __restrict__ off,
                                                                const RansSym* __restrict__ enc, const uchar* __restrict__ lut,
                                                                uchar* __restrict__ F, int* __restrict__ status) {
+    constexpr int SPW = 32 / W;
     __shared__ unsigned short f0[NTAB2];
-    __shared__ DecWarpSmem wsm[DW_WARPS];
+    __shared__ DecWarpSmem wsm[DW_WARPS * SPW];
+    for (int t = threadIdx.x; t < NTAB2; t += blockDim.x) f0[t] = (unsigned short)(enc[t * 256].fc & 0xffffu);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, sub = lane % W, grp = (threadIdx.x >> 5) * SPW + lane / W;
+    const int s = blockIdx.x * (DW_WARPS * SPW) + grp;
+    const bool have = s < a.nseg;
+    DecWarpSmem& m = wsm[grp];
+    const int T = a.T, mv = a.mv;
+    const Setup u = setup(T, a.seed, a.tm, a.sg, have ? s : a.nseg - 1);
+    WarpDec c; c.enc = enc; c.lut = lut; c.f0 = f0;
+    if (have) c.init(in + off[s], in + off[s + 1]);
+    else { c.init(in, in); c.x = RANS_L; c.over = false; }
+    uchar* fb = reinterpret_cast<uchar*>(m.fblk);
+    const uchar* pbs = reinterpret_cast<const uchar*>(m.pblk);
+    const int nb = have ? u.g.nb : 0;
+    const int nbmax = (int)__reduce_max_sync(0xffffffffu, (unsigned)nb);
+    int prev = 1;
+    for (int j = 0; j < nbmax; ++j) {
+        const bool live = j < nb && !c.over;
+        const long long b = u.g.b0 + j;
+        const uchar* pg = a.P + b * u.bs;
+        uchar* fg = F + b * u.bs;
+        int eq = 1;
+        if (live) { eq = c.get(FLAG + prev); prev = eq; }
+        if (live && eq) for (int i = sub; i < u.bs; i += W) fg[i] = pg[i];
+        const bool code = live && !eq;
+        if (!__any_sync(0xffffffffu, code)) continue;
+        __syncwarp();
+        if (code) {
+            for (int i = sub; i < 56; i += W) m.fblk[i] = 0;
+            for (int i = sub; i < u.bs; i += W) reinterpret_cast<uchar*>(m.pblk)[i] = pg[i];
+        }
+        __syncwarp();
+        int tv[MAXF];
+        if (code) {
+            int pv[MAXF];
+            unpack_fields(T, pbs, pv);
+            int any = 0;
+            for (int k = 0; k < u.nf; ++k) {
+                const int kd = fkind(T, k);
+                const int pr = fpred(T, mv, pv, k, k > 0 ? tv[0] : 0, k > 1 ? tv[1] : 0);
+                const int sym = c.get(fctx(kd, any));
+                int t;
+                if (kd < 2 && sym == 128) { const int lo = c.get(FESC_LO), hi = c.get(FESC_HI); t = lo | (hi << 8); }
+                else {
+                    t = pr + (int)(signed char)sym;
+                    if (kd < 2) t &= 0xffff;
+                    else if (T == 14) t = (int)(signed char)(t & 255);
+                }
+                tv[k] = t; any |= t != pr;
+            }
+            if (sub == 0) pack_fields(T, fb, tv);
+            // contexts and predictions of the block's weights, side by side
+            const long long gw0 = (b - u.m.blk0) * u.qk;
+            const long long col0 = u.m.cols > 0 ? gw0 % u.m.cols : 0;
+            for (int w = sub; w < u.qk; w += W) {
+                float ta, tc;
+                wscale(T, tv, w / u.sublen, ta, tc);
+                float xv, hv; seed_val(u.m.seed_type, u.sbase, gw0 + w, xv, hv, u.m.cols);
+                int r, sgn, ctx; predict_code(T, ta, tc, pbs, w, xv, hv, u.hboff, r, sgn, ctx, mv, pos8(col0 + w, u.m.cols));
+                m.ctx[w] = (unsigned short)ctx; m.pred[w] = (short)r; m.sgn[w] = (signed char)sgn;
+            }
+        }
+        __syncwarp();
+        if (code) {
+#pragma unroll 1
+            for (int w = 0; w < u.qk; w += 4) {          // four contexts per load, four symbols per store
+                const uint2 cx = *reinterpret_cast<const uint2*>(m.ctx + w);
+                unsigned sy = (unsigned)c.get((int)(cx.x & 0xffffu));
+                sy |= (unsigned)c.get((int)(cx.x >> 16)) << 8;
+                sy |= (unsigned)c.get((int)(cx.y & 0xffffu)) << 16;
+                sy |= (unsigned)c.get((int)(cx.y >> 16)) << 24;
+                if (sub == 0) *reinterpret_cast<unsigned*>(m.sym + w) = sy;
+            }
+        }
+        __syncwarp();
+        if (code) {
+            for (int w = sub; w < u.qk; w += W) {
+                int q = m.pred[w] + m.sgn[w] * (int)(signed char)m.sym[w];
+                if (T == 8) q = (int)(signed char)(q & 255);
+                put_code_shared(T, m.fblk, w, q);
+            }
+        }
+        __syncwarp();
+        if (code) for (int i = sub; i < u.bs; i += W) fg[i] = fb[i];
+    }
+    if (have && sub == 0 && !c.finished()) atomicOr(status, SG_ST_CORRUPT);
+}
+
+// ---- decoder of the lattice types: a warp per segment ------------------------------------------------------------------
+// What makes these blocks expensive is the ordering of all 256 - 2048 lattice points by their weighted distance to the
+// seed, once per group of 4 / 8 weights.  Here the 32 lanes of the warp share that: every lane measures the points
+// lane, lane + 32, ... and keeps its own 16 closest in order; the warp's closest, second closest, ... come out of
+// rounds of an arg-min over the lanes' list heads (only as many rounds as the decoded rank needs).  Everything that is
+// one chain (flag, fields, ranks, signs) is decoded by all lanes in lockstep.
+struct GridWarpSmem {
+    unsigned fblk[28], pblk[28];            // block sizes <= 110 bytes
+    float xs[256];                          // the block's seed values
+    float tab[128];                         // pair tables of the group being ranked: [pair][levels]
+    float dist[2048];                       // distance of every lattice point of the group being ranked
+    float gu[256], gw[256];                 // per weight: seed value over the unit's scale (sign-folded), search weight
+    unsigned char pn[32];                   // per unit of 8 weights: which seed values count as negative
+};
+template <int N> SG_DEVINL float point_dist_w(const float* tab, unsigned key) {
+    constexpr int B = N == 8 ? 2 : 3, E = 1 << (2 * B);
+    float d = 0.f;
+#pragma unroll
+    for (int p = 0; p < N / 2; ++p) d = d + tab[p * E + ((key >> (2 * B * p)) & (E - 1))];
+    return isnan(d) ? __int_as_float(0x7f800000) : d;
+}
+template <int N, bool SGN>
+SG_DEVINL void grid_block_warp(WarpDec& c, GridWarpSmem& m, int lane, int T, int mv, const int* tv, const uint16_t* __restrict__ gk,
+                               long long gw0, int cols, const float* im) {
+    constexpr int B = N == 8 ? 2 : 3, ng = 8 / N, L = 1 << B, E = L * L;
+    const float inf = __int_as_float(0x7f800000);
+    uchar* fb = reinterpret_cast<uchar*>(m.fblk);
+    const uchar* pb = reinterpret_cast<const uchar*>(m.pblk);
+    const int gs = grid_size(T);
+    const bool par = parity_type(T);
+    float sx2 = 0.f;
+    for (int i = 0; i < 256; ++i) { const float xv = m.xs[i]; sx2 += xv * xv; }
+    const float sigma2 = (T == 16 || T == 17) ? sx2 * (1.0f / 256.f) : 2.f * sx2 * (1.0f / 256.f);
+    const long long col0 = cols > 0 ? gw0 % cols : 0;
+    // what a unit's ranking needs from the seed, one unit per lane: weights, sign folding with the parity repair, values
+    // over the unit's scale (the scale does not depend on IQ1_M's shift bit, only the level offset does)
+    {
+        const int u = lane;
+        float gs_, gdl0;
+        gscale(T, fb, tv, u, gs_, gdl0);
+        float x[8], v[8], wv[8];
+        int pnb = 0;
+        for (int i = 0; i < 8; ++i) {
+            x[i] = m.xs[8 * u + i];
+            float wi = sqrtf(sigma2 + x[i] * x[i]);
+            if (im) wi = wi * im[(gw0 + 8 * u + i) % cols];
+            wv[i] = wi;
+            if (x[i] < 0.f) pnb |= 1 << i;
+            v[i] = SGN ? fabsf(x[i]) : x[i];
+        }
+        if (SGN && par && (__popc(pnb) & 1)) {         // an odd number of negatives: the least weighty one flips back
+            int imin = 0; float mn = wv[0] * x[0] * x[0];
+            for (int i = 1; i < 8; ++i) { const float a = wv[i] * x[i] * x[i]; if (a < mn) { mn = a; imin = i; } }
+            pnb ^= 1 << imin;
+            for (int i = 0; i < 8; ++i) if (i == imin) v[i] = -v[i];
+        }
+        for (int i = 0; i < 8; ++i) { m.gu[8 * u + i] = v[i] / gs_; m.gw[8 * u + i] = wv[i]; }
+        m.pn[u] = (unsigned char)pnb;
+    }
+    __syncwarp();
+    for (int u = 0; u < 32; ++u) {
+        const int p4 = pos4(col0 + 8 * u, cols);
+        const int rank0 = mv >= 2 ? GRANK2 + 4 * p4 : GRID_RANK;
+        const int sign0 = mv >= 2 ? GSIGN2 + 16 * p4 : GRID_SIGN;
+        if (T == 29) { if (c.get(GRID_SHIFT) ^ get_shift(pb, u)) { if (lane == 0) put_shift(fb, u); } __syncwarp(); }
+        float gu[8], gw[8], gs_, gdl;
+        int pn[8];
+        gscale(T, fb, tv, u, gs_, gdl);
+        for (int i = 0; i < 8; ++i) { gu[i] = m.gu[8 * u + i]; gw[i] = m.gw[8 * u + i]; pn[i] = (m.pn[u] >> i) & 1; }
+        int tg[2] = {0, 0};
+        for (int gg = 0; gg < ng; ++gg) {
+            // pair tables of this group, entries spread over the lanes
+            __syncwarp();
+            for (int e = lane; e < (N / 2) * E; e += 32) {
+                const int p = e / E, ee = e % E, la = ee & (L - 1), lb = ee >> B;
+                const float qa = SGN ? (float)(2 * la + 1) : (float)(la - 1) + gdl;
+                const float qb = SGN ? (float)(2 * lb + 1) : (float)(lb - 1) + gdl;
+                float ua = 0.f, ub = 0.f, wa = 0.f, wb = 0.f;
+#pragma unroll
+                for (int i = 0; i < N / 2; ++i) if (i == p) { ua = gu[gg * N + 2 * i]; ub = gu[gg * N + 2 * i + 1]; wa = gw[gg * N + 2 * i]; wb = gw[gg * N + 2 * i + 1]; }
+                const float ea = qa - ua, eb = qb - ub;
+                m.tab[e] = wa * (ea * ea) + wb * (eb * eb);
+            }
+            __syncwarp();
+            // distances of all points; every lane remembers the closest of its own (points lane, lane + 32, ...)
+            float md = inf; int mk = 0x7fffffff;
+            for (int k = lane; k < gs; k += 32) {
+                const float d = point_dist_w<N>(m.tab, __ldg(gk + k));
+                m.dist[k] = d;
+                if (d < md) { md = d; mk = k; }
+            }
+            // the warp's next closest point in the order (distance, index): arg-min over the lanes' closest; the winning
+            // lane strikes its point out and looks for its next one.  Points at infinite distance never come up.
+            auto next = [&](float& bd, int& bk) {
+                bd = md; bk = mk;
+#pragma unroll
+                for (int sft = 16; sft > 0; sft >>= 1) {
+                    const float od = __shfl_xor_sync(0xffffffffu, bd, sft);
+                    const int ok = __shfl_xor_sync(0xffffffffu, bk, sft);
+                    if (od < bd || (od == bd && ok < bk)) { bd = od; bk = ok; }
+                }
+                if (bk == mk && bk != 0x7fffffff) {
+                    m.dist[mk] = inf;
+                    md = inf; mk = 0x7fffffff;
+                    for (int k = lane; k < gs; k += 32) { const float d = m.dist[k]; if (d < md) { md = d; mk = k; } }
+                }
+            };
+            float d1, d2; int k1, k2;
+            next(d1, k1); next(d2, k2);
+            const int r = c.get(rank0 + gapctx(d1, d2));
+            int t;
+            if (r >= TOPK) { const int lo = c.get(FESC_LO), hi = c.get(FESC_HI); t = (lo | (hi << 8)) % gs; }
+            else {
+                // slot r of the ordered list; slots beyond the points at finite distance keep their own number
+                t = r == 0 ? k1 : k2;
+                for (int j = 2; j <= r; ++j) { float dj; next(dj, t); }
+                if (t == 0x7fffffff) t = r;
+            }
+            if (lane == 0) put_gidx(T, fb, u * ng + gg, t);
+            tg[gg] = t;
+        }
+        __syncwarp();
+        if (SGN) for (int j = 0; j < 8; ++j) {
+            if (par && j == 7) continue;
+            const int lev = (gk[tg[j / N]] >> (B * (j % N))) & ((1 << B) - 1);
+            const float m4 = fabsf(gu[j]) * 4.f;
+            const int sctx = sign0 + (lev == 0) * 8 + (m4 < 7.f ? (int)m4 : 7);
+            if (c.get(sctx) ^ pn[j]) { if (lane == 0) put_neg(T, fb, 8 * u + j); }
+        }
+        __syncwarp();
+        if (c.over) return;
+    }
+}
+
+__global__ void __launch_bounds__(DW_WARPS * 32) k_qr_dec_grid_warp(const Args a, const uchar* __restrict__ in, const unsigned long long* __restrict__ off,
+                                                                    const RansSym* __restrict__ enc, const uchar* __restrict__ lut,
+                                                                    uchar* __restrict__ F, int* __restrict__ status) {
+    __shared__ unsigned short f0[NTAB2];
+    __shared__ GridWarpSmem wsm[DW_WARPS];
     for (int t = threadIdx.x; t < NTAB2; t += blockDim.x) f0[t] = (unsigned short)(enc[t * 256].fc & 0xffffu);
     __syncthreads();
     const int lane = threadIdx.x & 31, s = blockIdx.x * DW_WARPS + (threadIdx.x >> 5);
     if (s >= a.nseg) return;
-    DecWarpSmem& m = wsm[threadIdx.x >> 5];
+    GridWarpSmem& m = wsm[threadIdx.x >> 5];
     const int T = a.T, mv = a.mv;
     const Setup u = setup(T, a.seed, a.tm, a.sg, s);
+    const float* im = u.m.imx_off >= 0 ? a.imx + u.m.imx_off : nullptr;
     WarpDec c; c.enc = enc; c.lut = lut; c.f0 = f0;
-    c.rd.init(in + off[s], in + off[s + 1]);
-    c.x = rans_init(c.rd);
+    c.init(in + off[s], in + off[s + 1]);
     uchar* fb = reinterpret_cast<uchar*>(m.fblk);
     const uchar* pbs = reinterpret_cast<const uchar*>(m.pblk);
     int prev = 1;
-    for (long long b = u.g.b0; b < u.g.b0 + u.g.nb; ++b) {
+    for (long long b = u.g.b0; b < u.g.b0 + u.g.nb && !c.over; ++b) {
         const uchar* pg = a.P + b * u.bs;
         uchar* fg = F + b * u.bs;
         const int eq = c.get(FLAG + prev);
         prev = eq;
         if (eq) { for (int i = lane; i < u.bs; i += 32) fg[i] = pg[i]; continue; }
+        const long long gw0 = (b - u.m.blk0) * u.qk;
         __syncwarp();
-        for (int i = lane; i < 56; i += 32) m.fblk[i] = 0;
+        if (lane < 28) m.fblk[lane] = 0;
         for (int i = lane; i < u.bs; i += 32) reinterpret_cast<uchar*>(m.pblk)[i] = pg[i];
+        for (int i = lane; i < 256; i += 32) { float xv, hv; seed_val(u.m.seed_type, u.sbase, gw0 + i, xv, hv, u.m.cols); m.xs[i] = xv; }
         __syncwarp();
         int tv[MAXF], pv[MAXF];
         unpack_fields(T, pbs, pv);
@@ -433,37 +694,20 @@ __global__ void __launch_bounds__(DW_WARPS * 32) k_qr_dec_warp(const Args a, con
             else {
                 t = pr + (int)(signed char)sym;
                 if (kd < 2) t &= 0xffff;
-                else if (T == 14) t = (int)(signed char)(t & 255);
             }
             tv[k] = t; any |= t != pr;
         }
         if (lane == 0) pack_fields(T, fb, tv);
-        // contexts and predictions of the block's weights, side by side
-        const long long gw0 = (b - u.m.blk0) * u.qk;
-        const long long col0 = u.m.cols > 0 ? gw0 % u.m.cols : 0;
-        for (int w = lane; w < u.qk; w += 32) {
-            float ta, tc;
-            wscale(T, tv, w / u.sublen, ta, tc);
-            float xv, hv; seed_val(u.m.seed_type, u.sbase, gw0 + w, xv, hv, u.m.cols);
-            int r, sgn, ctx; predict_code(T, ta, tc, pbs, w, xv, hv, u.hboff, r, sgn, ctx, mv, pos8(col0 + w, u.m.cols));
-            m.ctx[w] = (unsigned short)ctx; m.pred[w] = (short)r; m.sgn[w] = (signed char)sgn;
-        }
         __syncwarp();
-        for (int w = 0; w < u.qk; ++w) {
-            const int sy = c.get(m.ctx[w]);
-            if (lane == 0) m.sym[w] = (uchar)sy;
-        }
-        __syncwarp();
-        for (int w = lane; w < u.qk; w += 32) {
-            int q = m.pred[w] + m.sgn[w] * (int)(signed char)m.sym[w];
-            if (T == 8) q = (int)(signed char)(q & 255);
-            put_code_shared(T, m.fblk, w, q);
+        switch (T) {
+            case 18: case 21: grid_block_warp<4, true>(c, m, lane, T, mv, tv, a.gk, gw0, u.m.cols, im); break;
+            case 19: case 29: grid_block_warp<8, false>(c, m, lane, T, mv, tv, a.gk, gw0, u.m.cols, im); break;
+            default: grid_block_warp<8, true>(c, m, lane, T, mv, tv, a.gk, gw0, u.m.cols, im);
         }
         __syncwarp();
         for (int i = lane; i < u.bs; i += 32) fg[i] = fb[i];
-        if (c.rd.over) break;
     }
-    if (lane == 0 && (c.rd.over || c.x != RANS_L || c.rd.p != c.rd.end)) atomicOr(status, SG_ST_CORRUPT);
+    if (lane == 0 && !c.finished()) atomicOr(status, SG_ST_CORRUPT);
 }
 
 // ---- encoding in two steps ---------------------------------------------------------------------------------------
@@ -638,11 +882,14 @@ extern "C" int sg_qr_decode(int device, void* stream, int T, const unsigned char
     rc = use_device(device);
     if (rc != SG_OK) return rc;
     if (qr::is_grid(T))
-        k_qr_dec<<<(nseg + QR_TPB - 1) / QR_TPB, QR_TPB, grid_smem(T), (cudaStream_t)stream>>>(a, in, off, (const RansSym*)enc_tab, lut, F,
-                                                                                           status_word(device));
+        k_qr_dec_grid_warp<<<(nseg + DW_WARPS - 1) / DW_WARPS, DW_WARPS * 32, 0, (cudaStream_t)stream>>>(a, in, off, (const RansSym*)enc_tab, lut, F,
+                                                                                                      status_word(device));
     else
-        k_qr_dec_warp<<<(nseg + DW_WARPS - 1) / DW_WARPS, DW_WARPS * 32, 0, (cudaStream_t)stream>>>(a, in, off, (const RansSym*)enc_tab, lut, F,
-                                                                                                 status_word(device));
+    {
+        constexpr int W = 8, per_cta = DW_WARPS * (32 / W);
+        k_qr_dec_warp<W><<<(nseg + per_cta - 1) / per_cta, DW_WARPS * 32, 0, (cudaStream_t)stream>>>(a, in, off, (const RansSym*)enc_tab, lut, F,
+                                                                                                  status_word(device));
+    }
     return cuda_ok(cudaGetLastError());
 }
 
