@@ -54,21 +54,79 @@ SG_DEVINL void hadd(unsigned* counts, unsigned key) {
     if ((threadIdx.x & 31) == (unsigned)(__ffs(m) - 1)) atomicAdd(counts + key, (unsigned)__popc(m));
 }
 
-__global__ void __launch_bounds__(TPB) k_r2_hist(const unsigned char* __restrict__ dev, const TB* __restrict__ tb, const SG* __restrict__ sg,
-                                                 int nseg, Ctx c, unsigned* __restrict__ counts) {
-    const int s = blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= nseg) return;
-    const SG g = sg[s];
-    Cursor q; q.seek(dev, tb[g.t], g.i0, c.rowmap);
-    for (int k = 0; k < g.n; ++k) {
-        const unsigned u = q.w[q.j];
-        const int ex = (u >> 7) & 255, man = u & 127, sgn = u >> 15;
-        int pred, pe, sc; contexts(c, q.T, q.orow, q.j, pred, pe, sc);
-        hadd(counts, (unsigned)(q.T.tab + pe) * 256 + ex);
-        atomicAdd(counts + (size_t)(q.T.tab + 512 + mctx(ex, pred)) * 256 + man, 1u);
-        hadd(counts, (unsigned)(q.T.tab + 640 + sc) * 256 + sgn);
-        if (++q.j == q.T.rowlen) { q.j = 0; ++q.rc; if (k + 1 < g.n) q.row(dev, c.rowmap); }
+// counts do not depend on the order of the weights: a warp per segment, lanes on consecutive weights (coalesced reads).
+// Exponent and sign symbols repeat inside a warp and are added once per distinct value; mantissa symbols are spread
+// over 128 x 128 counters per role, which a CTA collects in shared memory (64 KB) and adds to global memory at its end;
+// so are the exponent symbols inside a window of 128 contexts x 64 exponents around the CTA's first weight (weights
+// of one tensor keep to a few octaves; what falls outside the window goes to global memory directly).
+constexpr int R2H_WARPS = 8, R2H_SEGS = 8;         // segments per warp
+__global__ void __launch_bounds__(R2H_WARPS * 32) k_r2_hist(const unsigned char* __restrict__ dev, const TB* __restrict__ tb,
+                                                            const SG* __restrict__ sg, int nseg, Ctx c, unsigned* __restrict__ counts) {
+    extern __shared__ unsigned mhist[];            // [128 contexts][128 symbols] of the role of the CTA's first segment
+    unsigned* ehist = mhist + 128 * 128;           // [128 contexts from pe0][64 exponents from ex0] of the same role
+    __shared__ int win[2];
+    for (int i = threadIdx.x; i < 128 * 128 + 128 * 64; i += blockDim.x) mhist[i] = 0;
+    const int lane = threadIdx.x & 31;
+    const int first = blockIdx.x * (R2H_WARPS * R2H_SEGS);
+    const int cta_tab = first < nseg ? tb[sg[first].t].tab : -1;
+    if (threadIdx.x == 0 && first < nseg) {
+        const SG g = sg[first];
+        const TB T = tb[g.t];
+        const int rc = (int)(g.i0 / T.rowlen), j = (int)(g.i0 % T.rowlen);
+        const int orow = T.rmap >= 0 ? c.rowmap[T.rmap + rc] : rc;
+        const unsigned u = reinterpret_cast<const unsigned short*>(dev + T.doff)[(size_t)orow * T.rowlen + j];
+        int pred, pe, sc; contexts(c, T, orow, j, pred, pe, sc);
+        win[0] = pe - 64; win[1] = (int)((u >> 7) & 255) - 40;      // weights mostly lie below the typical magnitude
     }
+    __syncthreads();
+    const int pe0 = win[0], ex0 = win[1];
+    for (int q = 0; q < R2H_SEGS; ++q) {
+        const int s = first + (threadIdx.x >> 5) * R2H_SEGS + q;
+        if (s >= nseg) break;
+        const SG g = sg[s];
+        const TB T = tb[g.t];
+        const bool local = T.tab == cta_tab;
+        // this lane's weight: compact row rc, column j; 32 weights further every turn (no division inside the loop)
+        int rc = (int)((g.i0 + lane) / T.rowlen), j = (int)((g.i0 + lane) % T.rowlen), orow = -1, have_rc = -1;
+        const unsigned short* base = reinterpret_cast<const unsigned short*>(dev + T.doff);
+        for (int k0 = 0; k0 < g.n; k0 += 32) {
+            const int k = k0 + lane;
+            const bool live = k < g.n;
+            unsigned e0 = 0xffffffffu, e2 = 0xffffffffu;
+            if (live) {
+                if (rc != have_rc) { orow = T.rmap >= 0 ? c.rowmap[T.rmap + rc] : rc; have_rc = rc; }
+                const unsigned u = base[(size_t)orow * T.rowlen + j];
+                const int ex = (u >> 7) & 255, man = u & 127, sgn = u >> 15;
+                int pred, pe, sc; contexts(c, T, orow, j, pred, pe, sc);
+                if (local && (unsigned)(pe - pe0) < 128u && (unsigned)(ex - ex0) < 64u) atomicAdd(ehist + (pe - pe0) * 64 + (ex - ex0), 1u);
+                else e0 = (unsigned)(T.tab + pe) * 256 + ex;
+                e2 = (unsigned)(T.tab + 640 + sc) * 256 + sgn;
+                const int mc = mctx(ex, pred);
+                if (local) atomicAdd(mhist + mc * 128 + man, 1u);
+                else atomicAdd(counts + (size_t)(T.tab + 512 + mc) * 256 + man, 1u);
+                j += 32;
+                while (j >= T.rowlen) { j -= T.rowlen; ++rc; }
+            }
+            if (__any_sync(0xffffffffu, e0 != 0xffffffffu)) {
+                const unsigned m0 = __match_any_sync(0xffffffffu, e0);
+                if (e0 != 0xffffffffu && lane == __ffs(m0) - 1) atomicAdd(counts + e0, (unsigned)__popc(m0));
+            }
+            const unsigned m2 = __match_any_sync(0xffffffffu, e2);
+            if (live && lane == __ffs(m2) - 1) atomicAdd(counts + e2, (unsigned)__popc(m2));
+        }
+    }
+    __syncthreads();
+    if (cta_tab >= 0)
+        for (int i = threadIdx.x; i < 128 * 128; i += blockDim.x) {
+            const unsigned v = mhist[i];
+            if (v) atomicAdd(counts + (size_t)(cta_tab + 512 + (i >> 7)) * 256 + (i & 127), v);
+        }
+    if (cta_tab >= 0)
+        for (int i = threadIdx.x; i < 128 * 64; i += blockDim.x) {
+            const unsigned v = ehist[i];
+            const int pe = pe0 + (i >> 6), ex = ex0 + (i & 63);
+            if (v) atomicAdd(counts + (size_t)(cta_tab + pe) * 256 + ex, v);
+        }
 }
 
 __global__ void __launch_bounds__(TPB) k_r2_enc(const unsigned char* __restrict__ dev, const TB* __restrict__ tb, const SG* __restrict__ sg,
@@ -81,15 +139,28 @@ __global__ void __launch_bounds__(TPB) k_r2_enc(const unsigned char* __restrict_
     unsigned char* slot = out + (size_t)s * cap;
     ByteWriterDown wr; wr.init(slot + cap);
     unsigned x = RANS_L;
-    for (int k = g.n - 1; k >= 0; --k) {
-        const unsigned u = q.w[q.j];
-        const int ex = (u >> 7) & 255, man = u & 127, sgn = u >> 15;
-        int pred, pe, sc; contexts(c, q.T, q.orow, q.j, pred, pe, sc);
-        rans_put<PB>(x, wr, enc[(size_t)(q.T.tab + 640 + sc) * 256 + sgn]);
-        rans_put<PB>(x, wr, enc[(size_t)(q.T.tab + 512 + mctx(ex, pred)) * 256 + man]);
-        rans_put<PB>(x, wr, enc[(size_t)(q.T.tab + pe) * 256 + ex]);
+    // four weights at a time: their table entries depend on the data only, not on the coder state, so the twelve loads
+    // are issued before the twelve coding steps that chain through x
+    for (int k = g.n - 1; k >= 0; k -= 4) {
+        RansSym e[4][3];
+        const int nv = k + 1 < 4 ? k + 1 : 4;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            if (v < nv) {
+                const unsigned u = q.w[q.j];
+                const int ex = (u >> 7) & 255, man = u & 127, sgn = u >> 15;
+                int pred, pe, sc; contexts(c, q.T, q.orow, q.j, pred, pe, sc);
+                e[v][0] = enc[(size_t)(q.T.tab + 640 + sc) * 256 + sgn];
+                e[v][1] = enc[(size_t)(q.T.tab + 512 + mctx(ex, pred)) * 256 + man];
+                e[v][2] = enc[(size_t)(q.T.tab + pe) * 256 + ex];
+                if (--q.j < 0) { q.j = q.T.rowlen - 1; --q.rc; if (k - v > 0) q.row(dev, c.rowmap); }
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            if (v < nv) { rans_put<PB>(x, wr, e[v][0]); rans_put<PB>(x, wr, e[v][1]); rans_put<PB>(x, wr, e[v][2]); }
+        }
         if (wr.ptr() < slot + 64) { out_len[s] = 0xffffffffu; return; }
-        if (--q.j < 0) { q.j = q.T.rowlen - 1; --q.rc; if (k > 0) q.row(dev, c.rowmap); }
     }
     rans_flush(x, wr);
     wr.flush(slot);
@@ -124,12 +195,32 @@ __global__ void __launch_bounds__(TPB) k_r2_dec(const unsigned char* __restrict_
 // 64-bit row fingerprints for duplicate-row detection (bf16v2.py:148-155): an order-dependent integer recurrence, one
 // lane per row
 __global__ void __launch_bounds__(128) k_row_hash(const unsigned short* __restrict__ w, int nrows, int rowlen, unsigned long long* __restrict__ h) {
-    const int r = blockIdx.x * blockDim.x + threadIdx.x;
-    if (r >= nrows) return;
+    // the recurrence runs along a row, one lane per row; the rows' data comes in through shared memory in tiles of
+    // 128 rows x 64 weights loaded with the lanes along the row (coalesced), read back with a 33-word row pitch
+    __shared__ unsigned tile[128][33];
+    const int r0 = blockIdx.x * 128, r = r0 + threadIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned long long a = 1469598103934665603ull;
-    const unsigned short* p = w + (size_t)r * rowlen;
-    for (int j = 0; j < rowlen; ++j) { a ^= p[j]; a *= 1099511628211ull; a ^= a >> 29; }
-    h[r] = a;
+    if ((rowlen & 63) || (reinterpret_cast<uintptr_t>(w) & 3)) {           // odd shapes: straight from global memory
+        if (r < nrows) {
+            const unsigned short* p = w + (size_t)r * rowlen;
+            for (int j = 0; j < rowlen; ++j) { a ^= p[j]; a *= 1099511628211ull; a ^= a >> 29; }
+            h[r] = a;
+        }
+        return;
+    }
+    for (int c0 = 0; c0 < rowlen; c0 += 64) {
+        __syncthreads();
+        for (int rr = warp; rr < 128; rr += 4)
+            tile[rr][lane] = r0 + rr < nrows ? reinterpret_cast<const unsigned*>(w + (size_t)(r0 + rr) * rowlen + c0)[lane] : 0u;
+        __syncthreads();
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i) {
+            const unsigned v = tile[threadIdx.x][i];
+            a ^= v & 0xffffu; a *= 1099511628211ull; a ^= a >> 29;
+            a ^= v >> 16;     a *= 1099511628211ull; a ^= a >> 29;
+        }
+    }
+    if (r < nrows) h[r] = a;
 }
 
 // duplicate rows copied from their source rows after decoding (bf16v2.py:475-480): pairs = (dup row, source row)
@@ -244,7 +335,13 @@ extern "C" int sg_r2_hist(int device, void* stream, const unsigned char* dev, co
     rc = use_device(device);
     if (rc != SG_OK) return rc;
     Ctx c = {rfi, cfi, scl, rowmap};
-    k_r2_hist<<<(nseg + TPB - 1) / TPB, TPB, 0, (cudaStream_t)stream>>>(dev, (const TB*)tb, (const SG*)sgp, nseg, c, counts);
+    {
+        rc = cuda_ok(cudaFuncSetAttribute(k_r2_hist, cudaFuncAttributeMaxDynamicSharedMemorySize, (128 * 128 + 128 * 64) * 4));
+        if (rc != SG_OK) return rc;
+        const int per_cta = R2H_WARPS * R2H_SEGS;
+        k_r2_hist<<<(nseg + per_cta - 1) / per_cta, R2H_WARPS * 32, (128 * 128 + 128 * 64) * 4, (cudaStream_t)stream>>>(dev, (const TB*)tb, (const SG*)sgp,
+                                                                                                           nseg, c, counts);
+    }
     return cuda_ok(cudaGetLastError());
 }
 
