@@ -2,8 +2,9 @@
 """Quantiser sweep benchmark (BASELINE config 2): one BF16 tensor of 4096 x 12288 seeded weights plus a
 12288-entry importance matrix, re-quantised into every ggml type the path handles.
 
-A step = one pass over the tensor for every type: the 20 types with the importance matrix, then the 15
-types whose matrix-free routine is a different code path.  Metric: GB/s of GGUF (quantised) bytes regrown.
+A step = one pass over the tensor for every type: the 20 types of the reference's table with the importance matrix,
+the 15 of them whose matrix-free routine is a different code path, and the 5 further quantisers of ggml-quants.c
+(TQ1_0, TQ2_0, MXFP4, NVFP4, Q1_0), which take no matrix: 25 types, 40 launches.  Metric: GB/s of GGUF (quantised) bytes regrown.
 
     python bench.py --gpus N --steps K --warmup W          (this repo's CUDA path)
     python bench.py --impl reference ...                   (the reference's own C quantisers on the host cores)
@@ -29,9 +30,11 @@ QFUN = {2: ("q4_0", 32, 18), 3: ("q4_1", 32, 20), 6: ("q5_0", 32, 22), 7: ("q5_1
         8: ("q8_0", 32, 34), 10: ("q2_K", 256, 84), 11: ("q3_K", 256, 110), 12: ("q4_K", 256, 144),
         13: ("q5_K", 256, 176), 14: ("q6_K", 256, 210), 16: ("iq2_xxs", 256, 66), 17: ("iq2_xs", 256, 74),
         18: ("iq3_xxs", 256, 98), 19: ("iq1_s", 256, 50), 20: ("iq4_nl", 32, 18), 21: ("iq3_s", 256, 110),
-        22: ("iq2_s", 256, 82), 23: ("iq4_xs", 256, 136), 29: ("iq1_m", 256, 56), 42: ("q2_0", 64, 18)}
+        22: ("iq2_s", 256, 82), 23: ("iq4_xs", 256, 136), 29: ("iq1_m", 256, 56), 42: ("q2_0", 64, 18),
+        34: ("tq1_0", 256, 54), 35: ("tq2_0", 256, 66), 39: ("mxfp4", 32, 17), 40: ("nvfp4", 64, 36), 41: ("q1_0", 128, 18)}
 NO_IMX_TOO = [2, 3, 6, 7, 10, 11, 12, 13, 14, 18, 20, 21, 22, 23, 29]     # types whose matrix-free routine differs
-CASES = [(t, True) for t in sorted(QFUN)] + [(t, False) for t in NO_IMX_TOO]
+NO_IMX_ONLY = [34, 35, 39, 40, 41]                                        # types that take no importance matrix
+CASES = [(t, True) for t in sorted(QFUN) if t not in NO_IMX_ONLY] + [(t, False) for t in NO_IMX_TOO + NO_IMX_ONLY]
 
 
 def quant_bytes(t, nrows=None, npr=NPR):
@@ -176,7 +179,6 @@ def run_ours(args):
     w = himx.to(dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     out_bytes = sum(quant_bytes(t) for t, _ in CASES)
-    hout = torch.empty(max(quant_bytes(t) for t, _ in CASES) + 64, dtype=torch.uint8).pin_memory()
 
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in CASES]
 
@@ -215,13 +217,27 @@ def run_ours(args):
     ms = e0.elapsed_time(e1)
     clocks = sampler.summary()
 
-    # end to end through the public API: host BF16 + importance matrix in, quantised bytes out to the host
+    # end to end through the public API: host BF16 + importance matrix in, quantised bytes out to the host.  The copies
+    # back run on a second stream behind each launch, so they overlap the next launch (every case has its own range
+    # of the pinned output buffer)
+    hall = torch.empty(out_bytes + 64 * len(CASES), dtype=torch.uint8).pin_memory()
+    copy_stream = torch.cuda.Stream(dev)
+
     def e2e_step():
         xd = hx.to(dev, non_blocking=True).view(torch.bfloat16).reshape(-1)
         wd = himx.to(dev, non_blocking=True)
+        pos, keep = 0, []
         for t, use in CASES:
             y = gq.quantize_tensors(t, [(xd, NPR)], [wd if use else None], device=True)[0]
-            hout[:y.numel()].copy_(y, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record()
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(done)
+                hall[pos:pos + y.numel()].copy_(y, non_blocking=True)
+            y.record_stream(copy_stream)
+            keep.append(y)
+            pos += y.numel() + 64
+        copy_stream.synchronize()
         torch.cuda.synchronize()
 
     e2e_step()

@@ -72,6 +72,11 @@ extern "C" {
 #define SG_IQ2_S 22
 #define SG_IQ4_XS 23
 #define SG_IQ1_M 29
+#define SG_TQ1_0 34
+#define SG_TQ2_0 35
+#define SG_MXFP4 39
+#define SG_NVFP4 40
+#define SG_Q1_0 41
 #define SG_Q2_0 42
 
 /* One tensor of a quantise / dequantise launch.  All tensors of a launch live in the same source,

@@ -23,7 +23,10 @@ QFUN = {2: ("q4_0", 32, 18), 3: ("q4_1", 32, 20), 6: ("q5_0", 32, 22), 7: ("q5_1
         8: ("q8_0", 32, 34), 10: ("q2_K", 256, 84), 11: ("q3_K", 256, 110), 12: ("q4_K", 256, 144),
         13: ("q5_K", 256, 176), 14: ("q6_K", 256, 210), 16: ("iq2_xxs", 256, 66), 17: ("iq2_xs", 256, 74),
         18: ("iq3_xxs", 256, 98), 19: ("iq1_s", 256, 50), 20: ("iq4_nl", 32, 18), 21: ("iq3_s", 256, 110),
-        22: ("iq2_s", 256, 82), 23: ("iq4_xs", 256, 136), 29: ("iq1_m", 256, 56), 42: ("q2_0", 64, 18)}
+        22: ("iq2_s", 256, 82), 23: ("iq4_xs", 256, 136), 29: ("iq1_m", 256, 56), 42: ("q2_0", 64, 18),
+        # not in the reference's table, but in its ggml-quants.c (lines 40, 350, 384, 2317, 2383)
+        34: ("tq1_0", 256, 54), 35: ("tq2_0", 256, 66), 39: ("mxfp4", 32, 17), 40: ("nvfp4", 64, 36), 41: ("q1_0", 128, 18)}
+EXTRA = {34, 35, 39, 40, 41}
 IQ2_INIT = {16, 17, 19, 22, 29}            # need iq2xs_init_impl(type)   seedpack/requant.py:28
 IQ3_INIT = {18: 256, 21: 512}              # need iq3xs_init_impl(grid)   seedpack/requant.py:29
 NEEDS_IMATRIX = {16, 17, 19}       # assert quant_weights (ggml-quants.c:3303, 3481, 4521 ...)

@@ -20,8 +20,8 @@ namespace sg {
 // the rounded reciprocal, which differs from the IEEE quotient in a few percent of cases
 // (the reference works around the same rewrite, seedpack/ptxfix.py:1-7).  Divisors therefore come
 // from constant memory, which the assembler cannot fold.
-enum DivK { DIV_15 = 0, DIV_31, DIV_127, DIV_63, DIV_5, DIV_COUNT };
-static __constant__ float c_div[DIV_COUNT] = {15.f, 31.f, 127.f, 63.f, 5.f};
+enum DivK { DIV_15 = 0, DIV_31, DIV_127, DIV_63, DIV_5, DIV_6, DIV_COUNT };
+static __constant__ float c_div[DIV_COUNT] = {15.f, 31.f, 127.f, 63.f, 5.f, 6.f};
 
 SG_DEVINL float fdiv(float a, float b) { return __fdiv_rn(a, b); }
 SG_DEVINL float fmul(float a, float b) { return __fmul_rn(a, b); }

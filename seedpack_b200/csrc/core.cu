@@ -42,6 +42,7 @@ static const TypeInfo TYPES[] = {
     {SG_IQ2_XXS, 256, 66, 1}, {SG_IQ2_XS, 256, 74, 1}, {SG_IQ3_XXS, 256, 98, 0}, {SG_IQ1_S, 256, 50, 1},
     {SG_IQ4_NL, 32, 18, 0}, {SG_IQ3_S, 256, 110, 0}, {SG_IQ2_S, 256, 82, 0}, {SG_IQ4_XS, 256, 136, 0},
     {SG_IQ1_M, 256, 56, 0}, {SG_Q2_0, 64, 18, 0},
+    {SG_TQ1_0, 256, 54, 0}, {SG_TQ2_0, 256, 66, 0}, {SG_MXFP4, 32, 17, 0}, {SG_NVFP4, 64, 36, 0}, {SG_Q1_0, 128, 18, 0},
 };
 
 }  // namespace sg

@@ -4,6 +4,7 @@
 // (4 bytes out per weight).  The bit layouts come from the same locators the residual coder uses.
 #include "api_util.h"
 #include "qr_model.cuh"
+#include "quant_extra.cuh"
 #include "quant_iq.cuh"
 
 namespace sg {
@@ -67,6 +68,49 @@ __global__ void __launch_bounds__(256) k_dequant(int T, const uchar* __restrict_
     x[i] = out;
 }
 
+// the five types outside the reference's own table: dequantize_row_q1_0 / mxfp4 / nvfp4 (ggml-quants.c:419-437, 569-612)
+// and dequantize_row_tq1_0 / tq2_0 (2429-2487)
+__global__ void __launch_bounds__(256) k_dequant_extra(int T, const uchar* __restrict__ y, float* __restrict__ x, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float kvf[16] = {0.f, 1.f, 2.f, 3.f, 4.f, 6.f, 8.f, 12.f, 0.f, -1.f, -2.f, -3.f, -4.f, -6.f, -8.f, -12.f};
+    const unsigned pow3[5] = {1, 3, 9, 27, 81};
+    float out = 0.f;
+    if (T == SG_Q1_0) {
+        const uchar* b = y + (i / 128) * 18;
+        const int w = (int)(i % 128);
+        const float d = f16_to_f32((uint16_t)(b[0] | (b[1] << 8)));
+        out = ((b[2 + (w >> 3)] >> (w & 7)) & 1) ? d : -d;
+    } else if (T == SG_TQ2_0) {
+        const uchar* b = y + (i / 256) * 66;
+        const int w = (int)(i % 256);
+        const float d = f16_to_f32((uint16_t)(b[64] | (b[65] << 8)));
+        const int q = (b[32 * (w >> 7) + (w & 31)] >> (2 * ((w >> 5) & 3))) & 3;
+        out = fmul((float)(q - 1), d);
+    } else if (T == SG_TQ1_0) {
+        const uchar* b = y + (i / 256) * 54;
+        const int w = (int)(i % 256);
+        const float d = f16_to_f32((uint16_t)(b[52] | (b[53] << 8)));
+        unsigned byte, n;
+        if (w < 160) { byte = b[w & 31]; n = w >> 5; }
+        else if (w < 240) { byte = b[32 + ((w - 160) & 15)]; n = (w - 160) >> 4; }
+        else { byte = b[48 + ((w - 240) & 3)]; n = (w - 240) >> 2; }
+        const unsigned q = (byte * pow3[n]) & 0xffu;
+        out = fmul((float)((int)((q * 3) >> 8) - 1), d);
+    } else if (T == SG_MXFP4) {
+        const uchar* b = y + (i / 32) * 17;
+        const int w = (int)(i % 32);
+        const float d = e8m0_half(b[0]);
+        out = fmul(kvf[w < 16 ? b[1 + w] & 15 : b[1 + w - 16] >> 4], d);
+    } else {
+        const uchar* b = y + (i / 64) * 36;
+        const int w = (int)(i % 64), sb = w >> 4, j = w & 15;
+        const float d = ue4m3_to_f32(b[sb]);
+        out = fmul(kvf[j < 8 ? b[4 + 8 * sb + j] & 15 : b[4 + 8 * sb + j - 8] >> 4], d);
+    }
+    x[i] = out;
+}
+
 // BF16 / F16 / F32 conversions of unquantised tensors (norms, embeddings kept in float): replaces
 // M28RepoGPU._float_dev (seedpack/repo3.py:673-689).  To BF16: round to nearest even by integer add on the bits.
 __global__ void __launch_bounds__(256) k_convert_float(const void* __restrict__ src, int st, void* __restrict__ dst, int dt, long long n) {
@@ -103,7 +147,10 @@ extern "C" int sg_dequantize(int device, void* stream, int T, const unsigned cha
     }
     const long long grid = (n_weights + 255) / 256;
     if (grid > 0x7fffffffLL) return SG_ERR_LIMIT;
-    k_dequant<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(T, y, x, n_weights, gk);
+    if (T == SG_Q1_0 || T == SG_TQ1_0 || T == SG_TQ2_0 || T == SG_MXFP4 || T == SG_NVFP4)
+        k_dequant_extra<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(T, y, x, n_weights);
+    else
+        k_dequant<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(T, y, x, n_weights, gk);
     return cuda_ok(cudaGetLastError());
 }
 

@@ -5,6 +5,7 @@
 
 #include "api_util.h"
 #include "quant_iq.cuh"
+#include "quant_extra.cuh"
 #include "quant_legacy.cuh"
 
 namespace sg {
@@ -62,6 +63,11 @@ static int launch_meansq(const Job& job, long long nrows, int dt, cudaStream_t s
 
 static bool legacy_imx_type(int t) { return t == SG_Q4_0 || t == SG_Q4_1 || t == SG_Q5_0 || t == SG_Q5_1; }
 
+// types whose quantize_<t> does the same with and without quant_weights
+static bool ignores_imatrix(int type) {
+    return type == SG_Q8_0 || type == SG_Q2_0 || type == SG_Q1_0 || type == SG_TQ1_0 || type == SG_TQ2_0 || type == SG_MXFP4 || type == SG_NVFP4;
+}
+
 static int dispatch(int type, int variant, bool imx, int device, const Job& job, int dt, cudaStream_t st) {
     switch (type) {
         case SG_Q4_0: return imx ? launch<LegacyImx<SG_Q4_0>, true>(job, dt, st) : launch_legacy_ref<SG_Q4_0>(job, dt, st);
@@ -70,6 +76,11 @@ static int dispatch(int type, int variant, bool imx, int device, const Job& job,
         case SG_Q5_1: return imx ? launch<LegacyImx<SG_Q5_1>, true>(job, dt, st) : launch_legacy_ref<SG_Q5_1>(job, dt, st);
         case SG_Q8_0: return launch_legacy_ref<SG_Q8_0>(job, dt, st);
         case SG_Q2_0: return launch_legacy_ref<SG_Q2_0>(job, dt, st);
+        case SG_Q1_0: return launch_extra<SG_Q1_0>(job, dt, st);
+        case SG_TQ1_0: return launch_extra<SG_TQ1_0>(job, dt, st);
+        case SG_TQ2_0: return launch_extra<SG_TQ2_0>(job, dt, st);
+        case SG_MXFP4: return launch_extra<SG_MXFP4>(job, dt, st);
+        case SG_NVFP4: return launch_extra<SG_NVFP4>(job, dt, st);
         case SG_Q2_K: return imx ? launch<Q2K, true>(job, dt, st) : launch<Q2K, false>(job, dt, st);
         case SG_Q3_K: return imx ? launch<Q3K, true>(job, dt, st) : launch<Q3K, false>(job, dt, st);
         case SG_Q4_K: return imx ? launch<Q45K<4>, true>(job, dt, st) : launch<Q45K<4>, false>(job, dt, st);
@@ -124,11 +135,11 @@ extern "C" int sg_quantize_tensors(int device, void* stream, int type, int varia
         Job job;
         memset(&job, 0, sizeof(job));
         job.x = x; job.y = (uint8_t*)y; job.w = w; job.status = status_word(device);
-        const bool imx = h[i].w_off >= 0 && type != SG_Q8_0 && type != SG_Q2_0;
+        const bool imx = h[i].w_off >= 0 && !ignores_imatrix(type);
         long long slabs = 0, rows = 0;
         int k = 0;
         while (i < n && k < SG_MAX_TENSORS) {
-            const bool imx_i = h[i].w_off >= 0 && type != SG_Q8_0 && type != SG_Q2_0;
+            const bool imx_i = h[i].w_off >= 0 && !ignores_imatrix(type);
             if (imx_i != imx) break;
             Tensor& t = job.t[k];
             t.xoff = h[i].x_off; t.yoff = h[i].y_off; t.woff = imx ? h[i].w_off : -1;

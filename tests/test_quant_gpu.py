@@ -140,3 +140,21 @@ def test_convert_float(gq):
         assert np.array_equal(h.view(torch.int16).cpu().numpy().view(np.uint16), x.astype(np.float16).view(np.uint16))
     back = gq.convert_float(b, torch.float32)
     assert np.array_equal(back.cpu().numpy(), synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(x)))
+
+
+def test_extra_types_match_golden(gq):
+    """TQ1_0, TQ2_0, MXFP4, NVFP4, Q1_0 against bytes and dequantised values the reference's C code produced
+    (tests/golden/quant_extra_golden.npz)"""
+    import os
+    import torch
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "quant_extra_golden.npz"))
+    npr = int(g["npr"])
+    x = torch.from_numpy(g["bits"].view(np.int16)).cuda().view(torch.bfloat16).reshape(-1)
+    for t in (34, 35, 39, 40, 41):
+        got = gq.quantize_tensors(t, [(x, npr)], [None])[0]
+        assert np.array_equal(got, g[f"q_{t}"]), _diff_report(t, np.asarray(got), g[f"q_{t}"])
+        back = gq.dequantize(t, torch.from_numpy(g[f"q_{t}"]).cuda()).cpu().numpy()
+        assert np.array_equal(back.view(np.uint32), g[f"d_{t}"].view(np.uint32)), t
+        # float32 sources holding the same values give the same bytes
+        assert np.array_equal(gq.quantize_tensors(t, [(x.float(), npr)], [None])[0], g[f"q_{t}"])
+    assert gq.status() == 0
