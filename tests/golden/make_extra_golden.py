@@ -1,6 +1,6 @@
 """Writes tests/golden/quant_extra_golden.npz: the five quantisers of ggml-quants.c that the reference's own type
 table leaves out (TQ1_0, TQ2_0, MXFP4, NVFP4, Q1_0), run through the reference's C code as compiled by oracle/Makefile
-(oracle/_ref), on a small seeded tensor, with their dequantised values.  Run where /root/reference is mounted:
+(oracle/_ref), on a small seeded tensor, with their dequantised values.  Run where the reference tree is mounted (SEEDPACK_REFERENCE names it):
 
     make -C oracle ref && python tests/golden/make_extra_golden.py
 """

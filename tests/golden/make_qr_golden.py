@@ -1,7 +1,7 @@
 """Writes tests/golden/qr_golden.npz: coded QR batches made by the REFERENCE (seedpack/qr.py encode, its --cpu path) for
 every scalar-code type, models 1 and 2: stored file blocks = the reference quantiser's output (no importance matrix)
 of a perturbed copy of the weights plus byte flips, predictions = its output on the seed weights.
-    python tests/golden/make_qr_golden.py [/root/reference]"""
+    python tests/golden/make_qr_golden.py <reference tree>"""
 import os
 import sys
 
@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 import refimport  # noqa: E402
 
-refimport.setup(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+refimport.setup(sys.argv[1] if len(sys.argv) > 1 else os.environ["SEEDPACK_REFERENCE"])
 import numpy as np  # noqa: E402
 from seedpack import gpuquant, qr  # noqa: E402
 from tests import synth  # noqa: E402

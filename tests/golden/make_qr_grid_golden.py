@@ -1,6 +1,6 @@
 """Writes tests/golden/qr_grid_golden.npz: coded QR batches of the lattice (IQ) types made by the REFERENCE
 (seedpack/qr.py encode, --cpu path), models 1 and 2, with an importance matrix, on small seeded tensors.
-    python tests/golden/make_qr_grid_golden.py [/root/reference]"""
+    python tests/golden/make_qr_grid_golden.py <reference tree>"""
 import os
 import sys
 
@@ -8,7 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 import refimport  # noqa: E402
 
-refimport.setup(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+refimport.setup(sys.argv[1] if len(sys.argv) > 1 else os.environ["SEEDPACK_REFERENCE"])
 import numpy as np  # noqa: E402
 from seedpack import gpuquant, qr  # noqa: E402
 from tests import synth  # noqa: E402

@@ -3,14 +3,14 @@ seedpack/gpuquant.py compiled for the host by seedpack/cpukernels.py) for every 
 without an importance matrix, plus the IQ1_M variant, on a small seeded tensor.  Run where the reference
 tree is mounted:
 
-    python tests/golden/make_quant_golden.py [/root/reference]
+    python tests/golden/make_quant_golden.py <reference tree>
 
 The fixture holds its own inputs (bf16 bit patterns and the importance matrix), so no test needs the
 reference tree."""
 import os
 import sys
 
-ref_tree = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+ref_tree = sys.argv[1] if len(sys.argv) > 1 else os.environ["SEEDPACK_REFERENCE"]
 os.environ["SEEDPACK_CPU"] = "1"
 os.environ.setdefault("SEEDPACK_CACHE", "/tmp/seedpack-golden-cache")
 os.makedirs(os.environ["SEEDPACK_CACHE"], exist_ok=True)

@@ -1,6 +1,6 @@
 """Writes tests/golden/r2_golden.npz: a small GGUF file of BF16 tensors (built with the reference's own minimal
 writer, seedpack/seed.py gguf_bytes) and the parts of its R2 chunk as coded by the REFERENCE (seedpack/bf16v2.py
-BF16v2.compress, --cpu path), plus detmath outputs on a sample.   python tests/golden/make_r2_golden.py [/root/reference]"""
+BF16v2.compress, --cpu path), plus detmath outputs on a sample.   python tests/golden/make_r2_golden.py <reference tree>"""
 import os
 import sys
 
@@ -8,7 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 import refimport  # noqa: E402
 
-refimport.setup(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+refimport.setup(sys.argv[1] if len(sys.argv) > 1 else os.environ["SEEDPACK_REFERENCE"])
 import numpy as np  # noqa: E402
 from seedpack import bf16v2, detmath, seed  # noqa: E402
 from seedpack.codecs_gguf import unpack  # noqa: E402

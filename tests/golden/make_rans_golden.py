@@ -1,6 +1,6 @@
 """Writes tests/golden/rans_golden.npz with the reference's own coder: seedpack/rans.py (_encode, numba) run per
 segment with PROB_BITS = 12 as the GPU coders do (seedpack/qr.py:651-663), tables from the reference's
-qr.normalize (seedpack/qr.py:904-923).   python tests/golden/make_rans_golden.py [/root/reference]"""
+qr.normalize (seedpack/qr.py:904-923).   python tests/golden/make_rans_golden.py <reference tree>"""
 import os
 import sys
 
@@ -8,7 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 import refimport  # noqa: E402
 
-refimport.setup(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+refimport.setup(sys.argv[1] if len(sys.argv) > 1 else os.environ["SEEDPACK_REFERENCE"])
 import numpy as np  # noqa: E402
 from seedpack import rans as R  # noqa: E402
 from seedpack import qr  # noqa: E402

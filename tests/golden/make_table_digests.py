@@ -1,5 +1,5 @@
 """Writes tests/golden/iq_table_digests.json from the reference's seedpack/ggml/iqtables.npz (run where the
-reference tree is mounted):  python tests/golden/make_table_digests.py [/root/reference]"""
+reference tree is mounted):  python tests/golden/make_table_digests.py <reference tree>"""
 import hashlib
 import json
 import os
@@ -7,7 +7,7 @@ import sys
 
 import numpy as np
 
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+ref = sys.argv[1] if len(sys.argv) > 1 else os.environ["SEEDPACK_REFERENCE"]
 tb = np.load(os.path.join(ref, "seedpack", "ggml", "iqtables.npz"))
 names = ["iq2_data_0", "iq2_data_1", "iq2_data_2", "iq2_data_3", "iq3_data_0", "iq3_data_1"]
 out = {}

@@ -5,7 +5,7 @@ import os
 import sys
 
 
-def setup(ref_tree="/root/reference"):
+def setup(ref_tree):
     os.environ["SEEDPACK_CPU"] = "1"
     os.environ.setdefault("SEEDPACK_CACHE", "/tmp/seedpack-golden-cache")
     os.environ.setdefault("NUMBA_CACHE_DIR", "/tmp/seedpack-golden-numba")
