@@ -73,7 +73,9 @@ template <int DT> struct Src;
 template <> struct Src<SG_DT_BF16> {
     static constexpr int BYTES = 2;
     static SG_DEVINL void load8(const void* p, long long idx, float* o) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p) + idx));
+        unpack8(__ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p) + idx)), o);
+    }
+    static SG_DEVINL void unpack8(const uint4 v, float* o) {
         o[0] = __uint_as_float(v.x << 16); o[1] = __uint_as_float(v.x & 0xffff0000u);
         o[2] = __uint_as_float(v.y << 16); o[3] = __uint_as_float(v.y & 0xffff0000u);
         o[4] = __uint_as_float(v.z << 16); o[5] = __uint_as_float(v.z & 0xffff0000u);
@@ -83,7 +85,9 @@ template <> struct Src<SG_DT_BF16> {
 template <> struct Src<SG_DT_F16> {
     static constexpr int BYTES = 2;
     static SG_DEVINL void load8(const void* p, long long idx, float* o) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p) + idx));
+        unpack8(__ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p) + idx)), o);
+    }
+    static SG_DEVINL void unpack8(const uint4 v, float* o) {
         o[0] = f16_to_f32((uint16_t)v.x); o[1] = f16_to_f32((uint16_t)(v.x >> 16));
         o[2] = f16_to_f32((uint16_t)v.y); o[3] = f16_to_f32((uint16_t)(v.y >> 16));
         o[4] = f16_to_f32((uint16_t)v.z); o[5] = f16_to_f32((uint16_t)(v.z >> 16));

@@ -408,7 +408,11 @@ template <int TYPE> struct Lattice {
         }
         const int total = q.sort(nr * NG);
 #pragma unroll 1
-        for (int p = tid; p < total; p += TPB) {
+        // the queue runs from long lists to short ones: threads take it back and forth (0 .. TPB-1, TPB-1 .. 0, ...), so
+        // that no warp collects the longest entry of every turn
+        for (int p0 = 0, turn = 0; p0 < total; p0 += TPB, ++turn) {
+            const int p = p0 + ((turn & 1) ? TPB - 1 - tid : tid);
+            if (p >= total) continue;
             const unsigned it = q.item[p];
             const int t2 = (int)(it >> 3), slot = (int)(it & 7), k = slot % NG;
             const int list = -(int)T.map[q.u[slot][t2]] - 1;
@@ -888,7 +892,9 @@ template <bool M, int VARIANT> struct IQ1 {
             const int total = q.sort(NG);
             float (*term)[TPB] = sm.pa;               // the prefix sums are dead by now
 #pragma unroll 1
-            for (int p = tid; p < total; p += TPB) {
+            for (int p0 = 0, turn = 0; p0 < total; p0 += TPB, ++turn) {
+                const int p = p0 + ((turn & 1) ? TPB - 1 - tid : tid);
+                if (p >= total) continue;
                 const unsigned it = q.item[p];
                 const int t2 = (int)(it / NG), k = (int)(it % NG);
                 const int list = -T.map[q.u[k][t2]] - 1;

@@ -144,6 +144,13 @@ template <> struct LegacyRef<SG_Q5_1> {
         for (int m = 0; m < 4; ++m) st4(y + 8 + 4 * m, qs[m]);
     }
 };
+// (int)roundf(v) for |v| < 2^22 in five instructions: v + copysign(0.5, v) is exact except at |v| = 0.5 - 2^-25, where it
+// rounds up to 1; that value, like everything below 0.5, rounds to 0.  NaN gives 0 (roundf's conversion gives INT_MIN on
+// the reference's host, whose low byte is 0 too - only the low byte is used below).
+SG_DEVINL int round_away_small(float v) {
+    const int q = __float2int_rz(fadd(v, copysignf(0.5f, v)));
+    return fabsf(v) < 0.5f ? 0 : q;
+}
 template <> struct LegacyRef<SG_Q8_0> {
     static constexpr int QK = 32, BS = 34;
     static SG_DEVINL void block(const float (&x)[32], uint8_t* y) {
@@ -155,7 +162,7 @@ template <> struct LegacyRef<SG_Q8_0> {
         st2(y, f32_to_f16(d));
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-            const int a = (int)roundf(fmul(x[j], id)), b = (int)roundf(fmul(x[j + 1], id));
+            const int a = round_away_small(fmul(x[j], id)), b = round_away_small(fmul(x[j + 1], id));
             st2(y + 2 + j, (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8));
         }
     }
