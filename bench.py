@@ -289,7 +289,7 @@ def run_ours(args):
                            "per_type": table},
                 "clocks": clocks,
                 "e2e": {"value": world * out_bytes / e2e_s / 1e9, "unit": "GB/s",
-                        "h2d_bytes_per_step": int(hx.numel() * 2 + himx.numel() * 4), "d2h_bytes_per_step": int(out_bytes)},
+                        "h2d_bytes_per_step": int(world * (hx.numel() * 2 + himx.numel() * 4)), "d2h_bytes_per_step": int(world * out_bytes)},
                 "gpu_launches": int(launches),
                 "roofline": {"bound": "hbm", "kernel": f"k_quant {QFUN[dt][0]}{'+imx' if duse else ''} (largest share of the step)",
                              "achieved": ach, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": ach / peak, "traffic": None},
