@@ -37,25 +37,19 @@ template <class E> SG_DEVINL void field_symbols(int kd, int any, int tv, int dl,
 
 // ---- one coder for the three passes ---------------------------------------------------------------------------
 struct Coder {
-    int mode;                       // 0 histogram, 1 encode (symbols arrive in reverse decode order), 2 decode,
+    int mode;                       // 0 histogram (symbols in decode order), 1 encode (symbols in reverse decode order),
                                     // 3 stage: like encode, but the (table, symbol) pairs are only written down
     unsigned* counts;
     unsigned* stage; int nstaged;
-    const RansSym* enc; const uchar* lut;
-    unsigned x; ByteWriterDown wr; ByteReaderUp rd; uchar* slot; bool ovf;
-    SG_DEVINL void sym(int tab, int& s) {
+    const RansSym* enc;
+    unsigned x; ByteWriterDown wr; uchar* slot; bool ovf;
+    SG_DEVINL void put(int tab, int s) {
         if (mode == 0) { atomicAdd(counts + tab * 256 + s, 1u); return; }
         if (mode == 3) { stage[nstaged++] = (unsigned)(tab * 256 + s); return; }
-        if (mode == 1) {
-            if (ovf) return;
-            rans_put<12>(x, wr, enc[tab * 256 + s]);
-            if (wr.ptr() < slot + 64) ovf = true;
-            return;
-        }
-        s = (int)rans_get<12>(x, rd, lut + ((size_t)tab << 12), enc + tab * 256);
+        if (ovf) return;
+        rans_put<12>(x, wr, enc[tab * 256 + s]);
+        if (wr.ptr() < slot + 64) ovf = true;
     }
-    SG_DEVINL void put(int tab, int s) { sym(tab, s); }
-    SG_DEVINL int get(int tab) { int s = 0; sym(tab, s); return s; }
 };
 
 // ---- grid types: rank of the true lattice point among all points, by weighted distance to the seed -------------
@@ -94,42 +88,23 @@ template <int N> SG_DEVINL void scan_rank(const float* tab, const uint16_t* __re
         rank += d < dt || (d == dt && k < t);
     }
 }
-// the first TOPK points of that order                                                       (decode)
-template <int N> SG_DEVINL void scan_top(const float* tab, const uint16_t* __restrict__ gk, int gs, float& d1, float& d2, int* top) {
-    const float inf = __int_as_float(0x7f800000);
-    float td[TOPK];
-#pragma unroll
-    for (int j = 0; j < TOPK; ++j) { td[j] = inf; top[j] = j; }
-    for (int k = 0; k < gs; ++k) {
-        const float d = point_dist<N>(tab, __ldg(gk + k));
-        if (d < td[TOPK - 1]) {
-            td[TOPK - 1] = d; top[TOPK - 1] = k;
-#pragma unroll
-            for (int j = TOPK - 1; j > 0; --j)
-                if (td[j] < td[j - 1]) { const float a = td[j]; td[j] = td[j - 1]; td[j - 1] = a; const int b = top[j]; top[j] = top[j - 1]; top[j - 1] = b; }
-        }
-    }
-    d1 = td[0]; d2 = td[1];
-}
-
-// all symbols of one differing block of a grid type after its scale fields (qr.py:553-637).  fb: stored block (decode:
-// being rebuilt, fields already written), tv: its unpacked fields.
+// all symbols of one differing block of a grid type after its scale fields (qr.py:553-637), in the encoder's order.
+// fb: stored block, tv: its unpacked fields.
 template <int N, bool SGN>
 SG_DEVINL void grid_block(Coder& c, int T, int mv, uchar* fb, const uchar* pb, const int* tv, const uint16_t* __restrict__ gk,
                           long long gw0, int st, const uchar* sbase, int cols, const float* im, float* tab) {
     constexpr int B = N == 8 ? 2 : 3, ng = 8 / N;
     const int gs = grid_size(T);
-    const bool par = parity_type(T), dec = c.mode == 2;
+    const bool par = parity_type(T);
     float sx2 = 0.f;
     for (int i = 0; i < 256; ++i) { float xv, hv; seed_val(st, sbase, gw0 + i, xv, hv, cols); sx2 += xv * xv; }
     const float sigma2 = (T == 16 || T == 17) ? sx2 * (1.0f / 256.f) : 2.f * sx2 * (1.0f / 256.f);
     const long long col0 = cols > 0 ? gw0 % cols : 0;
     for (int ui = 0; ui < 32; ++ui) {
-        const int u = dec ? ui : 31 - ui;
+        const int u = 31 - ui;
         const int p4 = pos4(col0 + 8 * u, cols);
         const int rank0 = mv >= 2 ? GRANK2 + 4 * p4 : GRID_RANK;
         const int sign0 = mv >= 2 ? GSIGN2 + 16 * p4 : GRID_SIGN;
-        if (dec && T == 29) { if (c.get(GRID_SHIFT) ^ get_shift(pb, u)) put_shift(fb, u); }
         float gu[8], gw[8], gs_, gdl;
         int pn[8];
         gscale(T, fb, tv, u, gs_, gdl);
@@ -161,44 +136,21 @@ SG_DEVINL void grid_block(Coder& c, int T, int mv, uchar* fb, const uchar* pb, c
             const float m4 = fabsf(gu[j]) * 4.f;
             return sign0 + (lev == 0) * 8 + (m4 < 7.f ? (int)m4 : 7);
         };
-        if (!dec) {
-            for (int gg = 0; gg < ng; ++gg) tg[gg] = get_gidx(T, fb, u * ng + gg);
-            if (SGN) for (int j = 7; j >= 0; --j) {
-                if (par && j == 7) continue;
-                c.put(sign_ctx(j), get_neg(T, fb, 8 * u + j) ^ pn[j]);
-            }
-            for (int gg = ng - 1; gg >= 0; --gg) {
-                pair_tables<N, SGN>(tab, gu + gg * N, gw + gg * N, gdl);
-                int rank; float d1, d2;
-                scan_rank<N>(tab, gk, gs, tg[gg], d1, d2, rank);
-                const int ctx = rank0 + gapctx(d1, d2);
-                if (rank >= TOPK) { c.put(FESC_HI, tg[gg] >> 8); c.put(FESC_LO, tg[gg] & 255); c.put(ctx, TOPK); }
-                else c.put(ctx, rank);
-            }
-            if (T == 29) c.put(GRID_SHIFT, get_shift(fb, u) ^ get_shift(pb, u));
-            if (c.ovf) return;
-        } else {
-            for (int gg = 0; gg < ng; ++gg) {
-                pair_tables<N, SGN>(tab, gu + gg * N, gw + gg * N, gdl);
-                int top[TOPK]; float d1, d2;
-                scan_top<N>(tab, gk, gs, d1, d2, top);
-                const int r = c.get(rank0 + gapctx(d1, d2));
-                int t;
-                if (r >= TOPK) { const int lo = c.get(FESC_LO), hi = c.get(FESC_HI); t = (lo | (hi << 8)) % gs; }
-                else {
-                    t = top[0];
-#pragma unroll
-                    for (int j = 1; j < TOPK; ++j) if (j == r) t = top[j];
-                }
-                put_gidx(T, fb, u * ng + gg, t);
-                tg[gg] = t;
-            }
-            if (SGN) for (int j = 0; j < 8; ++j) {
-                if (par && j == 7) continue;
-                if (c.get(sign_ctx(j)) ^ pn[j]) put_neg(T, fb, 8 * u + j);
-            }
-            if (c.rd.over) return;
+        for (int gg = 0; gg < ng; ++gg) tg[gg] = get_gidx(T, fb, u * ng + gg);
+        if (SGN) for (int j = 7; j >= 0; --j) {
+            if (par && j == 7) continue;
+            c.put(sign_ctx(j), get_neg(T, fb, 8 * u + j) ^ pn[j]);
         }
+        for (int gg = ng - 1; gg >= 0; --gg) {
+            pair_tables<N, SGN>(tab, gu + gg * N, gw + gg * N, gdl);
+            int rank; float d1, d2;
+            scan_rank<N>(tab, gk, gs, tg[gg], d1, d2, rank);
+            const int ctx = rank0 + gapctx(d1, d2);
+            if (rank >= TOPK) { c.put(FESC_HI, tg[gg] >> 8); c.put(FESC_LO, tg[gg] & 255); c.put(ctx, TOPK); }
+            else c.put(ctx, rank);
+        }
+        if (T == 29) c.put(GRID_SHIFT, get_shift(fb, u) ^ get_shift(pb, u));
+        if (c.ovf) return;
     }
 }
 SG_DEVINL void grid_code(Coder& c, int T, int mv, uchar* fb, const uchar* pb, const int* tv, const uint16_t* gk, long long gw0, int st,
@@ -220,21 +172,17 @@ struct Args {
     const uint16_t* gk; const float* imx;
 };
 
-// scalar-code types: the codes of one differing block, forwards (histogram, decode) or backwards (encode)
+// scalar-code types: the codes of one differing block, forwards (histogram) or backwards (encode, stage)
 SG_DEVINL void scalar_codes(Coder& c, int T, int mv, uchar* fb, const uchar* pb, const int* tv, const Setup& u, long long gw0) {
     const long long col0 = u.m.cols > 0 ? gw0 % u.m.cols : 0;
-    const bool fwd = c.mode == 0 || c.mode == 2, dec = c.mode == 2;
+    const bool fwd = c.mode == 0;
     int tsub = -1; float ta = 0.f, tc = 0.f;
     for (int i = 0; i < u.qk; ++i) {
         const int w = fwd ? i : u.qk - 1 - i;
         if (w / u.sublen != tsub) { tsub = w / u.sublen; wscale(T, tv, tsub, ta, tc); }
         float xv, hv; seed_val(u.m.seed_type, u.sbase, gw0 + w, xv, hv, u.m.cols);
         int r, sgn, ctx; predict_code(T, ta, tc, pb, w, xv, hv, u.hboff, r, sgn, ctx, mv, pos8(col0 + w, u.m.cols));
-        if (dec) {
-            int q = r + sgn * (int)(signed char)c.get(ctx);
-            if (T == 8) q = (int)(signed char)(q & 255);
-            put_code(T, fb, w, q);
-        } else c.put(ctx, (sgn * (get_code(T, fb, w) - r)) & 255);
+        c.put(ctx, (sgn * (get_code(T, fb, w) - r)) & 255);
     }
 }
 
@@ -306,49 +254,6 @@ __global__ void __launch_bounds__(QR_TPB) k_qr_enc(const Args a, const RansSym* 
     rans_flush(c.x, c.wr);
     c.wr.flush(c.slot);
     out_len[s] = (unsigned)(c.slot + cap - c.wr.ptr());
-}
-
-__global__ void __launch_bounds__(QR_TPB) k_qr_dec(const Args a, const uchar* __restrict__ in, const unsigned long long* __restrict__ off,
-                                                   const RansSym* __restrict__ enc, const uchar* __restrict__ lut, uchar* __restrict__ F,
-                                                   int* __restrict__ status) {
-    const int s = blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= a.nseg) return;
-    const int T = a.T, mv = a.mv;
-    const Setup u = setup(T, a.seed, a.tm, a.sg, s);
-    const float* im = u.m.imx_off >= 0 ? a.imx + u.m.imx_off : nullptr;
-    Coder c; c.mode = 2; c.enc = enc; c.lut = lut; c.ovf = false;
-    c.rd.init(in + off[s], in + off[s + 1]);
-    c.x = rans_init(c.rd);
-    int prev = 1;
-    for (long long b = u.g.b0; b < u.g.b0 + u.g.nb; ++b) {
-        uchar* fb = F + b * u.bs; const uchar* pb = a.P + b * u.bs;
-        const int eq = c.get(FLAG + prev);
-        prev = eq;
-        if (eq) { for (int i = 0; i < u.bs; ++i) fb[i] = pb[i]; continue; }
-        for (int i = 0; i < u.bs; ++i) fb[i] = 0;
-        int tv[MAXF], pv[MAXF];
-        unpack_fields(T, pb, pv);
-        int any = 0;
-        for (int k = 0; k < u.nf; ++k) {
-            const int kd = fkind(T, k);
-            const int pr = fpred(T, mv, pv, k, k > 0 ? tv[0] : 0, k > 1 ? tv[1] : 0);
-            const int sym = c.get(fctx(kd, any));
-            int t;
-            if (kd < 2 && sym == 128) { const int lo = c.get(FESC_LO), hi = c.get(FESC_HI); t = lo | (hi << 8); }
-            else {
-                t = pr + (int)(signed char)sym;
-                if (kd < 2) t &= 0xffff;
-                else if (T == 14) t = (int)(signed char)(t & 255);
-            }
-            tv[k] = t; any |= t != pr;
-        }
-        pack_fields(T, fb, tv);
-        const long long gw0 = (b - u.m.blk0) * u.qk;
-        if (is_grid(T)) grid_code(c, T, mv, fb, pb, tv, a.gk, gw0, u.m.seed_type, u.sbase, u.m.cols, im, gtab);
-        else scalar_codes(c, T, mv, fb, pb, tv, u, gw0);
-        if (c.rd.over) break;
-    }
-    if (c.rd.over || c.x != RANS_L || c.rd.p != c.rd.end) atomicOr(status, SG_ST_CORRUPT);
 }
 
 // ---- decoder of the scalar-code types: a warp per segment ------------------------------------------------------------
