@@ -36,14 +36,16 @@ static __constant__ int8_t c_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -
 
 // ==================================================================================================
 // IQ4_NL / IQ4_XS
-// best_index_int8(16, kvalues_iq4nl, x), ggml-quants.c:28-37, without data-dependent table walks: the binary
-// search ends with val[ml] <= x < val[ml + 1], i.e. ml = number of interior levels that are <= x (the two early
-// returns of the C code fall out of the same formula); the levels themselves come from a 16-entry table in
-// shared memory (16 distinct banks, so a warp's lookups never conflict).  Returns the index, *q = its level.
+// best_index_int8(16, kvalues_iq4nl, x), ggml-quants.c:28-37.  The search of the C code ends with val[ml] <= x < val[ml + 1]
+// (its two early returns fall out of the same formula with ml clamped to 14), so ml is the largest index whose level
+// is <= x: four halving steps over the 16-entry table in shared memory (16 distinct banks: a warp's lookups never
+// conflict).  Returns the index, *q = its level.
 SG_DEVINL int best_index_iq4(float x, const float* __restrict__ kv, float* q) {
-    int ml = (x >= -104.f) + (x >= -83.f) + (x >= -65.f) + (x >= -49.f) + (x >= -35.f) + (x >= -22.f) + (x >= -10.f) +
-             (x >= 1.f) + (x >= 13.f) + (x >= 25.f) + (x >= 38.f) + (x >= 53.f) + (x >= 69.f) + (x >= 89.f);
-    if (x != x) ml = 14;                                   // NaN: every `x < val` test of the search fails
+    int ml = x >= kv[8] ? 8 : 0;
+    ml += x >= kv[ml + 4] ? 4 : 0;
+    ml += x >= kv[ml + 2] ? 2 : 0;
+    ml += x >= kv[ml + 1] ? 1 : 0;
+    if (ml > 14 || x != x) ml = 14;                        // NaN: every `x < val` test of the search fails
     const float a = kv[ml], b = kv[ml + 1];
     const bool lower = fsub(x, a) < fsub(b, x);
     *q = lower ? a : b;
