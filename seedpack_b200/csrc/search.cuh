@@ -143,6 +143,18 @@ SG_DEVINL int qkx_cand_code(float iscale, float mn, int nmax, float xi) {
     return clampi(nearest_int(v), 0, nmax);
 }
 
+// the same code as a float.  V3: the value that goes into nearest_int lies in (0, nmax], where the rounding add of
+// nearest_int yields the integer's float directly (v + 1.5 * 2^23 - 1.5 * 2^23), with no integer detour.
+template <int N, bool V3>
+SG_DEVINL float qkx_cand_level(float iscale, float mn, int nmax, float xi) {
+    if (V3) {
+        const float v = fmul(iscale, fsub(xi, mn));
+        const float r = fsub(fadd(fminf(v, (float)nmax), 12582912.f), 12582912.f);
+        return v > 0.f ? r : 0.f;
+    }
+    return (float)qkx_cand_code<N, V3>(iscale, mn, nmax, xi);
+}
+
 template <int N, bool V3>
 SG_DEVINL QkxBest make_qkx_quants(int nmax, const float (&x)[N], const float (&wt)[N],
                                   float rmin, float rdelta, int nstep, bool use_mad) {
@@ -180,9 +192,10 @@ SG_DEVINL QkxBest make_qkx_quants(int nmax, const float (&x)[N], const float (&w
         for (int is = 0; is <= nstep; ++is) {
             iscale = fdiv(fadd(fadd(rmin, fmul(rdelta, (float)is)), fn), fsub(mx, mn));
             float sum_l = 0.f, sum_l2 = 0.f, sum_xl = 0.f;
+            float lv[N];                       // the candidate's levels, kept for the error pass
 #pragma unroll
             for (int i = 0; i < N; ++i) {
-                const float fl = (float)qkx_cand_code<N, V3>(iscale, mn, nmax, x[i]);
+                const float fl = lv[i] = qkx_cand_level<N, V3>(iscale, mn, nmax, x[i]);
                 const float w = wt[i];
                 sum_l = fadd(sum_l, fmul(w, fl));
                 sum_l2 = fadd(sum_l2, fmul(fmul(w, fl), fl));
@@ -199,7 +212,7 @@ SG_DEVINL QkxBest make_qkx_quants(int nmax, const float (&x)[N], const float (&w
                 float err = 0.f;
 #pragma unroll
                 for (int i = 0; i < N; ++i) {
-                    const float fl = (float)qkx_cand_code<N, V3>(iscale, mn, nmax, x[i]);
+                    const float fl = lv[i];
                     float diff = fsub(fadd(fmul(this_scale, fl), this_min), x[i]);
                     diff = use_mad ? fabsf(diff) : fmul(diff, diff);
                     err = fadd(err, fmul(wt[i], diff));
