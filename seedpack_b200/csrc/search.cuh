@@ -22,6 +22,9 @@ SG_DEVINL int clampi(int v, int lo, int hi) { return max(lo, min(hi, v)); }
 
 // ---- make_qx_quants, rmse_type == 1 (the only mode the quantisers on this path use) -------------
 struct QxBest { float scale; float iscale; bool zero; };
+// clamp(nearest_int(v), -nmax, nmax - 1) as a float, for |v| far below 2^22 (here |v| <= nmax + 1): the rounding add of
+// nearest_int yields the integer's float directly
+SG_DEVINL float qx_level(float v, float fn) { return fminf(fmaxf(fsub(fadd(v, 12582912.f), 12582912.f), -fn), fn - 1.f); }
 
 template <int N, bool HAVE_W>
 SG_DEVINL QxBest make_qx_quants(int nmax, const float (&x)[N], const float (&qw)[N]) {
@@ -39,9 +42,8 @@ SG_DEVINL QxBest make_qx_quants(int nmax, const float (&x)[N], const float (&qw)
     float sumlx = 0.f, suml2 = 0.f;
 #pragma unroll
     for (int i = 0; i < N; ++i) {
-        const int l = clampi(nearest_int(fmul(iscale, x[i])), -nmax, nmax - 1);
         const float w = HAVE_W ? qw[i] : fmul(x[i], x[i]);
-        const float fl = (float)l;
+        const float fl = qx_level(fmul(iscale, x[i]), fn);
         sumlx = fadd(sumlx, fmul(fmul(w, x[i]), fl));
         suml2 = fadd(suml2, fmul(fmul(w, fl), fl));
     }
@@ -55,9 +57,8 @@ SG_DEVINL QxBest make_qx_quants(int nmax, const float (&x)[N], const float (&qw)
         sumlx = 0.f; suml2 = 0.f;
 #pragma unroll
         for (int i = 0; i < N; ++i) {
-            const int l = clampi(nearest_int(fmul(iscale, x[i])), -nmax, nmax - 1);
             const float w = HAVE_W ? qw[i] : fmul(x[i], x[i]);
-            const float fl = (float)l;
+            const float fl = qx_level(fmul(iscale, x[i]), fn);
             sumlx = fadd(sumlx, fmul(fmul(w, x[i]), fl));
             suml2 = fadd(suml2, fmul(fmul(w, fl), fl));
         }
