@@ -757,7 +757,7 @@ template <bool M, int VARIANT> struct IQ1 {
                 for (int i1 = 0; i1 <= BLK; ++i1) {
                     const float sx1 = sm.pa[i1][tid], sw1 = sm.pb[i1][tid];
                     const float ax = fsub(sx1, sx0), aw = fsub(sw1, sw0);
-#pragma unroll 1
+#pragma unroll 4
                     for (int i2 = i1; i2 <= BLK; ++i2) {
                         const float sx2 = sm.pa[i2][tid], sw2 = sm.pb[i2][tid];
                         const float bx = fsub(sx2, sx1), cx = fsub(sxn, sx2);
@@ -802,7 +802,7 @@ template <bool M, int VARIANT> struct IQ1 {
                 for (int i1 = 0; i1 <= 16; ++i1) {
                     const float x10 = sm.pa[i1][tid], x11 = sm.pa[17 + i1][tid];
                     const float w10 = sm.pb[i1][tid], w11 = sm.pb[17 + i1][tid];
-#pragma unroll 1
+#pragma unroll 4
                     for (int i2 = i1; i2 <= 16; ++i2) {
                         const float x20 = sm.pa[i2][tid], x21 = sm.pa[17 + i2][tid];
                         const float w20 = sm.pb[i2][tid], w21 = sm.pb[17 + i2][tid];
