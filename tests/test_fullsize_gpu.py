@@ -1,0 +1,96 @@
+"""Properties that do not depend on the size, checked at the benchmark's full size (one BF16 tensor of 4096 x 12288 with
+its importance matrix, seeded): the CPU checker would need minutes per type there, so these tests lean on what must
+hold whatever the size - rows are independent, a coded batch decodes to what was coded, coding does not depend on how
+the work was cut."""
+import numpy as np
+import pytest
+
+from tests import synth
+
+pytestmark = pytest.mark.gpu
+NROWS, NPR = 4096, 12288
+
+
+@pytest.fixture(scope="module")
+def tensor():
+    import torch
+    bits = synth.weights(NROWS, NPR, 1, edge_cases=False)
+    imx = synth.imatrix(NPR, 1)
+    x = torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16).reshape(-1)
+    return bits, imx, x
+
+
+@pytest.mark.parametrize("t", [8, 3, 12, 14, 17, 18, 19, 29, 23, 35])
+def test_rows_are_independent_at_full_size(tensor, t):
+    """the whole tensor in one launch gives the bytes of its two halves quantised on their own, and of a sample of
+    single rows against the CPU checker"""
+    import torch
+    from oracle import ref
+    from seedpack_b200.gpuquant import GPUQuant
+    from seedpack_b200.requant import QFUN
+    bits, imx, x = tensor
+    gq = GPUQuant()
+    w = None if t == 35 else imx
+    whole = gq.quantize_tensors(t, [(x, NPR)], [w], device=True)[0]
+    half = NROWS // 2 * NPR
+    a, b = gq.quantize_tensors(t, [(x[:half], NPR), (x[half:], NPR)], [w, w], device=True)
+    assert torch.equal(whole, torch.cat([a, b]))
+    assert gq.status() == 0
+    if ref.available():
+        _, qk, bs = QFUN[t]
+        rb = NPR // qk * bs
+        h = whole.cpu().numpy()
+        for r in (0, 1, 2047, 2048, 4095):
+            want = ref.quantize(t, synth.bf16_bits_to_f32(bits[r:r + 1]).reshape(1, NPR), w, threads=1)
+            assert np.array_equal(h[r * rb:(r + 1) * rb], want), (t, r)
+
+
+@pytest.mark.parametrize("T", [12, 17])
+def test_qr_round_trip_at_full_size(tensor, T):
+    """a coded batch of the full tensor decodes to the file, and the single-pass and the staged encoder agree"""
+    from seedpack_b200.gpuquant import GPUQuant
+    from seedpack_b200.qr import GRID_TYPES, QRCodec
+    bits, imx, x = tensor
+    gq = GPUQuant()
+    rng = np.random.default_rng(5)
+    imx2 = (imx * np.exp(rng.normal(0, 0.3, imx.shape))).astype(np.float32)
+    P = gq.quantize_tensors(T, [(x, NPR)], [imx])[0]
+    F = gq.quantize_tensors(T, [(x, NPR)], [imx2])[0].copy()
+    F[::997] ^= 0x5a
+    seed = bits.view(np.uint8).reshape(-1)
+    gim = imx if T in GRID_TYPES else None
+    ioff = 0 if T in GRID_TYPES else -1
+    buf = QRCodec().encode(T, [(F, P, 0, 30, NPR, ioff)], seed, gim)
+    out = QRCodec().decode(T, buf, [(P, 0, 30, NPR, ioff)], seed, gim)
+    assert np.array_equal(out.cpu().numpy(), F)
+    if T == 12:
+        assert QRCodec(staged=False).encode(T, [(F, P, 0, 30, NPR, ioff)], seed, gim) == buf
+
+
+def test_r2_round_trip_and_grouping_at_full_size(tensor):
+    """the R2 parts of the full tensor decode to its bytes, and do not depend on the group size"""
+    from seedpack_b200.bf16v2 import BF16v2, R2Tensors, layout_of
+    bits, _, _ = tensor
+    data = bits.view(np.uint8).reshape(-1)
+    half = len(data) // 2
+    layout = layout_of([("blk.0.ffn_up.weight", 0, half, NPR), ("blk.1.ffn_up.weight", half, half, NPR)], len(data))
+    parts = BF16v2().compress_parts(data, layout)
+    small = BF16v2(group_bytes=half).compress_parts(data, layout)
+    assert parts["stream"] == small["stream"] and parts["tables"] == small["tables"] and parts["side"] == small["side"]
+    dev, outs = R2Tensors(parts).decode(range(2))
+    h = dev.cpu().numpy()
+    for k, (off, nb, _, _) in enumerate(layout["t"]):
+        assert np.array_equal(h[outs[k]:outs[k] + nb], data[off:off + nb])
+
+
+def test_rans_round_trip_on_a_large_stream():
+    import torch
+    from seedpack_b200.rans import RansCodec
+    n, ntab = 1 << 27, 294
+    g = torch.Generator(device="cuda"); g.manual_seed(3)
+    sym = torch.where(torch.rand(n, generator=g, device="cuda") < 0.97, 0, torch.randint(0, 64, (n,), generator=g, device="cuda")).to(torch.uint8)
+    tab = torch.randint(0, 292, (n // 32,), generator=g, device="cuda").to(torch.int16)
+    c = RansCodec()
+    r = c.encode(sym, tab, 32, ntab)
+    out = c.decode(r["stream"], r["off"], tab, 32, n, r["freq"], r["used"], ntab)
+    assert torch.equal(out, sym) and c.status() == 0
