@@ -389,9 +389,9 @@ __global__ void __launch_bounds__(DW_WARPS * 32) k_qr_dec_warp(const Args a, con
             // contexts and predictions of the block's weights, side by side
             const long long gw0 = (b - u.m.blk0) * u.qk;
             const long long col0 = u.m.cols > 0 ? gw0 % u.m.cols : 0;
+            int tsub = -1; float ta = 0.f, tc = 0.f;
             for (int w = sub; w < u.qk; w += W) {
-                float ta, tc;
-                wscale(T, tv, w / u.sublen, ta, tc);
+                if (w / u.sublen != tsub) { tsub = w / u.sublen; wscale(T, tv, tsub, ta, tc); }
                 float xv, hv; seed_val(u.m.seed_type, u.sbase, gw0 + w, xv, hv, u.m.cols);
                 int r, sgn, ctx; predict_code(T, ta, tc, pbs, w, xv, hv, u.hboff, r, sgn, ctx, mv, pos8(col0 + w, u.m.cols));
                 m.ctx[w] = (unsigned short)ctx; m.pred[w] = (short)r; m.sgn[w] = (signed char)sgn;

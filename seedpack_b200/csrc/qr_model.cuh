@@ -286,7 +286,8 @@ SG_DEVINL void predict_code(int T, float a, float c, const uchar* pblk, int w, f
         hu = __fdiv_rn(h, __fmul_rn(fabsf(a), g));
     } else {
         u = __fdiv_rn(__fsub_rn(x, c), a);
-        hu = __fdiv_rn(h, fabsf(a));
+        // exact seeds carry h = 0: 0 / |a| is 0 unless a is 0 or NaN, where it is NaN - no division needed to know that
+        hu = h == 0.f ? ((a == 0.f || a != a) ? __int_as_float(0x7fc00000) : 0.f) : __fdiv_rn(h, fabsf(a));
     }
     if (!isfinite(u) || !isfinite(hu)) { r = get_code(T, pblk, w); s = 1; ctx = NSB_MAX + 63; return; }
     const float ru = rintf(u), fr = __fsub_rn(u, ru);
