@@ -78,14 +78,19 @@ template <int N> SG_DEVINL float point_dist(const float* tab, unsigned key) {
     return isnan(d) ? __int_as_float(0x7f800000) : d;
 }
 // the two smallest distances and the rank of point t in the order (distance, index)        (encode / histogram)
+// Keys are read two at a time (gs is even, gk 4-byte aligned); points before t count when they are at most as far as
+// t, points from t on when they are strictly closer (t itself is not).
 template <int N> SG_DEVINL void scan_rank(const float* tab, const uint16_t* __restrict__ gk, int gs, int t, float& d1, float& d2, int& rank) {
     const float inf = __int_as_float(0x7f800000);
     const float dt = point_dist<N>(tab, gk[t]);
+    const unsigned* gk2 = reinterpret_cast<const unsigned*>(gk);
     d1 = inf; d2 = inf; rank = 0;
-    for (int k = 0; k < gs; ++k) {
-        const float d = point_dist<N>(tab, __ldg(gk + k));
-        if (d < d1) { d2 = d1; d1 = d; } else if (d < d2) d2 = d;
-        rank += d < dt || (d == dt && k < t);
+    auto two_smallest = [&](float d) { d2 = fminf(d2, fmaxf(d1, d)); d1 = fminf(d1, d); };
+    for (int k = 0; k < gs / 2; ++k) {              // every lane runs the same trip count
+        const unsigned kk = __ldg(gk2 + k);
+        const float da = point_dist<N>(tab, kk & 0xffffu), db = point_dist<N>(tab, kk >> 16);
+        two_smallest(da); two_smallest(db);
+        rank += (2 * k < t ? da <= dt : da < dt) + (2 * k + 1 < t ? db <= dt : db < dt);
     }
 }
 // all symbols of one differing block of a grid type after its scale fields (qr.py:553-637), in the encoder's order.
