@@ -1,0 +1,186 @@
+"""Binding of the reference's host code to libseedgrow.so.
+
+The reference keeps its command line, repository logic, windowing and container in Python and reaches the GPU
+through CuPy (seedpack/xp.py).  `install()` puts this package's realisation of that layer underneath it:
+
+    cupy / cupyx            -> refbind.cupy_shim   (device arrays, launches, pools: seedpack/xp.py:6-18)
+    zstandard               -> seedpack_b200.zstd  (only where the zstandard package is not installed)
+    gpuquant.GPUQuant       -> refbind.quant.GPUQuant          (seedpack/gpuquant.py:285-456)
+    gpuquant.to_host        -> refbind.quant.to_host           (gpuquant.py:262-282)
+    qr.encode / qr.decode   -> seedpack_b200.qr.QRCodec        (seedpack/qr.py:1007-1090; model once per block)
+    BF16v2._stats           -> sg_r2_stats                     (seedpack/bf16v2.py:225-244)
+    M28RepoGPU._float_dev   -> sg_convert_float                (seedpack/repo3.py:673-689)
+    every RawModule kernel  -> refbind.kernels                 (R2, detmath, gather, single-pass QR, dequantisers)
+    cpukernels.RawModule    -> raises                          (the reference's CUDA source is never compiled)
+
+After that `seedpack.cli.main()` - or `python -m seedpack_b200.refbind pack|unpack|test|list ...` - is the reference's
+own program with every kernel served by this library.  The reference is found as an installed / importable
+`seedpack` package, under $SEEDPACK_REFERENCE, or in baseline/_ref of this tree.
+"""
+import importlib
+import importlib.util
+import os
+import sys
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+_state = {}
+
+
+def find_reference():
+    """directory that holds the reference's `seedpack` package, or None"""
+    cands = [os.environ.get("SEEDPACK_REFERENCE"), os.path.join(_ROOT, "baseline", "_ref")]
+    for c in cands:
+        if c and os.path.isfile(os.path.join(c, "seedpack", "repo3.py")):
+            return c
+    spec = importlib.util.find_spec("seedpack")
+    if spec is not None and spec.origin:
+        return os.path.dirname(os.path.dirname(spec.origin))
+    return None
+
+
+def available():
+    return find_reference() is not None
+
+
+def install(reference=None, staged_qr=True):
+    """bind the reference (see the module docstring) -> its `seedpack` package.  Idempotent."""
+    if "pkg" in _state:
+        return _state["pkg"]
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("seedpack_b200.refbind needs a CUDA device: there is no CPU path (the reference has --cpu)")
+    if os.environ.get("SEEDPACK_CPU") == "1":
+        raise RuntimeError("SEEDPACK_CPU=1 selects the reference's own CPU kernels; unset it to bind libseedgrow.so")
+    if "seedpack" in sys.modules:
+        raise RuntimeError("the reference was imported before refbind.install()")
+    ref = reference or find_reference()
+    if ref is None:
+        raise RuntimeError("the reference package `seedpack` was not found (install it, or set SEEDPACK_REFERENCE)")
+    from .. import _lib
+    _lib.lib()                                    # fails loudly if the CUDA library is not built
+    from . import cupy_shim, kernels, quant
+    sys.modules["cupy"] = cupy_shim
+    sys.modules["cupyx"] = cupy_shim.cupyx
+    if importlib.util.find_spec("zstandard") is None:
+        from .. import zstd
+        sys.modules["zstandard"] = zstd
+    if ref not in sys.path:
+        sys.path.insert(0, ref)
+    import seedpack
+    from seedpack import cpukernels, xp
+    if xp.CPU or xp.cp is not cupy_shim:
+        raise RuntimeError("the reference did not pick up the binding's array module")
+
+    def _no_cpu_kernels(*a, **kw):
+        raise RuntimeError("the reference's CUDA source is not compiled in this process: kernels come from libseedgrow.so")
+    cpukernels.RawModule = _no_cpu_kernels
+    from seedpack import bf16v2, gpuquant, qr, repo3
+    gpuquant.GPUQuant = repo3.GPUQuant = quant.GPUQuant
+    gpuquant.to_host = repo3.to_host = quant.to_host
+    qr._GQ = None
+    _bind_qr(qr, staged_qr)
+    _bind_r2(bf16v2)
+    _bind_float(repo3)
+    _state["pkg"] = seedpack
+    return seedpack
+
+
+# ---- QR ---------------------------------------------------------------------------------------------------------------
+def _bind_qr(qr, staged):
+    """qr.encode / qr.decode through QRCodec: the model of a block is run once (sg_qr_stage*), where the reference's
+    kernels - and their one-to-one bindings in refbind.kernels - run it in the histogram and again in the coder"""
+    import numpy as np
+    import torch
+    from .. import qr as own
+    from . import cupy_shim as cp
+    from .quant import from_torch
+    if not staged:
+        return
+    codecs = {}
+
+    def codec():
+        d = torch.cuda.current_device()
+        if d not in codecs:
+            codecs[d] = own.QRCodec(d, staged=True)
+        return codecs[d]
+
+    def arr(a):
+        """host or device bytes of a tensor as QRCodec takes them"""
+        return a.dev_in() if isinstance(a, cp.ndarray) else a
+
+    def encode(T, items, seed_dev, imx_dev=None, mv=None):
+        its = [(arr(it[0]), arr(it[1])) + tuple(it[2:]) for it in items]
+        return codec().encode(T, its, arr(seed_dev), None if imx_dev is None else arr(imx_dev).view(torch.float32), mv)
+
+    def decode(T, buf, items, seed_dev, imx_dev=None):
+        its = [(arr(it[0]),) + tuple(it[1:]) for it in items]
+        F = codec().decode(T, buf, its, arr(seed_dev), None if imx_dev is None else arr(imx_dev).view(torch.float32))
+        return from_torch(F)
+
+    encode.__doc__, decode.__doc__ = qr.encode.__doc__, qr.decode.__doc__
+    qr.encode, qr.decode = encode, decode
+
+
+# ---- R2 ---------------------------------------------------------------------------------------------------------------
+def _bind_r2(bf16v2):
+    """BF16v2 and R2Tensors stay the reference's classes; their kernels come from refbind.kernels.  The per-tensor
+    statistics (`_stats`: a chain of array operations over the whole tensor around detmath) are one library call"""
+    import ctypes
+    import numpy as np
+    import torch
+    from .. import _lib
+    from . import cupy_shim as cp
+
+    def _stats(self, dev, rl):
+        nr = dev.size // 2 // rl
+        rfi, cfi, scl = cp.empty(nr, np.int16), cp.empty(rl, np.int16), cp.empty(rl, np.int8)
+        L = _lib.lib()
+        need = L.sg_r2_stats_scratch_bytes(nr, rl)
+        scratch = torch.empty(need + 16, dtype=torch.uint8, device=dev.dev_in().device)
+        p = lambda t: ctypes.c_void_p(t.data_ptr())
+        _lib.check(L.sg_r2_stats(torch.cuda.current_device(), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
+                                 p(dev.dev_in()), nr, rl, p(rfi.dev_out()), p(cfi.dev_out()), p(scl.dev_out()), p(scratch), need),
+                   "sg_r2_stats")
+        return rfi, cfi, scl
+
+    bf16v2.BF16v2._stats = _stats
+
+
+# ---- float tensors -----------------------------------------------------------------------------------------------------
+def _bind_float(repo3):
+    import ctypes
+    import numpy as np
+    import torch
+    from .. import _lib
+    from . import cupy_shim as cp
+    F32, F16, BF16 = repo3.F32, repo3.F16, repo3.BF16
+    code = {BF16: (_lib.DT_BF16, 2), F16: (_lib.DT_F16, 2), F32: (_lib.DT_F32, 4)}
+    reference_float_dev = repo3.M28RepoGPU._float_dev
+
+    def _float_dev(self, bt, ttype, dev=None, lo=0, hi=None):
+        a = self._src(bt, dev=dev)
+        if bt.type not in code or not isinstance(a, cp.ndarray):
+            return reference_float_dev(self, bt, ttype, dev, lo, hi)      # a quantised seed: dequantised first
+        a = a[lo:hi]
+        if bt.type == ttype:
+            return a.view(np.uint8)
+        (sd, _), (dd, dsz) = code[bt.type], code[ttype]
+        y = cp.empty(a.size * dsz, np.uint8)
+        src = a.dev_in()
+        if src.data_ptr() % 16:
+            src = src.clone()
+        _lib.check(_lib.lib().sg_convert_float(torch.cuda.current_device(), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
+                                               ctypes.c_void_p(src.data_ptr()), sd, ctypes.c_void_p(y.dev_out().data_ptr()), dd, a.size),
+                   "sg_convert_float")
+        return y
+
+    repo3.M28RepoGPU._float_dev = _float_dev
+
+
+def main(argv=None):
+    """the reference's command line on the bound kernels"""
+    install()
+    from seedpack import cli
+    if argv is not None:
+        sys.argv = ["seedpack"] + list(argv)
+    return cli.main()

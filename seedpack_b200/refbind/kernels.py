@@ -1,0 +1,251 @@
+"""Bindings of the reference's kernel names to the seedgrow C ABI.
+
+`function(name)` returns a callable with CuPy's launch signature `f(grid, block, args, shared_mem=0)`; `args` are
+the arguments the reference passes to its own kernel of that name (device arrays of refbind.cupy_shim, NumPy
+scalars).  Grid and block are ignored: each C-ABI entry point chooses its own launch.  A name without a binding
+raises, so nothing of the reference's CUDA source can run by accident.
+
+    reference kernel (file:line)                       C-ABI entry point
+    v2_hist / v2_enc / v2_dec   bf16v2.py:63-137       sg_r2_hist / sg_r2_encode / sg_r2_decode
+    row_hash                    bf16v2.py:148-155      sg_row_hash
+    build_lut                   bf16v2.py:139, qr.py:889   folded into the decoders' table preparation (sg_rans_tables)
+    gather                      qr.py:880-887, gpu2.py     sg_scan_gather
+    qr_hist / qr_enc / qr_dec   qr.py:674-807          sg_residual_blocks + sg_qr_hist / sg_qr_encode / sg_qr_decode
+    dm_log2 / dm_exp2 / dm_rows / dm_cols   detmath.py:67-106   sg_dm_log2 / sg_dm_exp2 / sg_dm_rows / sg_dm_cols
+    k_dq_<type>                 gpuquant.py:215-219    sg_dequantize
+    vq_bf16_to_f32 (elementwise) gpuquant.py:248-249   sg_convert_float
+
+The coders' tables: the reference hands its kernels (remap, freq, cum[, lut]); the C ABI wants the entries
+sg_rans_tables makes from the full frequency array.  `_tables` scatters the used rows into the full array on the
+device and keeps the result for the arrays it was made from (a coding pass launches several times with the same
+tables).
+"""
+import ctypes
+from collections import OrderedDict
+
+import numpy as np
+import torch
+
+from .. import _lib
+from ..requant import QFUN
+
+QR_NTAB, QR_PB, R2_PB = 294, 12, 15
+QR_BS = {2: 18, 3: 20, 6: 22, 7: 24, 8: 34, 10: 84, 11: 110, 12: 144, 13: 176, 14: 210, 20: 18, 23: 136, 42: 18,
+         16: 66, 17: 74, 18: 98, 19: 50, 21: 110, 22: 82, 29: 56}
+GRID_TYPES = {16, 17, 18, 19, 21, 22, 29}
+
+
+def _dev():
+    return torch.cuda.current_device()
+
+
+def _st():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _i(x):
+    return int(x)
+
+
+_TABS = OrderedDict()
+
+
+def _tables(remap, freq, pb, lut):
+    """(remap int32[ntab], freq uint16[nused][256]) -> (encoder entries, decoder symbol table or None) on the device"""
+    key = (id(remap.st), remap.off, id(freq.st), freq.off, pb)
+    hit = _TABS.get(key)
+    if hit is not None and (hit[1] is not None or not lut):
+        _TABS.move_to_end(key)
+        return hit[0], hit[1]
+    ntab = remap.size
+    r = remap.dev_in().view(torch.int32).to(torch.int64)
+    f = freq.dev_in().view(torch.int16).view(-1, 256)
+    full = torch.zeros((ntab, 256), dtype=torch.int16, device=f.device)
+    used = torch.nonzero(r >= 0).reshape(-1)
+    if used.numel():
+        full[used] = f[r[used]]
+    enc = torch.empty(ntab * 256 * 2, dtype=torch.int32, device=f.device)
+    l = torch.empty(ntab << pb, dtype=torch.uint8, device=f.device) if lut else None
+    _lib.check(_lib.lib().sg_rans_tables(_dev(), _st(), _p(full), ntab, pb, _p(enc), _p(l)), "sg_rans_tables")
+    _TABS[key] = (enc, l, remap, freq)           # the source arrays stay alive with the entry: their ids stay theirs
+    while len(_TABS) > 6:
+        _TABS.popitem(last=False)
+    return enc, l
+
+
+def _seg_ends(off_t, total):
+    """first bytes of the segments (any order, together covering [0, total)) -> one past their last bytes"""
+    srt, idx = torch.sort(off_t)
+    end_sorted = torch.cat([srt[1:], torch.tensor([total], dtype=srt.dtype, device=srt.device)])
+    end = torch.empty_like(off_t)
+    end[idx] = end_sorted
+    return end
+
+
+# ---- R2 -----------------------------------------------------------------------------------------------------------
+def _v2_hist(args):
+    dev, tb, sg, nseg, rfi, cfi, scl, rm, counts = args
+    _lib.check(_lib.lib().sg_r2_hist(_dev(), _st(), _p(dev.dev_in()), _p(tb.dev_in()), _p(sg.dev_in()), _i(nseg), _p(rfi.dev_in()),
+                                     _p(cfi.dev_in()), _p(scl.dev_in()), _p(rm.dev_in()), _p(counts.dev_inout())), "sg_r2_hist")
+
+
+def _v2_enc(args):
+    dev, tb, sg, nseg, rfi, cfi, scl, rowmap, remap, freq, cum, out, cap, out_len = args
+    enc, _ = _tables(remap, freq, R2_PB, False)
+    _lib.check(_lib.lib().sg_r2_encode(_dev(), _st(), _p(dev.dev_in()), _p(tb.dev_in()), _p(sg.dev_in()), _i(nseg), _p(rfi.dev_in()),
+                                       _p(cfi.dev_in()), _p(scl.dev_in()), _p(rowmap.dev_in()), _p(enc), _p(out.dev_out()), _i(cap),
+                                       _p(out_len.dev_out())), "sg_r2_encode")
+
+
+def _v2_dec(args):
+    stream, offs, dev, tb, sg, nseg, rfi, cfi, scl, rowmap, remap, freq, cum, lut = args
+    enc, l = _tables(remap, freq, R2_PB, True)
+    o = offs.dev_in().view(torch.int64)
+    e = _seg_ends(o, stream.size)
+    _lib.check(_lib.lib().sg_r2_decode(_dev(), _st(), _p(stream.dev_in()), _p(o), _p(e), _p(dev.dev_out()), _p(tb.dev_in()), _p(sg.dev_in()),
+                                       _i(nseg), _p(rfi.dev_in()), _p(cfi.dev_in()), _p(scl.dev_in()), _p(rowmap.dev_in()), _p(enc), _p(l)),
+               "sg_r2_decode")
+    _corrupt("R2")
+
+
+def _corrupt(what):
+    bits = ctypes.c_int(0)
+    _lib.check(_lib.lib().sg_status_fetch(_dev(), _st(), ctypes.byref(bits)), "sg_status_fetch")
+    if bits.value & 4:
+        raise ValueError(f"{what}: corrupt coded stream")
+
+
+def _row_hash(args):
+    u, nr, rl, h = args
+    _lib.check(_lib.lib().sg_row_hash(_dev(), _st(), _p(u.dev_in()), _i(nr), _i(rl), _p(h.dev_out())), "sg_row_hash")
+
+
+def _build_lut(args):
+    pass                                   # the decoders' symbol table is made with their encoder entries (_tables)
+
+
+def _gather(args):
+    out, cap, out_len, offs, nseg, dst = args
+    if _i(nseg) == 0:
+        return
+    _lib.check(_lib.lib().sg_scan_gather(_dev(), _st(), _p(out.dev_in()), _i(cap), _p(out_len.dev_in()), _i(nseg), _p(dst.dev_out()),
+                                         dst.size, _p(offs.dev_inout())), "sg_scan_gather")
+
+
+# ---- QR (single-pass kernels) -------------------------------------------------------------------------------------
+def _qr_common(T, F, P, imx):
+    T = _i(T)
+    if T in GRID_TYPES:
+        from .. import tables
+        tables.install(_dev())
+    nb = F.size // QR_BS[T]
+    ne = torch.empty(max(nb, 1), dtype=torch.uint8, device=F.dev_in().device)
+    cnt = torch.zeros(1, dtype=torch.int64, device=ne.device)
+    _lib.check(_lib.lib().sg_residual_blocks(_dev(), _st(), _p(F.dev_in()), _p(P.dev_in()), QR_BS[T], nb, _p(ne), _p(cnt)), "sg_residual_blocks")
+    return T, ne
+
+
+def _qr_hist(args):
+    T, F, P, seed, tm, sg, nseg, counts, gk, imx, mv = args
+    T, ne = _qr_common(T, F, P, imx)
+    _lib.check(_lib.lib().sg_qr_hist(_dev(), _st(), T, _p(F.dev_in()), _p(P.dev_in()), _p(ne), _p(seed.dev_in()), _p(tm.dev_in()), _p(sg.dev_in()),
+                                     _i(nseg), _p(imx.dev_in()), _p(counts.dev_inout()), _i(mv)), "sg_qr_hist")
+
+
+def _qr_enc(args):
+    T, F, P, seed, tm, sg, nseg, remap, freq, cum, out, cap, out_len, gk, imx, mv = args
+    T, ne = _qr_common(T, F, P, imx)
+    enc, _ = _tables(remap, freq, QR_PB, False)
+    _lib.check(_lib.lib().sg_qr_encode(_dev(), _st(), T, _p(F.dev_in()), _p(P.dev_in()), _p(ne), _p(seed.dev_in()), _p(tm.dev_in()),
+                                       _p(sg.dev_in()), _i(nseg), _p(imx.dev_in()), _p(enc), _p(out.dev_out()), _i(cap), _p(out_len.dev_out()),
+                                       _i(mv)), "sg_qr_encode")
+
+
+def _qr_dec(args):
+    T, stream, offs, P, seed, tm, sg, nseg, remap, freq, cum, lut, F, gk, imx, mv = args
+    T = _i(T)
+    if T in GRID_TYPES:
+        from .. import tables
+        tables.install(_dev())
+    enc, l = _tables(remap, freq, QR_PB, True)
+    o = offs.dev_in().view(torch.int64)
+    off = torch.cat([o, torch.tensor([stream.size], dtype=torch.int64, device=o.device)])
+    _lib.check(_lib.lib().sg_qr_decode(_dev(), _st(), T, _p(stream.dev_in()), _p(off), _p(P.dev_in()), _p(seed.dev_in()), _p(tm.dev_in()),
+                                       _p(sg.dev_in()), _i(nseg), _p(imx.dev_in()), _p(enc), _p(l), _p(F.dev_out()), _i(mv)), "sg_qr_decode")
+    _corrupt("QR batch")
+
+
+# ---- detmath ---------------------------------------------------------------------------------------------------------
+def _dm_log2(args):
+    x, n, y = args
+    _lib.check(_lib.lib().sg_dm_log2(_dev(), _st(), _p(x.dev_in()), _i(n), _p(y.dev_out())), "sg_dm_log2")
+
+
+def _dm_exp2(args):
+    x, n, y = args
+    _lib.check(_lib.lib().sg_dm_exp2(_dev(), _st(), _p(x.dev_in()), _i(n), _p(y.dev_out())), "sg_dm_exp2")
+
+
+def _dm_rows(args):
+    x, nr, nc, square, out = args
+    _lib.check(_lib.lib().sg_dm_rows(_dev(), _st(), _p(x.dev_in()), _i(nr), _i(nc), _i(square), _p(out.dev_out())), "sg_dm_rows")
+
+
+def _dm_cols(args):
+    x, nr, nc, square, m, has_mask, out = args
+    _lib.check(_lib.lib().sg_dm_cols(_dev(), _st(), _p(x.dev_in()), _i(nr), _i(nc), _i(square), _p(m.dev_in()) if _i(has_mask) else None,
+                                     _p(out.dev_out())), "sg_dm_cols")
+
+
+# ---- dequantisers, float conversion ------------------------------------------------------------------------------------
+def _dequant(T):
+    qk, bs = QFUN[T][1], QFUN[T][2]
+
+    def f(args):
+        y, x, nrows, npr, rb = args
+        n = _i(nrows) * _i(npr)
+        if T in GRID_TYPES:
+            from .. import tables
+            tables.install(_dev())
+        _lib.check(_lib.lib().sg_dequantize(_dev(), _st(), T, _p(y.dev_in()), _p(x.dev_out()), n), f"sg_dequantize(type {T})")
+    return f
+
+
+def _bf16_to_f32(a, y=None):
+    from . import cupy_shim as cp
+    if y is None:
+        y = cp.empty(a.shape, np.float32)
+    _lib.check(_lib.lib().sg_convert_float(_dev(), _st(), _p(a.dev_in()), _lib.DT_BF16, _p(y.dev_out()), _lib.DT_F32, a.size), "sg_convert_float")
+    return y
+
+
+_BOUND = {"v2_hist": _v2_hist, "v2_enc": _v2_enc, "v2_dec": _v2_dec, "row_hash": _row_hash, "build_lut": _build_lut,
+          "gather": _gather, "qr_hist": _qr_hist, "qr_enc": _qr_enc, "qr_dec": _qr_dec,
+          "dm_log2": _dm_log2, "dm_exp2": _dm_exp2, "dm_rows": _dm_rows, "dm_cols": _dm_cols}
+for _t, (_name, _, _) in QFUN.items():
+    _BOUND["k_dq_" + _name[len("quantize_"):]] = _dequant(_t)
+
+
+def function(name):
+    f = _BOUND.get(name)
+    if f is None:
+        raise NotImplementedError(f"kernel '{name}' of the reference has no binding to libseedgrow.so "
+                                  "(its CUDA source is never compiled here)")
+
+    def launch(grid, block, args, shared_mem=0):
+        f(args)
+    launch.__name__ = name
+    return launch
+
+
+def elementwise(name):
+    if name == "vq_bf16_to_f32":
+        return _bf16_to_f32
+
+    def missing(*a, **kw):
+        raise NotImplementedError(f"elementwise kernel '{name}' of the reference has no binding")
+    return missing

@@ -1,12 +1,9 @@
-"""Type table and importance-matrix loaders (host side).
+"""Type table of the quantisers (host side).
 
-Mirrors seedpack/requant.py: `QFUN` (:21-27) and `load_imatrix` / `imatrix_chunks` (:59-91) keep their
-names and meanings; the CPU quantiser binding of the reference (:114-134) has no counterpart here -
-quantisation runs on the GPU only (see gpuquant.GPUQuant).
+`QFUN` keeps the name and meaning of seedpack/requant.py:21-27.  The importance-matrix loaders of that file
+(:59-112) are host code that stays the reference's; its CPU quantiser binding (:114-134) has no counterpart
+here - quantisation runs on the GPU only (see gpuquant.GPUQuant).
 """
-import struct
-
-import numpy as np
 
 # ggml type -> (function name, block elements, block bytes)
 QFUN = {2: ("quantize_q4_0", 32, 18), 3: ("quantize_q4_1", 32, 20), 6: ("quantize_q5_0", 32, 22),
@@ -23,33 +20,3 @@ QFUN = {2: ("quantize_q4_0", 32, 18), 3: ("quantize_q4_1", 32, 20), 6: ("quantiz
 NEEDS_IMATRIX = {16, 17, 19}
 # (type, variant) pairs beyond variant 0 (seedpack/gpuquant.py:182-185)
 VARIANTS = {29: 1}
-
-
-def load_imatrix(path_or_bytes, divide=True):
-    """llama.cpp legacy imatrix .dat -> {tensor name: float32 array}, values divided by the call
-    count as llama-quantize does (seedpack/requant.py:59-74)."""
-    buf = open(path_or_bytes, "rb").read() if isinstance(path_or_bytes, str) else path_or_bytes
-    if buf[:4] == b"GGUF":
-        raise NotImplementedError("GGUF-form imatrix files are read by the archive layer, not here")
-    (n,), pos, out = struct.unpack_from("<i", buf), 4, {}
-    for _ in range(n):
-        (ln,) = struct.unpack_from("<i", buf, pos); pos += 4
-        name = buf[pos:pos + ln].decode(); pos += ln
-        ncall, nval = struct.unpack_from("<ii", buf, pos); pos += 8
-        v = np.frombuffer(buf, np.float32, nval, pos).copy(); pos += 4 * nval
-        if divide and ncall > 0:
-            v /= np.float32(ncall)
-        out[name] = v
-    return out
-
-
-def imatrix_chunks(buf):
-    """chunk count written after the entries of a legacy .dat, None if absent (seedpack/requant.py:77-91)"""
-    try:
-        (n,), pos = struct.unpack_from("<i", buf), 4
-        for _ in range(n):
-            (ln,) = struct.unpack_from("<i", buf, pos); pos += 4 + ln
-            _, nval = struct.unpack_from("<ii", buf, pos); pos += 8 + 4 * nval
-        return struct.unpack_from("<i", buf, pos)[0] if len(buf) >= pos + 4 else None
-    except struct.error:
-        return None

@@ -47,12 +47,30 @@ def test_zstd_binding_roundtrip():
     assert zstd.decompress(zstd.compress(b"", 19), 16) == b""
 
 
-def test_imatrix_loader(tmp_path):
-    import struct
-    from seedpack_b200.requant import imatrix_chunks, load_imatrix
-    vals = np.arange(8, dtype=np.float32)
-    name = b"blk.0.ffn_up.weight"
-    buf = struct.pack("<i", 1) + struct.pack("<i", len(name)) + name + struct.pack("<ii", 4, 8) + vals.tobytes() + struct.pack("<i", 77)
-    d = load_imatrix(buf)
-    assert np.array_equal(d["blk.0.ffn_up.weight"], vals / 4)
-    assert imatrix_chunks(buf) == 77
+def test_zstd_streams_and_prefix_dictionary():
+    """the parts of the zstandard interface the archive layer uses: streamed compression with a pledged size and worker
+    threads, a raw-content dictionary, and the forward reader"""
+    import io
+    from seedpack_b200 import zstd
+    rng = np.random.default_rng(5)
+    head = rng.integers(0, 256, 4096, np.uint8).tobytes()
+    data = head * 3 + bytes(200000) + rng.integers(0, 4, 300000, np.uint8).tobytes()
+    zd = zstd.ZstdCompressionDict(head, dict_type=zstd.DICT_TYPE_RAWCONTENT)
+    prm = zstd.ZstdCompressionParameters.from_level(7, window_log=25, threads=4)
+    whole = zstd.ZstdCompressor(compression_params=prm, dict_data=zd).compress(data)
+    assert zstd.ZstdDecompressor(dict_data=zd).decompress(whole) == data
+    obj = zstd.ZstdCompressor(compression_params=prm, dict_data=zd).compressobj(size=len(data))
+    parts = [obj.compress(data[o:o + 70001]) for o in range(0, len(data), 70001)] + [obj.flush()]
+    frame = b"".join(parts)
+    out = bytearray(len(data))
+    with zstd.ZstdDecompressor(dict_data=zd).stream_reader(io.BytesIO(frame), read_size=1 << 12) as r:
+        o = 0
+        while o < len(out):
+            k = r.readinto(memoryview(out)[o:o + 50000])
+            assert k
+            o += k
+    assert bytes(out) == data
+    with zstd.ZstdDecompressor(dict_data=zd).stream_reader(frame) as r:
+        assert r.read() == data
+    plain = zstd.ZstdCompressor(level=19).compress(data)
+    assert len(whole) < len(plain)           # the dictionary removes the three copies of `head`
