@@ -228,7 +228,10 @@ class BF16v2:
             off = torch.empty(nseg + 1, dtype=torch.int64, device=self.device)
             with _lib.timed("scan_gather"):
                 _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, None, 0, _p(off)), "sg_scan_gather")
-            if self._status() & 2:
+            bits = self._status()
+            if bits & 4:
+                raise ValueError("rANS encoder: a coded symbol has frequency 0 in its table")
+            if bits & 2:
                 raise RuntimeError("rANS segment overflow")
             total = int(off[-1].item())
             dst = torch.empty(total + 32, dtype=torch.uint8, device=self.device)
@@ -260,8 +263,8 @@ class R2Tensors:
         self.rfi = _dev(np.frombuffer(side, np.int16, nrow, 0).copy(), self.device)
         self.cfi = _dev(np.frombuffer(side, np.int16, ncol, 2 * nrow).copy(), self.device)
         self.scl = _dev(np.frombuffer(side, np.int8, ncol, 2 * nrow + 2 * ncol).copy(), self.device)
-        freq, used = load_tables(parts["tables"])
         self.ntab = layout["nroles"] * TPT
+        freq, used = load_tables(parts["tables"], PB, self.ntab)
         helper = BF16v2(device=self.device.index)
         self.enc, self.lut = helper._tables(freq, used, self.ntab, lut=True)
         lens = np.frombuffer(zstd.decompress(bytes(parts["lens"]), 1 << 32), np.uint32)

@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(QR_TPB) k_qr_enc(const Args a, const RansSym* 
     if (c.ovf) { out_len[s] = 0xffffffffu; return; }
     rans_flush(c.x, c.wr);
     c.wr.flush(c.slot);
-    out_len[s] = (unsigned)(c.slot + cap - c.wr.ptr());
+    out_len[s] = c.wr.bad ? LEN_NOFREQ : (unsigned)(c.slot + cap - c.wr.ptr());
 }
 
 // ---- decoder of the scalar-code types: a warp per segment ------------------------------------------------------------
@@ -717,7 +717,7 @@ __global__ void __launch_bounds__(QR_TPB) k_qr_stage_code(const SG* __restrict__
     if (ovf) { out_len[s] = 0xffffffffu; return; }
     rans_flush(x, wr);
     wr.flush(slot);
-    out_len[s] = (unsigned)(slot + cap - wr.ptr());
+    out_len[s] = wr.bad ? LEN_NOFREQ : (unsigned)(slot + cap - wr.ptr());
 }
 
 }  // namespace qr

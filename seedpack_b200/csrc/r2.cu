@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(TPB) k_r2_enc(const unsigned char* __restrict_
     }
     rans_flush(x, wr);
     wr.flush(slot);
-    out_len[s] = (unsigned)(slot + cap - wr.ptr());
+    out_len[s] = wr.bad ? LEN_NOFREQ : (unsigned)(slot + cap - wr.ptr());
 }
 
 __global__ void __launch_bounds__(TPB) k_r2_dec(const unsigned char* __restrict__ in, const unsigned long long* __restrict__ in_off,

@@ -30,7 +30,8 @@ __global__ void __launch_bounds__(256) k_rans_tables(const uint16_t* __restrict_
     cum[s + 1] = incl;
     if (s == 0) cum[0] = 0;
     __syncthreads();
-    if (s == 255 && incl != 0 && incl != (1u << pb)) atomicOr(status, SG_ST_CORRUPT);     // a used table must sum to 2^PB
+    const bool whole = cum[256] == (1u << pb);                                             // a used table must sum to 2^PB
+    if (s == 255 && incl != 0 && !whole) atomicOr(status, SG_ST_CORRUPT);
     const unsigned c = incl - f;
     RansSym e;
     e.fc = f | (c << 16);
@@ -39,7 +40,7 @@ __global__ void __launch_bounds__(256) k_rans_tables(const uint16_t* __restrict_
         e.rcp = (unsigned)((((unsigned long long)1 << (sh + 31)) + f - 1) / f);
     } else e.rcp = 0xffffffffu;
     enc[t * 256 + s] = e;
-    if (lut) {
+    if (lut && whole) {               // any other row would write outside its 2^PB slots: its LUT is left alone
         uint8_t* l = lut + ((size_t)t << pb);
         for (unsigned i = c; i < incl; ++i) l[i] = (uint8_t)s;
     }
@@ -103,7 +104,7 @@ __global__ void __launch_bounds__(64) k_rans_encode(const uint8_t* __restrict__ 
     }
     rans_flush(x, w);
     w.flush(slot);
-    out_len[s] = (unsigned)(slot + cap - w.ptr());
+    out_len[s] = w.bad ? LEN_NOFREQ : (unsigned)(slot + cap - w.ptr());
 }
 
 // ---- scan + gather ---------------------------------------------------------------------------------------
@@ -119,7 +120,8 @@ __global__ void __launch_bounds__(1024) k_scan_lens(const unsigned* __restrict__
     for (int base = 0; base < nseg; base += 1024) {
         const int i = base + threadIdx.x;
         unsigned l = i < nseg ? len[i] : 0;
-        if (l == 0xffffffffu) { atomicOr(status, SG_ST_OVERFLOW); l = 0; }
+        if (l == LEN_OVERFLOW) { atomicOr(status, SG_ST_OVERFLOW); l = 0; }
+        else if (l == LEN_NOFREQ) { atomicOr(status, SG_ST_CORRUPT); l = 0; }
         unsigned long long v = l;
         for (int o = 1; o < 32; o <<= 1) { const unsigned long long n = __shfl_up_sync(0xffffffffu, v, o); if ((threadIdx.x & 31) >= o) v += n; }
         if ((threadIdx.x & 31) == 31) wsum[threadIdx.x >> 5] = v;
@@ -140,7 +142,7 @@ __global__ void __launch_bounds__(256) k_gather(const uint8_t* __restrict__ src,
     const int s = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (s >= nseg) return;
     const unsigned l = len[s];
-    if (l == 0xffffffffu || off[s] + l > dst_cap) return;
+    if (l >= LEN_NOFREQ || off[s] + l > dst_cap) return;
     const uint8_t* a = src + (size_t)(s + 1) * cap - l;
     uint8_t* d = dst + off[s];
     for (unsigned i = lane; i < l; i += 32) d[i] = a[i];

@@ -17,6 +17,8 @@
 namespace sg {
 
 constexpr unsigned RANS_L = 1u << 23;
+constexpr unsigned LEN_OVERFLOW = 0xffffffffu;     // out_len of a segment whose slot was too small (retry with more)
+constexpr unsigned LEN_NOFREQ   = 0xfffffffeu;     // out_len of a segment that met a symbol its table gives no frequency
 
 // encoder entry for one (table, symbol): rcp = ceil(2^(31+s) / freq) with s = ceil(log2 freq); fc = freq | cum << 16
 struct __align__(8) RansSym { unsigned rcp, fc; };
@@ -37,7 +39,8 @@ struct ByteWriterDown {
     uint8_t* base;                 // address of the current window
     unsigned long long lo, hi;     // window contents (byte k of the window at bits 8k of lo / hi)
     int pos;                       // bytes still free in the window: next byte goes to index pos - 1
-    SG_DEVINL void init(uint8_t* end) { base = end - 16; lo = hi = 0; pos = 16; }
+    unsigned bad;                  // set when a symbol with frequency 0 was coded (tables not made from these symbols)
+    SG_DEVINL void init(uint8_t* end) { base = end - 16; lo = hi = 0; pos = 16; bad = 0; }
     SG_DEVINL void put(unsigned b) {
         --pos;
         if (pos >= 8) hi |= (unsigned long long)b << (8 * (pos - 8));
@@ -93,7 +96,10 @@ template <int PB, class W>
 SG_DEVINL void rans_put(unsigned& x, W& w, const RansSym e) {
     const unsigned f = e.fc & 0xffffu, c = e.fc >> 16;
     const unsigned xm = ((RANS_L >> PB) << 8) * f;
-    while (x >= xm) { w.put(x & 0xff); x >>= 8; }
+    // x < 2^31 and xm >= 2^(31 - PB) for f >= 1: at most two bytes leave per symbol (PB <= 15).  Written as two steps,
+    // not a loop: a zero frequency (xm = 0) would never end it; such a symbol marks the segment instead.
+    w.bad |= (unsigned)(f == 0);
+    if (x >= xm) { w.put(x & 0xff); x >>= 8; if (x >= xm) { w.put(x & 0xff); x >>= 8; } }
     const unsigned q = rans_div(x, f, e.rcp);
     x = (q << PB) + (x - q * f) + c;
 }

@@ -22,8 +22,10 @@ __device__ __forceinline__ unsigned nz_bytes(unsigned v) {
 }
 
 template <bool HAVE_C, bool WRITE>
-__global__ void __launch_bounds__(256) k_residual(const uint8_t* __restrict__ a, const uint8_t* __restrict__ b,
-                                                  const uint8_t* __restrict__ c, uint8_t* __restrict__ out, size_t nbytes,
+// `out` may be the same buffer as `a` (r ^= p in place): neither is declared restrict, and a kernel that writes reads
+// `a` with ordinary loads, not through the read-only path
+__global__ void __launch_bounds__(256) k_residual(const uint8_t* a, const uint8_t* __restrict__ b,
+                                                  const uint8_t* __restrict__ c, uint8_t* out, size_t nbytes,
                                                   unsigned long long* __restrict__ counts, bool vec) {
     unsigned long long local = 0;
     const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
@@ -35,7 +37,7 @@ __global__ void __launch_bounds__(256) k_residual(const uint8_t* __restrict__ a,
         const uint4* cv = reinterpret_cast<const uint4*>(c);
         uint4* ov = reinterpret_cast<uint4*>(out);
         for (size_t i = tid; i < nv; i += nth) {
-            uint4 x = __ldg(av + i);
+            uint4 x = WRITE ? av[i] : __ldg(av + i);
             if (b) { const uint4 y = __ldg(bv + i); x.x ^= y.x; x.y ^= y.y; x.z ^= y.z; x.w ^= y.w; }
             if (HAVE_C) { const uint4 z = __ldg(cv + i); x.x ^= z.x; x.y ^= z.y; x.z ^= z.z; x.w ^= z.w; }
             if (WRITE) ov[i] = x;

@@ -54,12 +54,41 @@ def store_tables(freq, used):
     return zstd.compress(struct.pack("<I", len(u)) + du.tobytes() + np.ascontiguousarray(freq, np.uint16).tobytes(), 19)
 
 
-def load_tables(buf):
+def load_tables(buf, pb=PB, ntab=None):
+    """the `t` part of a batch -> (freq uint16 [n][256], used table ids).  A part whose rows do not each sum to 2^pb, or
+    whose ids are not increasing and below `ntab`, is rejected here, before any kernel sees it"""
     raw = zstd.decompress(bytes(buf), max_output_size=1 << 30)
+    if len(raw) < 4:
+        raise ValueError("coder tables: truncated part")
     (n,) = struct.unpack_from("<I", raw)
-    used = np.cumsum(np.frombuffer(raw, np.uint32, n, 4).astype(np.int64))
+    if len(raw) != 4 + 4 * n + 512 * n:
+        raise ValueError("coder tables: the part's length does not match its table count")
+    du = np.frombuffer(raw, np.uint32, n, 4).astype(np.int64)
+    used = np.cumsum(du)
     freq = np.frombuffer(raw, np.uint16, n * 256, 4 + 4 * n).reshape(n, 256)
+    if n and ((du[1:] <= 0).any() or (ntab is not None and used[-1] >= ntab)):
+        raise ValueError("coder tables: table ids out of order or out of range")
+    if n and (freq.sum(1, dtype=np.int64) != (1 << pb)).any():
+        raise ValueError("coder tables: a row of frequencies does not sum to 2^PB")
     return freq, used
+
+
+LEN_OVERFLOW, LEN_NOFREQ = 0xffffffff, 0xfffffffe       # sentinels in a coder launch's segment lengths
+
+
+def check_lens(lens):
+    """raise if a segment met a symbol to which its table gives no frequency (tables made from other symbols)"""
+    if (np.asarray(lens) == LEN_NOFREQ).any():
+        raise ValueError("rANS encoder: a coded symbol has frequency 0 in its table")
+
+
+def check_tables(freq, used, counts):
+    """every (table, symbol) that occurs in `counts` [ntab][256] must have a frequency >= 1 in (freq, used)"""
+    c = np.asarray(counts).reshape(-1, 256)
+    full = np.zeros(c.shape, np.uint16)
+    full[np.asarray(used)] = freq
+    if ((c > 0) & (full == 0)).any():
+        raise ValueError("rANS encoder: the tables give no frequency to a symbol that occurs")
 
 
 def seg_blocks(T):
@@ -198,20 +227,21 @@ class QRCodec:
                 with _lib.timed("qr_encode"):
                     _lib.check(self.lib.sg_qr_encode(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(enc),
                                                      _p(slots), cap, _p(lens), mv), "sg_qr_encode")
-            off = torch.empty(nseg + 1, dtype=torch.int64, device=self.device)
-            with _lib.timed("scan_gather"):
-                _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, None, 0, _p(off)), "sg_scan_gather")
-            if not (self._status() & 2):
+            # the segments' lengths are read on the host (they are part of the batch anyway): sentinels are seen there,
+            # not through the device status word, which other threads' calls share
+            lens_h = lens[:nseg].cpu().numpy().view(np.uint32)
+            check_lens(lens_h)
+            if not (lens_h == LEN_OVERFLOW).any():
                 break
             cap *= 2
         else:
             raise RuntimeError("QR segment overflow")
-        total = int(off[-1].item())
+        total = int(lens_h.sum(dtype=np.uint64))
+        off = torch.empty(nseg + 1, dtype=torch.int64, device=self.device)
         dst = torch.empty(total + 32, dtype=torch.uint8, device=self.device)
         with _lib.timed("scan_gather"):
             _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, _p(dst), total, _p(off)), "sg_scan_gather")
         stream = dst[:total].cpu().numpy().tobytes()
-        lens_h = lens[:nseg].cpu().numpy().view(np.uint32)
         out = {"t": store_tables(freq, used), "l": zstd.compress(lens_h.astype(np.uint32).tobytes(), 19), "s": stream}
         if mv != 1:
             out["v"] = bytes([mv])
@@ -232,7 +262,7 @@ class QRCodec:
                                              [it[4] if len(it) > 4 else -1 for it in items])
         P = _gather([it[0] for it in items], self.device)
         seed = _dev_u8(seed_dev, self.device)
-        freq, used = load_tables(ch["t"])
+        freq, used = load_tables(ch["t"], PB, NTAB2)
         enc, lut = self._tables(freq, used, lut=True)
         lens = np.frombuffer(zstd.decompress(bytes(ch["l"]), max_output_size=1 << 30), np.uint32).astype(np.uint64)
         offs = np.zeros(nseg + 1, np.uint64); offs[1:] = np.cumsum(lens)

@@ -87,7 +87,10 @@ class RansCodec:
             with _lib.timed("scan_gather"):
                 _lib.check(self.lib.sg_scan_gather(self.device.index, self._stream(), _p(slots), cap, _p(lens), nseg, None, 0, _p(off)),
                            "sg_scan_gather")
-            if self.status() & 2:                 # a slot overflowed: retry with twice the room (seedpack/qr.py:1043-1053)
+            bits = self.status()
+            if bits & 4:
+                raise ValueError("rANS encoder: a coded symbol has frequency 0 in its table")
+            if bits & 2:                          # a slot overflowed: retry with twice the room (seedpack/qr.py:1043-1053)
                 cap *= 2
                 continue
             total = int(off[-1].item())

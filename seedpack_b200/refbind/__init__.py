@@ -42,8 +42,12 @@ def available():
     return find_reference() is not None
 
 
-def install(reference=None, staged_qr=True):
-    """bind the reference (see the module docstring) -> its `seedpack` package.  Idempotent."""
+def install(reference=None, staged_qr=None):
+    """bind the reference (see the module docstring) -> its `seedpack` package.  Idempotent.
+    staged_qr False (or SEEDGROW_QR_SINGLE_PASS=1): qr.encode / qr.decode stay the reference's functions and their
+    qr_hist / qr_enc / qr_dec launches go through the one-to-one kernel bindings (same bytes, the model run twice)"""
+    if staged_qr is None:
+        staged_qr = os.environ.get("SEEDGROW_QR_SINGLE_PASS") != "1"
     if "pkg" in _state:
         return _state["pkg"]
     import torch

@@ -62,6 +62,9 @@ def _tables(remap, freq, pb, lut):
         _TABS.move_to_end(key)
         return hit[0], hit[1]
     ntab = remap.size
+    sums = freq._h().reshape(-1, 256).sum(1, dtype=np.int64)
+    if freq.size and (sums != (1 << pb)).any():
+        raise ValueError("coder tables: a row of frequencies does not sum to 2^PB (damaged table part)")
     r = remap.dev_in().view(torch.int32).to(torch.int64)
     f = freq.dev_in().view(torch.int16).view(-1, 256)
     full = torch.zeros((ntab, 256), dtype=torch.int16, device=f.device)
@@ -132,8 +135,11 @@ def _gather(args):
     out, cap, out_len, offs, nseg, dst = args
     if _i(nseg) == 0:
         return
+    if (out_len._h() == 0xfffffffe).any():       # (the caller has read the lengths already: a host copy exists)
+        raise ValueError("rANS encoder: a coded symbol has frequency 0 in its table")
     _lib.check(_lib.lib().sg_scan_gather(_dev(), _st(), _p(out.dev_in()), _i(cap), _p(out_len.dev_in()), _i(nseg), _p(dst.dev_out()),
                                          dst.size, _p(offs.dev_inout())), "sg_scan_gather")
+
 
 
 # ---- QR (single-pass kernels) -------------------------------------------------------------------------------------

@@ -12,7 +12,7 @@ def test_normalize_gpu_matches_reference_tables():
     from seedpack_b200.qr import load_tables
     G = np.load(os.path.join(HERE, "golden", "r2_golden.npz"))
     freq, used = normalize_gpu(G["counts"], 1 << 15)
-    wf, wu = load_tables(G["part_tables"].tobytes())
+    wf, wu = load_tables(G["part_tables"].tobytes(), 15)
     assert np.array_equal(used, wu) and np.array_equal(freq, wf)
     assert (freq.astype(np.int64).sum(1) == 1 << 15).all()
 
@@ -21,7 +21,7 @@ def test_store_tables_roundtrip_and_bytes():
     from seedpack_b200.qr import load_tables, store_tables
     G = np.load(os.path.join(HERE, "golden", "r2_golden.npz"))
     buf = G["part_tables"].tobytes()
-    freq, used = load_tables(buf)
+    freq, used = load_tables(buf, 15)
     assert store_tables(freq, used) == buf                      # same libzstd, same level: same bytes
 
 
@@ -74,3 +74,35 @@ def test_zstd_streams_and_prefix_dictionary():
         assert r.read() == data
     plain = zstd.ZstdCompressor(level=19).compress(data)
     assert len(whole) < len(plain)           # the dictionary removes the three copies of `head`
+
+
+def test_damaged_table_part_is_rejected_before_any_launch():
+    """a `t` part whose rows do not sum to 2^PB (or whose ids run backwards) never reaches sg_rans_tables"""
+    import struct
+    import pytest
+    from seedpack_b200 import zstd
+    from seedpack_b200.qr import check_lens, check_tables, load_tables, store_tables
+    freq = np.zeros((2, 256), np.uint16)
+    freq[0, 0], freq[0, 7] = 4000, 96
+    freq[1, 3] = 4096
+    good = store_tables(freq, np.array([5, 90]))
+    f, u = load_tables(good, 12, 294)
+    assert np.array_equal(f, freq) and list(u) == [5, 90]
+    bad = freq.copy(); bad[1, 3] = 65535; bad[1, 4] = 65535          # sums far beyond 2^12
+    with pytest.raises(ValueError):
+        load_tables(store_tables(bad, np.array([5, 90])), 12, 294)
+    with pytest.raises(ValueError):
+        load_tables(store_tables(freq, np.array([5, 400])), 12, 294)  # id beyond the table count
+    raw = struct.pack("<I", 2) + struct.pack("<II", 9, 0) + freq.tobytes()
+    with pytest.raises(ValueError):
+        load_tables(zstd.compress(raw, 3), 12, 294)                   # ids not increasing
+    with pytest.raises(ValueError):
+        load_tables(zstd.compress(raw[:-10], 3), 12, 294)             # truncated
+    counts = np.zeros((294, 256), np.int64)
+    counts[5, 0] = 10; counts[90, 3] = 1
+    check_tables(freq, [5, 90], counts)
+    counts[5, 9] = 1                                                  # occurs, but the table gives it nothing
+    with pytest.raises(ValueError):
+        check_tables(freq, [5, 90], counts)
+    with pytest.raises(ValueError):
+        check_lens(np.array([10, 0xfffffffe], np.uint32))
