@@ -1,16 +1,26 @@
 #!/usr/bin/env python
-"""Quantiser sweep benchmark (BASELINE config 2): one BF16 tensor of 4096 x 12288 seeded weights plus a
-12288-entry importance matrix, re-quantised into every ggml type the path handles.
+"""Benchmarks of the re-quantise / residual / rANS path.
 
-A step = one pass over the tensor for every type: the 20 types of the reference's table with the importance matrix,
-the 15 of them whose matrix-free routine is a different code path, and the 5 further quantisers of ggml-quants.c
-(TQ1_0, TQ2_0, MXFP4, NVFP4, Q1_0), which take no matrix: 25 types, 40 launches.  Metric: GB/s of GGUF (quantised) bytes regrown.
+Default workload `pack`: a seeded synthetic model repository of the 0.6B shape (28 layers, hidden 1024, FFN 3072,
+vocabulary 151936; BF16 base + Q8_0, Q4_K_M-shaped and Q6_K files with 0.5 % of the blocks disturbed) is packed into an
+archive and the archive is tested (every file restored in memory and checked) - the reference's own command line,
+repository code and container running on this library's kernels (seedpack_b200.refbind).  A step = one pack + one
+test.  Metric: GB/s of GGUF bytes, pack and unpack.
+
+    e2e      wall clock through the command-line entry points: files read from disk, host <-> device copies, zstd,
+             hashing, container writes included
+    value    the same bytes over the device time of the step's library calls (CUDA events around every C-ABI call):
+             what the kernels alone sustain, with the host pipeline taken out
 
     python bench.py --gpus N --steps K --warmup W          (this repo's CUDA path)
-    python bench.py --impl reference ...                   (the reference's own C quantisers on the host cores)
+    python bench.py --impl reference ...                   (the reference's own --cpu path on the host cores, on a
+                                                            bounded sample: one layer of the same shape)
+    python bench.py --workload quant | rans | qr | r2      (kernel-level workloads: the quantiser sweep over one
+                                                            4096 x 12288 tensor and 25 types; the coders)
 
-Multi-GPU: the path shards by tensor / row-block with no exchange; every rank quantises its own tensor
-of the full size (weak scaling), timed on the device, maximum over ranks.
+Multi-GPU (`pack`): the repository's derived files are dealt out to the ranks (a file's chunks depend only on the
+base and on that file), every rank packs and tests its share, timed by wall clock, maximum over ranks; rank 0's
+line carries a digest over all ranks' per-file chunks, which does not depend on N.
 """
 import argparse
 import json
@@ -309,6 +319,266 @@ def run_ours(args):
 
 
 # ------------------------------------------------------------------------------------------------------
+# `pack`: the reference's command line (pack, test) on a synthetic repository, kernels from this library
+def _bench_tmp():
+    """where the benchmark's repository and archive live: $SEEDGROW_BENCH_TMP, else RAM-backed /dev/shm when it has
+    room (inputs as hot as a page cache would hold them), else the system's temporary directory"""
+    import shutil
+    import tempfile
+    d = os.environ.get("SEEDGROW_BENCH_TMP")
+    if not d:
+        try:
+            d = "/dev/shm" if shutil.disk_usage("/dev/shm").free > (12 << 30) else None
+        except OSError:
+            d = None
+    return tempfile.mkdtemp(prefix="seedgrow-bench-", dir=d)
+
+
+def _repo_text(cfg_name):
+    from seedpack_b200 import synthrepo
+    c = synthrepo.CONFIGS[cfg_name]
+    return (f"synthetic repository '{cfg_name}': {c['layers']} layers, hidden {c['hidden']}, FFN {c['ffn']}, vocabulary {c['vocab']}, "
+            f"BF16 base in {c['shards']} file(s) + {len(synthrepo.file_labels(c))} quant files"
+            f"{' made with an importance matrix' if c['imatrix'] else ', no importance matrix'}, {100 * c['flip']:.1f}% of blocks disturbed")
+
+
+def _file_digest(path):
+    import hashlib
+    h = hashlib.sha256()
+    with open(path, "rb") as f:
+        for b in iter(lambda: f.read(1 << 22), b""):
+            h.update(b)
+    return h.hexdigest()
+
+
+def _quiet(fn, *a):
+    """run a command-line entry point with its progress output discarded; SystemExit with a message is an error"""
+    import contextlib
+    import io
+    buf = io.StringIO()
+    try:
+        with contextlib.redirect_stdout(buf):
+            fn(*a)
+    except SystemExit as e:
+        if e.code not in (None, 0):
+            raise RuntimeError(f"{a}: {e.code}\n{buf.getvalue()[-2000:]}")
+    return buf.getvalue()
+
+
+def _reference_cli():
+    """the reference's command-line module with its own CPU kernels (SEEDPACK_CPU=1), for the CPU legs"""
+    from seedpack_b200 import refbind
+    ref = refbind.find_reference()
+    if ref is None:
+        return None
+    import importlib.util
+    os.environ["SEEDPACK_CPU"] = "1"
+    os.environ.setdefault("SEEDPACK_CACHE", os.path.join(ROOT, "oracle", "_build", "refcache"))
+    os.environ.setdefault("NUMBA_CACHE_DIR", os.path.join(ROOT, "oracle", "_build", "numba"))
+    os.makedirs(os.environ["SEEDPACK_CACHE"], exist_ok=True)
+    if ref not in sys.path:
+        sys.path.insert(0, ref)
+    if importlib.util.find_spec("zstandard") is None:
+        from seedpack_b200 import zstd
+        sys.modules["zstandard"] = zstd
+    from seedpack import cli
+    return cli
+
+
+PACK_METRIC = "pack/unpack GB/s of GGUF bytes"
+SAMPLE = "c1-micro"
+
+
+def run_reference_pack(args):
+    """--impl reference: the reference's own `pack --cpu` and `test --cpu` on the host cores, on a bounded sample of the
+    workload (one layer of the same shape), in this process"""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import shutil
+    threads = os.cpu_count() or 1
+    cfg = {"workload": _repo_text(args.repo)}
+    cli = _reference_cli()
+    if cli is None:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference package is not installed under baseline/_ref (nor $SEEDPACK_REFERENCE)"}))
+        return
+    tmp = _bench_tmp()
+    try:
+        repo = args.repo_dir
+        if not repo:
+            from oracle import ref as oref
+            from seedpack_b200 import synthrepo
+            repo = os.path.join(tmp, "repo")
+            synthrepo.make_repo(repo, SAMPLE, lambda ty, bits, w: oref.quantize(ty, oref.bf16_to_f32(bits), w), seed=1, keep_weights=True)
+        nbytes = sum(os.path.getsize(os.path.join(repo, n)) for n in os.listdir(repo))
+        arc = os.path.join(tmp, "ref.seedpack")
+        tp = tu = 0.0
+        warm = min(args.warmup, 1)
+        for k in range(warm + args.steps):
+            t0 = time.perf_counter()
+            _quiet(cli.main, ["pack", "--cpu", "-q", "-f", "-o", arc, repo])
+            t1 = time.perf_counter()
+            _quiet(cli.main, ["test", "--cpu", arc])
+            t2 = time.perf_counter()
+            if k >= warm:
+                tp += t1 - t0; tu += t2 - t1
+        val = 2 * nbytes * args.steps / (tp + tu) / 1e9
+        sample = (f"'{SAMPLE}' (one layer of the 0.6B shape, vocabulary 4096: {nbytes} bytes, {100 * nbytes / 2.7e9:.1f}% of the full repository), "
+                  f"python -m seedpack pack --cpu + test --cpu, {threads} host threads")
+        line = {"impl": "reference", "metric": PACK_METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+                "warmup": warm, "ms_per_step": (tp + tu) / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+                "pack_gbs": nbytes * args.steps / tp / 1e9, "unpack_gbs": nbytes * args.steps / tu / 1e9,
+                "archive_sha256": _file_digest(arc),
+                "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "reference", "sample": sample},
+                "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+
+
+def run_pack(args):
+    import shutil
+    import torch
+    import torch.distributed as dist
+    from seedpack_b200 import _lib, refbind, synthrepo
+    from seedpack_b200.gpuquant import GPUQuant
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    if not refbind.available():
+        raise RuntimeError("the reference package is not here (baseline/_ref or $SEEDPACK_REFERENCE): pack needs its host code")
+    gq = GPUQuant(local)
+
+    def quantize(ty, bits, w):
+        x = torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).to(dev).reshape(-1)
+        return gq.quantize_tensors(ty, [(x, bits.shape[1])], [w])[0]
+
+    tmp = _bench_tmp()
+    try:
+        os.environ.setdefault("SOURCE_DATE_EPOCH", "1700000000")
+        repo = os.path.join(tmp, "repo")
+        made = synthrepo.make_repo(repo, args.repo, quantize, seed=1 + rank, keep_weights=True)
+        nbytes = made["bytes"]
+        arc = os.path.join(tmp, "a.seedpack")
+        refbind.install()
+        from seedpack import cli
+        from seedpack_b200.refbind import cupy_shim
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        def step():
+            t0 = time.perf_counter()
+            _quiet(cli.main, ["pack", "-q", "-f", "-o", arc, repo])
+            t1 = time.perf_counter()
+            _quiet(cli.main, ["test", arc])
+            return t1 - t0, time.perf_counter() - t1
+
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        sampler = ClockSampler(local)
+        sampler.start()
+        cupy_shim.STATS.update(h2d=0, d2h=0)
+        _lib.COPIES.update(h2d=0, d2h=0)
+        _lib.timing_start(calls=True)
+        tp = tu = 0.0
+        t_all = time.perf_counter()
+        for _ in range(args.steps):
+            a, b = step()
+            tp += a; tu += b
+        barrier()
+        wall = time.perf_counter() - t_all
+        calls = _lib.timing_stop(counts=True)
+        clocks = sampler.summary()
+        dev_ms = sum(v[0] for v in calls.values())
+        h2d = (cupy_shim.STATS["h2d"] + _lib.COPIES["h2d"]) / args.steps
+        d2h = (cupy_shim.STATS["d2h"] + _lib.COPIES["d2h"]) / args.steps
+        # every file back, compared with what went in
+        out = os.path.join(tmp, "out")
+        _quiet(cli.main, ["unpack", "-o", out, arc])
+        names = sorted(os.listdir(repo))
+        exact = sum(1 for n in names if os.path.exists(os.path.join(out, n)) and _file_digest(os.path.join(out, n)) == _file_digest(os.path.join(repo, n)))
+        shutil.rmtree(out, ignore_errors=True)
+        if world > 1:
+            t = torch.tensor([wall, dev_ms, tp, tu], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            wall, dev_ms, tp, tu = (float(x) for x in t)
+            c = torch.tensor([nbytes, exact, len(names), h2d, d2h], device=dev, dtype=torch.float64)
+            dist.all_reduce(c, op=dist.ReduceOp.SUM)
+            nbytes_all, exact, total, h2d, d2h = float(c[0]), int(c[1]), int(c[2]), float(c[3]), float(c[4])
+        else:
+            nbytes_all, total = nbytes, len(names)
+        if rank == 0:
+            peak, peak_kind = peaks()
+            per = {k: {"ms": round(v[0] / args.steps, 3), "calls": v[1] // args.steps} for k, v in sorted(calls.items(), key=lambda kv: -kv[1][0])}
+            dom = next(iter(per)) if per else None
+            line = {"metric": PACK_METRIC, "value": 2 * nbytes_all * args.steps / (dev_ms * 1e-3) / 1e9 if dev_ms else None, "unit": "GB/s",
+                    "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
+                    "wall_ms_per_step": wall / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                    "dtype": "f32", "data": "synthetic",
+                    "config": {"workload": _repo_text(args.repo) + (", one repository per GPU" if world > 1 else ""),
+                               "step": "pack + test of the repository; bytes per step = 2 x repository bytes",
+                               "value_is": "bytes over the summed device time of the step's library calls (CUDA events around each call)",
+                               "l2": "inputs larger than L2 (base 1.2 GB, files 1.5 GB)", "repository_bytes": int(nbytes),
+                               "library_calls": per},
+                    "clocks": clocks,
+                    "e2e": {"value": 2 * nbytes_all * args.steps / wall / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
+                            "d2h_bytes_per_step": int(d2h), "pack_gbs": nbytes_all * args.steps / tp / 1e9,
+                            "unpack_gbs": nbytes_all * args.steps / tu / 1e9},
+                    "bit_exact_files": f"{exact}/{total}", "archive_sha256": _file_digest(arc),
+                    "gpu_launches": int(sum(v[1] for v in calls.values())),
+                    "roofline": pack_roofline(per, dom, args, peak, peak_kind, clocks)}
+            line["cpu_baseline"] = pack_cpu_baseline(args, tmp, quantize, cli) if world == 1 else None
+            print(json.dumps(line))
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+        if world > 1:
+            dist.destroy_process_group()
+
+
+def pack_roofline(per, dom, args, peak, peak_kind, clocks):
+    """the library call with the largest share of the step's device time"""
+    if dom is None:
+        return None
+    return {"bound": "hbm", "kernel": dom, "achieved": None, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": None,
+            "traffic": None, "share_of_device_time": round(per[dom]["ms"] / max(sum(v["ms"] for v in per.values()), 1e-9), 3)}
+
+
+def pack_cpu_baseline(args, tmp, quantize, cli):
+    """the reference's --cpu path on the bounded sample, in a child process (its kernels and this process's cannot share
+    one interpreter); and this library on the same sample, for a like-for-like ratio and an archive comparison"""
+    from seedpack_b200 import synthrepo
+    try:
+        repo = os.path.join(tmp, "sample")
+        made = synthrepo.make_repo(repo, SAMPLE, quantize, seed=1, keep_weights=True)
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "1", "--warmup", "0", "--repo-dir", repo],
+                           capture_output=True, text=True, timeout=1200, env={k: v for k, v in os.environ.items() if k != "SEEDPACK_CPU"})
+        ref_line = json.loads(r.stdout.strip().splitlines()[-1])
+        if "unavailable" in ref_line:
+            return {"value": None, "unit": "GB/s", "cores": 0, "kind": "reference", "sample": ref_line["unavailable"]}
+        arc = os.path.join(tmp, "sample.seedpack")
+        _quiet(cli.main, ["pack", "-q", "-f", "-o", arc, repo])
+        t0 = time.perf_counter()
+        _quiet(cli.main, ["pack", "-q", "-f", "-o", arc, repo])
+        _quiet(cli.main, ["test", arc])
+        ours = 2 * made["bytes"] / (time.perf_counter() - t0) / 1e9
+        out = dict(ref_line["cpu_baseline"])
+        out.update(pack_gbs=ref_line["pack_gbs"], unpack_gbs=ref_line["unpack_gbs"], this_library_on_the_sample_gbs=ours,
+                   sample_archive_identical=_file_digest(arc) == ref_line["archive_sha256"])
+        return out
+    except Exception as e:                                   # the baseline is reported, never required
+        return {"value": None, "unit": "GB/s", "cores": 0, "kind": "reference", "sample": f"failed: {e}"}
+
+
+
+# ------------------------------------------------------------------------------------------------------
 # Coder workloads (not the default): the rANS symbol coder on BASELINE config 3's stream, the QR residual coder and the
 # R2 BF16 base codec on the config-2 tensor.  Kernel times are CUDA-event times of the library calls
 # (seedpack_b200._lib.timed); `e2e` is wall time through the Python classes with host buffers on both sides.
@@ -541,8 +811,10 @@ def main():
     ap.add_argument("--ref-rows", type=int, default=0, help="rows of the tensor the CPU baseline quantises per step")
     ap.add_argument("--rows", type=int, default=NROWS, help="rows of the tensor (profiling captures use fewer)")
     ap.add_argument("--only", default="", help="comma-separated launch names to keep, e.g. q4_K+imx,iq2_xs+imx")
-    ap.add_argument("--workload", default="quant", choices=["quant", "rans", "qr", "r2"],
-                    help="quant: the quantiser sweep (the headline); rans / qr / r2: the coders, one GPU")
+    ap.add_argument("--workload", default="pack", choices=["pack", "quant", "rans", "qr", "r2"],
+                    help="pack: pack + test of a synthetic repository (the headline); quant: the quantiser sweep; rans / qr / r2: the coders, one GPU")
+    ap.add_argument("--repo", default="c1", help="pack: synthetic repository (a key of seedpack_b200.synthrepo.CONFIGS)")
+    ap.add_argument("--repo-dir", default="", help="--impl reference: an existing repository directory to pack instead of making the sample")
     ap.add_argument("--symbols", type=int, default=1 << 30, help="rans: symbols in the stream")
     ap.add_argument("--tensors", type=int, default=4, help="qr / r2: tensors of the benchmark shape in the batch / file")
     ap.add_argument("--qr-types", default="8,12,14,17,18", help="qr: ggml type ids, one coding batch each")
@@ -552,7 +824,9 @@ def main():
         keep = set(args.only.split(","))
         CASES = [c for c in CASES if case_name(*c) in keep]
         assert CASES, "no such launch"
-    if args.impl == "reference":
+    if args.workload == "pack":
+        (run_reference_pack if args.impl == "reference" else run_pack)(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.workload != "quant":
         if int(os.environ.get("RANK", "0")) == 0:

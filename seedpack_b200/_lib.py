@@ -90,16 +90,28 @@ def check(status, where):
         raise SgError(status, where)
 
 
-# ---- optional per-kernel device timing (benchmarks) ------------------------------------------------------------
+# ---- optional per-call device timing and copy accounting (benchmarks) ----------------------------------------------
 import contextlib
+import threading
 
 _TIMES = None
+_TLOCK = threading.Lock()
+COPIES = {"h2d": 0, "d2h": 0}          # bytes the host-side classes moved between host and device
+
+
+def count_h2d(n):
+    COPIES["h2d"] += int(n)
+
+
+def count_d2h(n):
+    COPIES["d2h"] += int(n)
 
 
 @contextlib.contextmanager
 def timed(name):
-    """with timing_start() active: CUDA-event time of the enclosed launches on torch's current stream, summed per name"""
-    if _TIMES is None:
+    """with timing_start() active: CUDA-event time of the enclosed launches on torch's current stream, summed per name
+    (not while timing_start(calls=True) times every library call itself)"""
+    if _TIMES is None or "__calls__" in _TIMES:
         yield
         return
     import torch
@@ -110,16 +122,51 @@ def timed(name):
     _TIMES.setdefault(name, []).append((e0, e1))
 
 
-def timing_start():
+def _label(name, args):
+    if name == "sg_quantize_tensors":
+        return f"{name}[{args[2]}{'' if args[7] is None else '+imx'}]"
+    if name in ("sg_qr_hist", "sg_qr_encode", "sg_qr_decode", "sg_qr_stage", "sg_qr_stage_hist", "sg_qr_stage_encode", "sg_dequantize"):
+        return f"{name}[{args[2]}]"
+    return name
+
+
+def timing_start(calls=False):
+    """start collecting device times.  calls=True: every library call that takes a stream is timed by its entry-point
+    name (quantisers and QR calls by type as well) with a pair of CUDA events recorded around it on torch's current
+    stream; the calls of different host threads are serialised while this is on, so that no pair spans another
+    thread's launches.  calls=False: only the regions marked with timed() in the host classes"""
     global _TIMES
     _TIMES = {}
+    if not calls:
+        return
+    import torch
+    L = lib()
+    _TIMES["__calls__"] = {}
+    for name, (res, args) in SIGNATURES.items():
+        if len(args) < 2 or args[0] is not _I or args[1] is not _P or name in ("sg_status_fetch", "sg_tables_install"):
+            continue
+        raw = getattr(L, name)
+
+        def wrapped(*a, _raw=raw, _name=name):
+            with _TLOCK:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                rc = _raw(*a)
+                e1.record()
+                _TIMES.setdefault(_label(_name, a), []).append((e0, e1))
+            return rc
+        _TIMES["__calls__"][name] = raw
+        setattr(L, name, wrapped)
 
 
-def timing_stop():
-    """-> {name: milliseconds} of everything timed since timing_start()"""
+def timing_stop(counts=False):
+    """-> {name: milliseconds} of everything timed since timing_start() (with counts: {name: (ms, calls)})"""
     global _TIMES
     import torch
     torch.cuda.synchronize()
-    out = {k: sum(a.elapsed_time(b) for a, b in v) for k, v in (_TIMES or {}).items()}
+    t = _TIMES or {}
+    for name, raw in (t.pop("__calls__", None) or {}).items():
+        setattr(lib(), name, raw)
+    out = {k: (sum(a.elapsed_time(b) for a, b in v), len(v)) for k, v in t.items()}
     _TIMES = None
-    return out
+    return out if counts else {k: v[0] for k, v in out.items()}

@@ -121,6 +121,35 @@ def batches(T, sizes):
     return out
 
 
+# ---- records: checked on the host before anything is launched -----------------------------------------------------------
+SEED_ITEM = {30: 2, 1: 2, 0: 4, 99: 8}          # bytes per weight of the seed types the kernels read: BF16, F16, F32, (x, h) pairs
+COLRMS = 98                                      # no seed: one float32 per column (seedpack/qr.py:899)
+
+
+def check_records(T, nblocks, seed_offs, seed_types, cols, imx_offs, seed_bytes, imx_floats):
+    """every offset a kernel will add to the seed or importance buffer stays inside it, every seed type is one the
+    kernels know.  Raises ValueError; nothing has been launched at that point.  (The reference trusts its caller:
+    seedpack/qr.py:1014-1019.)"""
+    for i, nb in enumerate(nblocks):
+        st, off, c, io = int(seed_types[i]), int(seed_offs[i]), int(cols[i]), int(imx_offs[i])
+        nw = nb * QK[T]
+        if c < 0 or (c and (c % QK[T] or nw % c)):
+            raise ValueError(f"tensor {i}: {c} weights per row do not divide its {nw} weights into rows of whole blocks")
+        if st in SEED_ITEM:
+            item = SEED_ITEM[st]
+            if off < 0 or off % min(item, 4) or off + nw * item > seed_bytes:
+                raise ValueError(f"tensor {i}: seed bytes {off}..{off + nw * item} (type {st}) are outside the seed buffer of {seed_bytes}")
+        elif st == COLRMS:
+            if c <= 0 or off < 0 or off % 4 or off + 4 * c > seed_bytes:
+                raise ValueError(f"tensor {i}: column statistics {off}..{off + 4 * c} are outside the seed buffer of {seed_bytes}")
+        else:
+            raise ValueError(f"tensor {i}: seed type {st} is not one the coder reads (BF16 30, F16 1, F32 0, 98, 99)")
+        if io >= 0 and (c <= 0 or io + c > imx_floats):
+            raise ValueError(f"tensor {i}: importance values {io}..{io + c} are outside the {imx_floats} given")
+        if io < -1:
+            raise ValueError(f"tensor {i}: importance offset {io}")
+
+
 # ---- device plumbing ---------------------------------------------------------------------------------------------------
 def _p(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
@@ -129,6 +158,7 @@ def _p(t):
 def _dev_u8(a, device):
     if isinstance(a, torch.Tensor):
         return a.to(device).view(torch.uint8).reshape(-1)
+    _lib.count_h2d(len(a) if not isinstance(a, np.ndarray) else a.nbytes)
     return torch.from_numpy(np.frombuffer(memoryview(a), np.uint8).copy() if not isinstance(a, np.ndarray) else np.ascontiguousarray(a).view(np.uint8).reshape(-1)).to(device)
 
 
@@ -163,7 +193,8 @@ class QRCodec:
             return imx_dev.to(self.device, torch.float32).contiguous().reshape(-1)
         return torch.from_numpy(np.ascontiguousarray(imx_dev, np.float32).reshape(-1)).to(self.device)
 
-    def _records(self, T, nbs, seed_offs, seed_types, cols, imx_offs):
+    def _records(self, T, nbs, seed_offs, seed_types, cols, imx_offs, seed_bytes, imx_floats):
+        check_records(T, nbs, seed_offs, seed_types, cols, imx_offs, seed_bytes, imx_floats)
         tm, sg, nb = _layout(T, nbs)
         tm["seed_off"], tm["seed_type"], tm["cols"], tm["imx_off"] = seed_offs, seed_types, cols, imx_offs
         tm_d = torch.from_numpy(tm.view(np.uint8).copy()).to(self.device)
@@ -188,12 +219,16 @@ class QRCodec:
         imx = self._imx(T, imx_dev)
         bs, d, st = BS[T], self.device.index, self._stream()
         nbs = [len(it[0]) // bs for it in items]
+        for k, it in enumerate(items):
+            if len(it[0]) % bs or len(it[0]) != len(it[1]):
+                raise ValueError(f"tensor {k}: file and prediction must be the same whole number of {bs}-byte blocks")
+        seed = _dev_u8(seed_dev, self.device)
         tm_d, sg_d, nseg, nb = self._records(T, nbs, [it[2] for it in items], [it[3] for it in items],
                                              [it[4] if len(it) > 4 else 0 for it in items],
-                                             [it[5] if len(it) > 5 else -1 for it in items])
+                                             [it[5] if len(it) > 5 else -1 for it in items], seed.numel(),
+                                             0 if imx is None else imx.numel())
         F = _gather([it[0] for it in items], self.device)
         P = _gather([it[1] for it in items], self.device)
-        seed = _dev_u8(seed_dev, self.device)
         ne = torch.empty(max(nb, 1), dtype=torch.uint8, device=self.device)
         ndiff = torch.zeros(1, dtype=torch.int64, device=self.device)
         with _lib.timed("residual_blocks"):
@@ -242,6 +277,7 @@ class QRCodec:
         with _lib.timed("scan_gather"):
             _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, _p(dst), total, _p(off)), "sg_scan_gather")
         stream = dst[:total].cpu().numpy().tobytes()
+        _lib.count_d2h(total + 4 * nseg + NTAB2 * 1024)
         out = {"t": store_tables(freq, used), "l": zstd.compress(lens_h.astype(np.uint32).tobytes(), 19), "s": stream}
         if mv != 1:
             out["v"] = bytes([mv])
@@ -257,11 +293,12 @@ class QRCodec:
         mv = ch["v"][0] if "v" in ch else 1
         bs, d, st = BS[T], self.device.index, self._stream()
         nbs = [len(it[0]) // bs for it in items]
+        seed = _dev_u8(seed_dev, self.device)
         tm_d, sg_d, nseg, nb = self._records(T, nbs, [it[1] for it in items], [it[2] for it in items],
                                              [it[3] if len(it) > 3 else 0 for it in items],
-                                             [it[4] if len(it) > 4 else -1 for it in items])
+                                             [it[4] if len(it) > 4 else -1 for it in items], seed.numel(),
+                                             0 if imx is None else imx.numel())
         P = _gather([it[0] for it in items], self.device)
-        seed = _dev_u8(seed_dev, self.device)
         freq, used = load_tables(ch["t"], PB, NTAB2)
         enc, lut = self._tables(freq, used, lut=True)
         lens = np.frombuffer(zstd.decompress(bytes(ch["l"]), max_output_size=1 << 30), np.uint32).astype(np.uint64)
@@ -271,6 +308,7 @@ class QRCodec:
             raise ValueError("QR batch: segment lengths do not add up to the stream length")
         sd = torch.zeros((len(s) + 31) // 16 * 16, dtype=torch.uint8, device=self.device)
         sd[:len(s)] = torch.from_numpy(s.copy()).to(self.device)
+        _lib.count_h2d(len(s) + 8 * nseg)
         F = torch.empty(nb * bs, dtype=torch.uint8, device=self.device)
         off_d = torch.from_numpy(offs.view(np.int64)).to(self.device)
         with _lib.timed("qr_decode"):

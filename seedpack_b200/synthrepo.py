@@ -43,6 +43,10 @@ CONFIGS = {
     "c1-mini": dict(layers=4, hidden=1024, ffn=3072, q_heads=16, kv_heads=8, head_dim=128, vocab=4096, tied=True,
                     imatrix=False, shards=1, flip=0.005, alter=0.0,
                     files={"Q8_0": "q8_0", "Q4_K_M": "q4_k_m", "Q6_K": "q6_k"}),
+    # one layer of the 0.6B shape and a 4096-token vocabulary: the bounded sample the CPU baseline is timed on
+    "c1-micro": dict(layers=1, hidden=1024, ffn=3072, q_heads=16, kv_heads=8, head_dim=128, vocab=4096, tied=True,
+                     imatrix=False, shards=1, flip=0.005, alter=0.0,
+                     files={"Q8_0": "q8_0", "Q4_K_M": "q4_k_m", "Q6_K": "q6_k"}),
     # a repository of a few megabytes for tests of the host logic
     "c1-nano": dict(layers=2, hidden=256, ffn=768, q_heads=2, kv_heads=1, head_dim=128, vocab=512, tied=True,
                     imatrix=False, shards=1, flip=0.005, alter=0.0,
@@ -120,6 +124,9 @@ def weights(seed, name, shape):
     return bf16_round(x).reshape(rows, cols)
 
 
+_draw_weights = weights
+
+
 def importance(seed, name, cols):
     return np.exp(1.5 * _rng(seed, "imx:" + name).standard_normal(cols)).astype(np.float32)
 
@@ -182,23 +189,29 @@ def _flip(seed, key, q, bs, share):
     q[blocks * bs + r.integers(0, bs, k)] ^= r.integers(1, 256, k).astype(np.uint8)
 
 
-def make_repo(root, config, quantize, seed=0, name="synth", only=None):
+def make_repo(root, config, quantize, seed=0, name="synth", only=None, keep_weights=False):
     """write the repository `config` (a key of CONFIGS or a dict of the same form) under `root` ->
     {"base": [paths], "files": {label: path}, "extras": [paths], "bytes": total}.
     quantize(ggml type, BF16 bits as a (rows, cols) uint16 array, importance vector or None) -> uint8 array.
-    only: labels of the quant files to make (default: all of the configuration)"""
+    only: labels of the quant files to make (default: all of the configuration); keep_weights: hold every base tensor
+    in memory while the files are written (each is drawn once instead of once per file)"""
     cfg = CONFIGS[config] if isinstance(config, str) else config
     os.makedirs(root, exist_ok=True)
     shapes = tensor_shapes(cfg)
     L = cfg["layers"]
+    held = {}
+
+    def weights(seed, n, s, _draw=_draw_weights):
+        if not keep_weights:
+            return _draw(seed, n, s)
+        if n not in held:
+            held[n] = _draw(seed, n, s)
+        return held[n]
+
     out = {"base": [], "files": {}, "extras": []}
 
     def layer_of(n):
         return int(n.split(".")[1]) if n.startswith("blk.") else 0
-
-    def base_tensor(n, shp):
-        w = weights(seed, n, shp)
-        return (n, shp, F32 if len(shp) == 1 else BF16, w.nbytes, lambda w=w: w)
 
     # base model: one file, or shards named <name>-0000k-of-0000N.gguf holding consecutive tensors
     ns = cfg["shards"]

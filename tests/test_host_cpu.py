@@ -106,3 +106,28 @@ def test_damaged_table_part_is_rejected_before_any_launch():
         check_tables(freq, [5, 90], counts)
     with pytest.raises(ValueError):
         check_lens(np.array([10, 0xfffffffe], np.uint32))
+
+
+def test_batch_records_are_bounds_checked_on_the_host():
+    """offsets into the seed and importance buffers, and the seed type, are checked before any launch"""
+    import pytest
+    from seedpack_b200.qr import check_records
+    T = 12                                            # Q4_K: 256 weights per block
+    ok = dict(T=T, nblocks=[8, 4], seed_offs=[0, 4096], seed_types=[30, 30], cols=[1024, 1024], imx_offs=[-1, -1],
+              seed_bytes=4096 + 4 * 256 * 2, imx_floats=0)
+    check_records(**ok)
+    for change in (dict(seed_bytes=4096 + 4 * 256 * 2 - 2),            # the last tensor's seed runs past the buffer
+                   dict(seed_offs=[0, -2]), dict(seed_offs=[1, 4096]),  # negative / odd BF16 offset
+                   dict(seed_types=[30, 12]),                           # a quantised seed: not read by these kernels
+                   dict(seed_types=[30, 77]),
+                   dict(cols=[1000, 1024]),                             # not whole blocks per row
+                   dict(cols=[1024, 768]),                              # 4 blocks are not whole rows of 768
+                   dict(imx_offs=[0, -1], imx_floats=1000),             # importance vector shorter than a row
+                   dict(imx_offs=[-3, -1])):
+        with pytest.raises(ValueError):
+            check_records(**{**ok, **change})
+    check_records(T, [8], [0], [98], [1024], [-1], 4096, 0)          # no seed: one float per column
+    with pytest.raises(ValueError):
+        check_records(T, [8], [0], [98], [0], [-1], 4096, 0)         # ... needs the row length
+    check_records(17, [8], [0], [0], [2048], [0], 8 * 256 * 4, 2048)  # F32 seed, lattice type with importance values
+    check_records(T, [8], [0], [99], [0], [-1], 8 * 256 * 8, 0)       # explicit (x, h) pairs

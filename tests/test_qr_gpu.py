@@ -136,3 +136,46 @@ def test_grid_single_pass_and_staged_encoders_agree(T):
     enc, _ = _grid_items(T)
     seed = GG["seed_bits"].view(np.uint8)
     assert QRCodec(staged=False).encode(T, enc, seed, GG["imx"], mv=2) == QRCodec(staged=True).encode(T, enc, seed, GG["imx"], mv=2)
+
+
+# ---- seed types other than BF16, wide rows (tests/golden/qr_seed_golden.npz, made by the reference) -----------------------
+GS = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "qr_seed_golden.npz"))
+S_SHAPES = [tuple(int(v) for v in s) for s in GS["shapes"]]
+
+
+def _seed_items(T, kind):
+    from seedpack_b200.qr import BS, GRID_TYPES, QK
+    F, P, bs = GS[f"F_{T}"], (GS["P98"] if kind == 98 else GS[f"P_{T}"]), BS[T]
+    offs = GS["offs98"] if kind == 98 else GS[f"offs_{T}_{kind}"]
+    enc, dec, o, io = [], [], 0, 0
+    for k, (nr, npr) in enumerate(S_SHAPES):
+        n = nr * npr // QK[T] * bs
+        tail = (int(offs[k]), kind, npr, io if T in GRID_TYPES else -1)
+        enc.append((F[o:o + n], P[o:o + n]) + tail)
+        dec.append((P[o:o + n],) + tail)
+        o += n; io += npr
+    return enc, dec
+
+
+@pytest.mark.parametrize("mv", [1, 2])
+@pytest.mark.parametrize("T,kind", [(12, 1), (12, 0), (12, 99), (12, 98), (17, 1), (17, 0), (17, 99)])
+def test_other_seed_types_match_the_reference(T, kind, mv):
+    """F16, F32, explicit (x, h) and column-RMS seeds; an 8192-column tensor reaches every row-position context"""
+    from seedpack_b200.qr import GRID_TYPES, QRCodec
+    c = QRCodec()
+    enc, dec = _seed_items(T, kind)
+    seed = GS["seed98"] if kind == 98 else GS[f"seed_{T}_{kind}"]
+    imx = GS["imx"] if T in GRID_TYPES else None
+    want = (GS[f"B98_{mv}"] if kind == 98 else GS[f"B_{T}_{kind}_{mv}"]).tobytes()
+    for staged in (True, False):
+        c.staged = staged
+        assert c.encode(T, enc, seed, imx, mv=mv) == want, f"staged={staged}"
+    assert np.array_equal(c.decode(T, want, dec, seed, imx).cpu().numpy(), GS[f"F_{T}"])
+
+
+def test_unknown_seed_type_is_refused():
+    from seedpack_b200.qr import QRCodec
+    enc, _ = _seed_items(12, 1)
+    bad = [it[:3] + (12,) + it[4:] for it in enc]            # a quantised seed: these kernels do not read it
+    with pytest.raises(ValueError):
+        QRCodec().encode(12, bad, GS["seed_12_1"], None)
