@@ -260,6 +260,11 @@ SG_API int sg_dm_rows(int device, void *stream, const float *x, long long nr, lo
 SG_API int sg_dm_cols(int device, void *stream, const float *x, long long nr, long long nc, int square,
                       const unsigned char *mask, double *out);
 
+/* Diagnostic: out[i] = nearest_int(x[i]), the magic-number rounding every quantiser uses (ggml-quants.c:621-626), so that
+ * the device form can be swept over its whole input range on its own (tests/test_helpers_gpu.py).  The conversions
+ * f32 -> f16 / f16 -> f32 (ggml-impl.h:396-443) are swept through sg_convert_float. */
+SG_API int sg_selftest_nearest_int(int device, void *stream, const float *x, int *out, long long n);
+
 /* Allocation-free variant for hosts that cannot tolerate (or cannot supply memory for) a device allocation while
  * they run - a packer that has split the measured free device memory into fixed windows, or a pipeline whose
  * other streams must not be stalled by cudaMalloc's device-wide synchronisation.  It has no counterpart in the

@@ -67,6 +67,7 @@ SIGNATURES = {
     "sg_dm_exp2": (_I, [_I, _P, _P, _L, _P]),
     "sg_dm_rows": (_I, [_I, _P, _P, _L, _L, _I, _P]),
     "sg_dm_cols": (_I, [_I, _P, _P, _L, _L, _I, _P, _P]),
+    "sg_selftest_nearest_int": (_I, [_I, _P, _P, _P, _L]),
     "sg_quantize_legacy_imx_static": (_I, [_I, _P, _I, _P, _I, _P, _P, ctypes.POINTER(sg_tensor), _I]),
 }
 

@@ -165,3 +165,20 @@ extern "C" int sg_convert_float(int device, void* stream, const void* src, int s
     k_convert_float<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(src, src_dtype, dst, dst_dtype, n);
     return cuda_ok(cudaGetLastError());
 }
+
+// nearest_int of every element: the rounding helper of all quantisers, exposed so that it can be swept on its own
+__global__ void __launch_bounds__(256) k_nearest_int(const float* __restrict__ x, int* __restrict__ out, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = sg::nearest_int(x[i]);
+}
+
+extern "C" int sg_selftest_nearest_int(int device, void* stream, const float* x, int* out, long long n) {
+    if (n < 0 || (n && (!x || !out))) return SG_ERR_ARG;
+    if (n == 0) return SG_OK;
+    int rc = use_device(device);
+    if (rc != SG_OK) return rc;
+    const long long grid = (n + 255) / 256;
+    if (grid > 0x7fffffffLL) return SG_ERR_LIMIT;
+    k_nearest_int<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(x, out, n);
+    return cuda_ok(cudaGetLastError());
+}

@@ -554,8 +554,17 @@ class CUDARuntimeError(RuntimeError):
     pass
 
 
+_MEMINFO = [0.0, None]
+
+
 def _mem_get_info():
-    return torch.cuda.mem_get_info()
+    """(free, total) device bytes; the driver call behind it synchronises, and the reference polls it in inner loops
+    (repo3._dev_free, _fits_gpu, _window_bytes), so an answer is reused for a quarter of a second"""
+    import time
+    now = time.monotonic()
+    if _MEMINFO[1] is None or now - _MEMINFO[0] > 0.25:
+        _MEMINFO[0], _MEMINFO[1] = now, torch.cuda.mem_get_info()
+    return _MEMINFO[1]
 
 
 def _memcpy(dst, src, size, kind=None):
@@ -631,9 +640,10 @@ cuda = _NS(runtime=runtime, Device=Device, Stream=Stream, Event=Event, get_curre
 
 
 class _DevicePool:
-    """torch's caching allocator seen as CuPy's pool.  Cached blocks are handed back only under memory pressure:
-    returning them costs a device-wide synchronisation, and this card is not short of memory"""
-    LOW = 8 << 30
+    """torch's caching allocator seen as CuPy's pool.  Cached blocks are handed back only when the cache has grown past
+    half of the card: returning them costs a device-wide synchronisation (and so does asking the driver how much is
+    free), and the reference asks for it after every file and every batch (repo3._release, _trim_cached)"""
+    _limit = None
 
     def free_bytes(self):
         return max(0, torch.cuda.memory_reserved() - torch.cuda.memory_allocated())
@@ -648,7 +658,9 @@ class _DevicePool:
         return 0
 
     def free_all_blocks(self, stream=None):
-        if torch.cuda.mem_get_info()[0] < self.LOW:
+        if self._limit is None:
+            type(self)._limit = torch.cuda.get_device_properties(torch.cuda.current_device()).total_memory // 2
+        if torch.cuda.memory_reserved() > self._limit:
             torch.cuda.empty_cache()
 
     def set_limit(self, size=None, fraction=None):

@@ -59,12 +59,13 @@ class GPUQuant:
             return w
         if isinstance(w, cp.ndarray):
             return w.dev_in().view(torch.float32)
-        key = (id(w), len(w))
+        w = np.ascontiguousarray(w, np.float32).reshape(-1)
+        key = hash(w.tobytes())                      # by content: unit weights are a fresh array per tensor (repo3.py:859-860)
         hit = self._imx.get(key)
-        if hit is None or hit[0] is not w:
+        if hit is None or hit[0].size != w.size or not np.array_equal(hit[0], w):
             if len(self._imx) > 4096:
                 self._imx.clear()
-            hit = (w, torch.from_numpy(np.ascontiguousarray(w, np.float32).reshape(-1)).to(self.q.device))
+            hit = (w.copy(), torch.from_numpy(w).to(self.q.device))
             self._imx[key] = hit
         return hit[1]
 

@@ -20,17 +20,24 @@ def tensor():
     return bits, imx, x
 
 
-@pytest.mark.parametrize("t", [8, 3, 12, 14, 17, 18, 19, 29, 23, 35])
-def test_rows_are_independent_at_full_size(tensor, t):
-    """the whole tensor in one launch gives the bytes of its two halves quantised on their own, and of a sample of
-    single rows against the CPU checker"""
+# the benchmark's 40 launches: every type of the reference's table with the importance matrix, the 15 whose matrix-free
+# routine is another code path, and the 5 further quantisers, which take none
+_ALL = [2, 3, 6, 7, 8, 10, 11, 12, 13, 14, 16, 17, 18, 19, 20, 21, 22, 23, 29, 42]
+CASES = [(t, True) for t in _ALL] + [(t, False) for t in (2, 3, 6, 7, 10, 11, 12, 13, 14, 18, 20, 21, 22, 23, 29, 34, 35, 39, 40, 41)]
+
+
+@pytest.mark.parametrize("t,use", CASES)
+def test_rows_are_independent_at_full_size(tensor, t, use):
+    """the whole tensor in one launch gives the bytes of its two halves quantised on their own, and five of its rows
+    (12288 weights each: 48 super-blocks, the whole-row mean square of the legacy importance paths) equal the
+    reference's C code"""
     import torch
     from oracle import ref
     from seedpack_b200.gpuquant import GPUQuant
     from seedpack_b200.requant import QFUN
     bits, imx, x = tensor
     gq = GPUQuant()
-    w = None if t == 35 else imx
+    w = imx if use else None
     whole = gq.quantize_tensors(t, [(x, NPR)], [w], device=True)[0]
     half = NROWS // 2 * NPR
     a, b = gq.quantize_tensors(t, [(x[:half], NPR), (x[half:], NPR)], [w, w], device=True)
@@ -39,10 +46,11 @@ def test_rows_are_independent_at_full_size(tensor, t):
     if ref.available():
         _, qk, bs = QFUN[t]
         rb = NPR // qk * bs
-        h = whole.cpu().numpy()
-        for r in (0, 1, 2047, 2048, 4095):
+        rows = (0, 1, 2047, 2048, 4095)
+        h = torch.cat([whole[r * rb:(r + 1) * rb] for r in rows]).cpu().numpy()
+        for k, r in enumerate(rows):
             want = ref.quantize(t, synth.bf16_bits_to_f32(bits[r:r + 1]).reshape(1, NPR), w, threads=1)
-            assert np.array_equal(h[r * rb:(r + 1) * rb], want), (t, r)
+            assert np.array_equal(h[k * rb:(k + 1) * rb], want), (t, use, r)
 
 
 @pytest.mark.parametrize("T", [12, 17])
