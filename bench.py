@@ -579,6 +579,94 @@ def pack_cpu_baseline(args, tmp, quantize, cli):
 
 
 # ------------------------------------------------------------------------------------------------------
+# `shard`: one window of a 27B-shaped repository (rows of 5120 and 17408 weights) cut over the ranks by rANS segment:
+# every rank regrows the rows behind its segments, compares them with the stored blocks, models and counts its segments;
+# counts are added through the host, tables normalised on every rank alike, segments coded and gathered on rank 0.
+SHARD_TYPES = [2, 3, 6, 7, 8, 10, 11, 12, 13, 14, 16, 17, 18, 19, 20, 21, 22, 23, 29, 42]
+
+
+def run_shard(args):
+    import hashlib
+    import torch
+    import torch.distributed as dist
+    from seedpack_b200 import shardcode
+    from seedpack_b200.qr import BS, QK
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.new_group(backend="gloo")           # the path's own exchange goes through the host
+    types = [int(t) for t in args.shard_types.split(",")] if args.shard_types else SHARD_TYPES
+    shapes = [(args.shard_rows, 5120), (args.shard_rows // 4, 17408)]
+    case = shardcode.make_case(types[0], shapes, seed=11)
+    batches = {}
+    for T in types:
+        b = shardcode.ShardedBatch(dict(case, T=T), rank, world, local, group=group)
+        if batches:                                      # the base window and importance vectors are on the device once
+            first = next(iter(batches.values()))
+            b.seed, b.imx = first.seed, first.imx
+        batches[T] = b.prepare()
+    nweights = sum(nr * nc for nr, nc in shapes)
+    file_bytes = sum(nweights // QK[T] * BS[T] for T in types)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        h = hashlib.sha256()
+        nd = 0
+        for T in types:
+            buf, d = batches[T].run()
+            nd += d
+            if buf is not None:
+                h.update(buf)
+        return h.hexdigest(), nd
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        digest, ndiff = step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.summary()
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    if rank == 0:
+        peak, peak_kind = peaks()
+        ms_step = ms / args.steps
+        val = file_bytes / (ms_step * 1e-3) / 1e9
+        line = {"metric": "sharded regrow + compare + code, GB/s of GGUF bytes", "value": val, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": f"one window of a 27B-shaped repository: BF16 tensors {shapes[0][0]}x5120 and {shapes[1][0]}x17408 "
+                                       f"({nweights} weights), stored as {len(types)} quant types with another importance vector and ~0.5% "
+                                       "of blocks disturbed; per type: regrow, compare, QR-code; cut over the ranks by rANS segment, counts "
+                                       "and coded segments exchanged through the host (gloo)",
+                           "l2": "inputs larger than L2", "types": types},
+                "clocks": clocks, "batches_sha256": digest, "gpu_launches": int(len(types) * 7 * args.steps),
+                "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                        "note": "the window and the stored blocks are resident; the host exchange is inside the timed region"},
+                "roofline": None, "cpu_baseline": None}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------------------
 # Coder workloads (not the default): the rANS symbol coder on BASELINE config 3's stream, the QR residual coder and the
 # R2 BF16 base codec on the config-2 tensor.  Kernel times are CUDA-event times of the library calls
 # (seedpack_b200._lib.timed); `e2e` is wall time through the Python classes with host buffers on both sides.
@@ -811,8 +899,10 @@ def main():
     ap.add_argument("--ref-rows", type=int, default=0, help="rows of the tensor the CPU baseline quantises per step")
     ap.add_argument("--rows", type=int, default=NROWS, help="rows of the tensor (profiling captures use fewer)")
     ap.add_argument("--only", default="", help="comma-separated launch names to keep, e.g. q4_K+imx,iq2_xs+imx")
-    ap.add_argument("--workload", default="pack", choices=["pack", "quant", "rans", "qr", "r2"],
+    ap.add_argument("--workload", default="pack", choices=["pack", "quant", "shard", "rans", "qr", "r2"],
                     help="pack: pack + test of a synthetic repository (the headline); quant: the quantiser sweep; rans / qr / r2: the coders, one GPU")
+    ap.add_argument("--shard-rows", type=int, default=8192, help="shard: rows of the 5120-column tensor (the 17408-column one has a quarter)")
+    ap.add_argument("--shard-types", default="", help="shard: comma-separated ggml type ids (default: the 20 types of the reference's table)")
     ap.add_argument("--repo", default="c1", help="pack: synthetic repository (a key of seedpack_b200.synthrepo.CONFIGS)")
     ap.add_argument("--repo-dir", default="", help="--impl reference: an existing repository directory to pack instead of making the sample")
     ap.add_argument("--symbols", type=int, default=1 << 30, help="rans: symbols in the stream")
@@ -826,6 +916,8 @@ def main():
         assert CASES, "no such launch"
     if args.workload == "pack":
         (run_reference_pack if args.impl == "reference" else run_pack)(args)
+    elif args.workload == "shard":
+        run_shard(args)
     elif args.impl == "reference":
         run_reference(args)
     elif args.workload != "quant":

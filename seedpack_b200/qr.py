@@ -210,9 +210,15 @@ class QRCodec:
         _lib.check(self.lib.sg_rans_tables(self.device.index, self._stream(), _p(f), NTAB2, PB, _p(enc), _p(l)), "sg_rans_tables")
         return enc, l
 
-    def encode(self, T, items, seed_dev, imx_dev=None, mv=None):
-        """items: [(file tensor bytes, predicted bytes, seed byte offset, seed type[, weights per row, imatrix
-        offset])] of one batch, all of ggml type T -> bytes of the coded batch (seedpack/qr.py:1007-1061)"""
+    # ---- encoding, in the three steps a sharded run needs ------------------------------------------------------------
+    # A batch's segments are independent once its tables are fixed, and its tables are the normalised SUM of the
+    # segments' symbol counts.  So: hist() models this rank's segments and counts their symbols; the counts of all
+    # ranks are added (seedpack_b200.shard.sum_counts) and normalised on every rank alike; code() codes this rank's
+    # segments with those tables; the ranks' lengths and bytes, joined in segment order (shard.gather_segments), go
+    # into finish().  encode() is the three steps over all segments on one GPU.
+    def hist(self, T, items, seed_dev, imx_dev=None, mv=None, segs=None):
+        """model the segments [s0, s1) of the batch (default: all) -> (state for code(), counts [294, 256] int64).
+        Only the blocks of those segments are brought to the device."""
         if T not in QR_TYPES:
             raise ValueError(f"ggml type {T} has no QR model")
         mv = MODEL if mv is None else mv
@@ -223,37 +229,70 @@ class QRCodec:
             if len(it[0]) % bs or len(it[0]) != len(it[1]):
                 raise ValueError(f"tensor {k}: file and prediction must be the same whole number of {bs}-byte blocks")
         seed = _dev_u8(seed_dev, self.device)
-        tm_d, sg_d, nseg, nb = self._records(T, nbs, [it[2] for it in items], [it[3] for it in items],
-                                             [it[4] if len(it) > 4 else 0 for it in items],
-                                             [it[5] if len(it) > 5 else -1 for it in items], seed.numel(),
-                                             0 if imx is None else imx.numel())
-        F = _gather([it[0] for it in items], self.device)
-        P = _gather([it[1] for it in items], self.device)
+        seed_offs, seed_types = [it[2] for it in items], [it[3] for it in items]
+        cols = [it[4] if len(it) > 4 else 0 for it in items]
+        imx_offs = [it[5] if len(it) > 5 else -1 for it in items]
+        check_records(T, nbs, seed_offs, seed_types, cols, imx_offs, seed.numel(), 0 if imx is None else imx.numel())
+        tm, sg, nb_all = _layout(T, nbs)
+        tm["seed_off"], tm["seed_type"], tm["cols"], tm["imx_off"] = seed_offs, seed_types, cols, imx_offs
+        s0, s1 = (0, len(sg)) if segs is None else segs
+        if not 0 <= s0 <= s1 <= len(sg):
+            raise ValueError(f"segments {s0}..{s1} of a batch of {len(sg)}")
+        sg = sg[s0:s1].copy()
+        nseg = len(sg)
+        # this share's blocks are one contiguous range [B0, B1) of the batch: records are rebased to it
+        B0 = int(sg["b0"][0]) if nseg else 0
+        B1 = int(sg["b0"][-1] + sg["nb"][-1]) if nseg else 0
+        nb = B1 - B0
+        sg["b0"] -= B0
+        tm = tm.copy()
+        tm["blk0"] -= B0
+        fparts, pparts = [], []
+        for k, it in enumerate(items):
+            a = max(B0, int(tm["blk0"][k]) + B0) - (int(tm["blk0"][k]) + B0)        # first block of tensor k in the range
+            z = min(B1, int(tm["blk0"][k]) + B0 + nbs[k]) - (int(tm["blk0"][k]) + B0)
+            if z > a:
+                fparts.append(it[0][a * bs:z * bs]); pparts.append(it[1][a * bs:z * bs])
+        F = _gather(fparts, self.device) if fparts else torch.empty(0, dtype=torch.uint8, device=self.device)
+        P = _gather(pparts, self.device) if pparts else torch.empty(0, dtype=torch.uint8, device=self.device)
+        tm_d = torch.from_numpy(tm.view(np.uint8).copy()).to(self.device)
+        sg_d = torch.from_numpy(sg.view(np.uint8).copy()).to(self.device) if nseg else torch.zeros(16, dtype=torch.uint8, device=self.device)
         ne = torch.empty(max(nb, 1), dtype=torch.uint8, device=self.device)
         ndiff = torch.zeros(1, dtype=torch.int64, device=self.device)
-        with _lib.timed("residual_blocks"):
-            _lib.check(self.lib.sg_residual_blocks(d, st, _p(F), _p(P), bs, nb, _p(ne), _p(ndiff)), "sg_residual_blocks")
         counts = torch.zeros(NTAB2 * 256, dtype=torch.int32, device=self.device)
         stage = None
-        if self.staged:            # the model once, one lane per block; histogram and coder work on the staged pairs
-            nstage = self.lib.sg_qr_stage_bytes(T, nb)
-            stage = torch.empty(max(nstage, 16), dtype=torch.uint8, device=self.device)
-            with _lib.timed("qr_stage"):
-                _lib.check(self.lib.sg_qr_stage(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), mv, nb, _p(stage),
-                                                nstage), "sg_qr_stage")
-            with _lib.timed("qr_stage_hist"):
-                _lib.check(self.lib.sg_qr_stage_hist(d, st, T, nb, _p(stage), _p(counts)), "sg_qr_stage_hist")
-        else:
-            with _lib.timed("qr_hist"):
-                _lib.check(self.lib.sg_qr_hist(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(counts), mv),
-                           "sg_qr_hist")
-        freq, used = normalize(counts.cpu().numpy().astype(np.uint32).reshape(NTAB2, 256))
+        if nseg:
+            with _lib.timed("residual_blocks"):
+                _lib.check(self.lib.sg_residual_blocks(d, st, _p(F), _p(P), bs, nb, _p(ne), _p(ndiff)), "sg_residual_blocks")
+            if self.staged:            # the model once, one lane per block; histogram and coder work on the staged pairs
+                nstage = self.lib.sg_qr_stage_bytes(T, nb)
+                stage = torch.empty(max(nstage, 16), dtype=torch.uint8, device=self.device)
+                with _lib.timed("qr_stage"):
+                    _lib.check(self.lib.sg_qr_stage(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), mv, nb, _p(stage),
+                                                    nstage), "sg_qr_stage")
+                with _lib.timed("qr_stage_hist"):
+                    _lib.check(self.lib.sg_qr_stage_hist(d, st, T, nb, _p(stage), _p(counts)), "sg_qr_stage_hist")
+            else:
+                with _lib.timed("qr_hist"):
+                    _lib.check(self.lib.sg_qr_hist(d, st, T, _p(F), _p(P), _p(ne), _p(seed), _p(tm_d), _p(sg_d), nseg, _p(imx), _p(counts), mv),
+                               "sg_qr_hist")
+        state = dict(T=T, mv=mv, F=F, P=P, seed=seed, imx=imx, tm_d=tm_d, sg_d=sg_d, nseg=nseg, nb=nb, ne=ne, stage=stage)
+        _lib.count_d2h(NTAB2 * 1024)
+        return state, counts.cpu().numpy().view(np.uint32).astype(np.int64).reshape(NTAB2, 256)
+
+    def code(self, state, freq, used):
+        """code the segments hist() modelled with the tables (freq, used) -> (their lengths uint32, their bytes)"""
+        T, mv, nseg, nb = state["T"], state["mv"], state["nseg"], state["nb"]
+        if not nseg:
+            return np.zeros(0, np.uint32), b""
+        d, st = self.device.index, self._stream()
+        F, P, seed, imx, tm_d, sg_d, ne, stage = (state[k] for k in ("F", "P", "seed", "imx", "tm_d", "sg_d", "ne", "stage"))
         enc, _ = self._tables(freq, used, lut=False)
         cap = seg_blocks(T) * (3 * BS[T] if T in GRID_TYPES else (QK[T] + NSB_MAX) * 2) + 1024
         cap = (cap + 15) // 16 * 16
         for _ in range(3):
-            slots = torch.empty(max(nseg, 1) * cap, dtype=torch.uint8, device=self.device)
-            lens = torch.zeros(max(nseg, 1), dtype=torch.int32, device=self.device)
+            slots = torch.empty(nseg * cap, dtype=torch.uint8, device=self.device)
+            lens = torch.zeros(nseg, dtype=torch.int32, device=self.device)
             if self.staged:
                 with _lib.timed("qr_stage_encode"):
                     _lib.check(self.lib.sg_qr_stage_encode(d, st, T, nb, _p(stage), _p(sg_d), nseg, _p(enc), _p(slots), cap, _p(lens)),
@@ -264,7 +303,7 @@ class QRCodec:
                                                      _p(slots), cap, _p(lens), mv), "sg_qr_encode")
             # the segments' lengths are read on the host (they are part of the batch anyway): sentinels are seen there,
             # not through the device status word, which other threads' calls share
-            lens_h = lens[:nseg].cpu().numpy().view(np.uint32)
+            lens_h = lens.cpu().numpy().view(np.uint32)
             check_lens(lens_h)
             if not (lens_h == LEN_OVERFLOW).any():
                 break
@@ -277,11 +316,24 @@ class QRCodec:
         with _lib.timed("scan_gather"):
             _lib.check(self.lib.sg_scan_gather(d, st, _p(slots), cap, _p(lens), nseg, _p(dst), total, _p(off)), "sg_scan_gather")
         stream = dst[:total].cpu().numpy().tobytes()
-        _lib.count_d2h(total + 4 * nseg + NTAB2 * 1024)
-        out = {"t": store_tables(freq, used), "l": zstd.compress(lens_h.astype(np.uint32).tobytes(), 19), "s": stream}
+        _lib.count_d2h(total + 4 * nseg)
+        return lens_h.astype(np.uint32), stream
+
+    @staticmethod
+    def finish(freq, used, lens, stream, mv=MODEL):
+        """the batch as the archive holds it (seedpack/qr.py:1058-1061): tables, segment lengths, streams, model byte"""
+        out = {"t": store_tables(freq, used), "l": zstd.compress(np.asarray(lens, np.uint32).tobytes(), 19), "s": bytes(stream)}
         if mv != 1:
             out["v"] = bytes([mv])
         return pack(out)
+
+    def encode(self, T, items, seed_dev, imx_dev=None, mv=None):
+        """items: [(file tensor bytes, predicted bytes, seed byte offset, seed type[, weights per row, imatrix
+        offset])] of one batch, all of ggml type T -> bytes of the coded batch (seedpack/qr.py:1007-1061)"""
+        state, counts = self.hist(T, items, seed_dev, imx_dev, mv)
+        freq, used = normalize(counts)
+        lens, stream = self.code(state, freq, used)
+        return self.finish(freq, used, lens, stream, state["mv"])
 
     def decode(self, T, buf, items, seed_dev, imx_dev=None):
         """items: [(predicted bytes, seed byte offset, seed type[, weights per row, imatrix offset])] -> device uint8

@@ -63,6 +63,7 @@ def install(reference=None, staged_qr=None):
     from .. import _lib
     _lib.lib()                                    # fails loudly if the CUDA library is not built
     from . import cupy_shim, kernels, quant
+    cupy_shim.bind_device()                       # this process's GPU: the one current now, for all of its threads
     sys.modules["cupy"] = cupy_shim
     sys.modules["cupyx"] = cupy_shim.cupyx
     if importlib.util.find_spec("zstandard") is None:
@@ -103,7 +104,7 @@ def _bind_qr(qr, staged):
     codecs = {}
 
     def codec():
-        d = torch.cuda.current_device()
+        d = cp.device_index()
         if d not in codecs:
             codecs[d] = own.QRCodec(d, staged=True)
         return codecs[d]
@@ -142,7 +143,8 @@ def _bind_r2(bf16v2):
         need = L.sg_r2_stats_scratch_bytes(nr, rl)
         scratch = torch.empty(need + 16, dtype=torch.uint8, device=dev.dev_in().device)
         p = lambda t: ctypes.c_void_p(t.data_ptr())
-        _lib.check(L.sg_r2_stats(torch.cuda.current_device(), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
+        d = cp.device_index()
+        _lib.check(L.sg_r2_stats(d, ctypes.c_void_p(torch.cuda.current_stream(d).cuda_stream),
                                  p(dev.dev_in()), nr, rl, p(rfi.dev_out()), p(cfi.dev_out()), p(scl.dev_out()), p(scratch), need),
                    "sg_r2_stats")
         return rfi, cfi, scl
@@ -173,7 +175,8 @@ def _bind_float(repo3):
         src = a.dev_in()
         if src.data_ptr() % 16:
             src = src.clone()
-        _lib.check(_lib.lib().sg_convert_float(torch.cuda.current_device(), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
+        d = cp.device_index()
+        _lib.check(_lib.lib().sg_convert_float(d, ctypes.c_void_p(torch.cuda.current_stream(d).cuda_stream),
                                                ctypes.c_void_p(src.data_ptr()), sd, ctypes.c_void_p(y.dev_out().data_ptr()), dd, a.size),
                    "sg_convert_float")
         return y

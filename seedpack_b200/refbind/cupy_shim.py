@@ -34,8 +34,32 @@ STATS = {"d2h": 0, "h2d": 0, "host_ops": 0}
 _LOCK = threading.RLock()          # residency changes of a storage (arrays are shared between the pipelines' threads)
 
 
+# One process drives one GPU: the device that was current when the binding was installed.  torch's "current device" is
+# a per-thread setting that starts at device 0 in every new thread, and the reference works from several threads
+# (window preparation, the QR coder, the base coder): each of them is put on the bound device the first time it comes
+# through here, so that no allocation or launch of a worker thread lands on another process's GPU.
+DEVICE = None
+_TLS = threading.local()
+
+
+def bind_device(index=None):
+    global DEVICE
+    DEVICE = torch.cuda.current_device() if index is None else int(index)
+    return DEVICE
+
+
+def device_index():
+    """the bound device's ordinal; the calling thread is switched to it"""
+    if DEVICE is None:
+        bind_device()
+    if getattr(_TLS, "dev", None) != DEVICE:
+        torch.cuda.set_device(DEVICE)
+        _TLS.dev = DEVICE
+    return DEVICE
+
+
 def _device():
-    return torch.device("cuda", torch.cuda.current_device())
+    return torch.device("cuda", device_index())
 
 
 class _Storage:
@@ -563,7 +587,7 @@ def _mem_get_info():
     import time
     now = time.monotonic()
     if _MEMINFO[1] is None or now - _MEMINFO[0] > 0.25:
-        _MEMINFO[0], _MEMINFO[1] = now, torch.cuda.mem_get_info()
+        _MEMINFO[0], _MEMINFO[1] = now, torch.cuda.mem_get_info(device_index())
     return _MEMINFO[1]
 
 
@@ -572,12 +596,12 @@ def _memcpy(dst, src, size, kind=None):
 
 
 runtime = _NS(memGetInfo=_mem_get_info, CUDARuntimeError=CUDARuntimeError, getDeviceCount=torch.cuda.device_count,
-              memcpy=_memcpy, deviceSetLimit=lambda *a: None, deviceSynchronize=torch.cuda.synchronize)
+              memcpy=_memcpy, deviceSetLimit=lambda *a: None, deviceSynchronize=lambda: torch.cuda.synchronize(device_index()))
 
 
 class Device:
     def __init__(self, device=None):
-        self.id = torch.cuda.current_device() if device is None else int(device)
+        self.id = device_index() if device is None else int(device)
 
     @property
     def compute_capability(self):
@@ -609,7 +633,7 @@ class Stream:
         self.ptr = 0
 
     def synchronize(self):
-        torch.cuda.current_stream().synchronize()
+        torch.cuda.current_stream(device_index()).synchronize()
 
     def use(self):
         return self
@@ -646,21 +670,23 @@ class _DevicePool:
     _limit = None
 
     def free_bytes(self):
-        return max(0, torch.cuda.memory_reserved() - torch.cuda.memory_allocated())
+        d = device_index()
+        return max(0, torch.cuda.memory_reserved(d) - torch.cuda.memory_allocated(d))
 
     def used_bytes(self):
-        return torch.cuda.memory_allocated()
+        return torch.cuda.memory_allocated(device_index())
 
     def total_bytes(self):
-        return torch.cuda.memory_reserved()
+        return torch.cuda.memory_reserved(device_index())
 
     def n_free_blocks(self):
         return 0
 
     def free_all_blocks(self, stream=None):
+        d = device_index()
         if self._limit is None:
-            type(self)._limit = torch.cuda.get_device_properties(torch.cuda.current_device()).total_memory // 2
-        if torch.cuda.memory_reserved() > self._limit:
+            type(self)._limit = torch.cuda.get_device_properties(d).total_memory // 2
+        if torch.cuda.memory_reserved(d) > self._limit:
             torch.cuda.empty_cache()
 
     def set_limit(self, size=None, fraction=None):

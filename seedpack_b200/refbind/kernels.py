@@ -36,11 +36,12 @@ GRID_TYPES = {16, 17, 18, 19, 21, 22, 29}
 
 
 def _dev():
-    return torch.cuda.current_device()
+    from .cupy_shim import device_index
+    return device_index()
 
 
 def _st():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return ctypes.c_void_p(torch.cuda.current_stream(_dev()).cuda_stream)
 
 
 def _p(t):

@@ -50,7 +50,7 @@ class GPUQuant:
     def __init__(self, fmad=False):
         if fmad:
             raise NotImplementedError("the kernels are built without FMA contraction only (as the archives need)")
-        self.q = _gq.GPUQuant()
+        self.q = _gq.GPUQuant(cp.device_index())
         self._imx = {}
 
     def _imatrix(self, w):
@@ -73,6 +73,7 @@ class GPUQuant:
         """srcs: [(weights as bf16 bits (uint16) / f16 / f32 device array, or an object that yields one, weights per
         row)] -> the quantised bytes of every tensor: NumPy arrays in page-locked memory, device arrays with `device`;
         with on_result, on_result(index, bytes) per tensor as its group completes, and nothing is returned"""
+        cp.device_index()                            # (a worker thread's first call: put it on this process's GPU)
         out, i = [], 0
         while i < len(srcs):
             j, n, group = i, 0, []

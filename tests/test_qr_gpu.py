@@ -179,3 +179,34 @@ def test_unknown_seed_type_is_refused():
     bad = [it[:3] + (12,) + it[4:] for it in enc]            # a quantised seed: these kernels do not read it
     with pytest.raises(ValueError):
         QRCodec().encode(12, bad, GS["seed_12_1"], None)
+
+
+# ---- sharded coding: segment ranges, counts summed before the tables are made ------------------------------------------------
+@pytest.mark.parametrize("T", [8, 12, 17])
+def test_batch_coded_in_segment_ranges_equals_the_references_batch(T):
+    """what every rank of a sharded run does, here one range after the other on one GPU: model and count a range of
+    segments, add the counts, normalise once, code each range, join lengths and bytes in segment order"""
+    from seedpack_b200 import shard
+    from seedpack_b200.qr import MODEL, QRCodec, _layout, BS
+    from seedpack_b200.rans import normalize
+    c = QRCodec()
+    if T == 17:
+        G2 = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "qr_grid_golden.npz"))
+        shapes = [tuple(int(v) for v in s) for s in G2["shapes"]]
+        F, P, bs = G2[f"F_{T}"], G2[f"P_{T}"], BS[T]
+        enc, o = [], 0
+        for k, (nr, npr) in enumerate(shapes):
+            n = nr * npr // 256 * bs
+            enc.append((F[o:o + n], P[o:o + n], int(G2["seed_offs"][k]), 30, npr, int(G2["imx_offs"][k]))); o += n
+        seed, imx, want = G2["seed_bits"].view(np.uint8), G2["imx"], G2[f"B_{T}_2"].tobytes()
+    else:
+        enc, _ = _items(T)
+        seed, imx, want = G["seed_bits"].view(np.uint8), None, G[f"B_{T}_2"].tobytes()
+    nseg = len(_layout(T, [len(it[0]) // BS[T] for it in enc])[1])
+    assert nseg >= 2
+    for world in (2, 3):
+        parts = [c.hist(T, enc, seed, imx, MODEL, shard.segment_range(nseg, r, world)) for r in range(world)]
+        freq, used = normalize(sum(p[1] for p in parts))
+        coded = [c.code(p[0], freq, used) for p in parts]
+        got = c.finish(freq, used, np.concatenate([x[0] for x in coded]), b"".join(x[1] for x in coded), MODEL)
+        assert got == want, f"world {world}"
