@@ -47,6 +47,26 @@ NO_IMX_ONLY = [34, 35, 39, 40, 41]                                        # type
 CASES = [(t, True) for t in sorted(QFUN) if t not in NO_IMX_ONLY] + [(t, False) for t in NO_IMX_TOO + NO_IMX_ONLY]
 
 
+# fp32 add / mul thread instructions and all thread instructions per weight of every launch of the sweep, counted by ncu
+# on a 256-row tensor (profiles/quant_fp32_ops_ncu.md gives the command); the counts per weight do not depend on the
+# number of rows.  Launches with fewer than 30 fp32 operations per weight are bound by memory traffic and instruction
+# issue for the packing; the others by the quantisers' scale searches: fp32 add / mul issue.
+OPS = {"q6_K+imx": [186.2, 286.2], "iq2_xxs+imx": [695.1, 2780.0], "iq2_xs+imx": [1118.8, 5405.5], "iq3_xxs+imx": [1795.9, 4190.8],
+       "iq1_s+imx": [576.5, 1235.0], "iq4_nl+imx": [143.6, 646.4], "iq3_s+imx": [1287.9, 2870.3], "iq2_s+imx": [467.9, 1669.1],
+       "iq4_xs+imx": [144.3, 650.9], "iq1_m+imx": [379.4, 1044.6], "q2_0+imx": [2.1, 13.7], "q4_0": [2.3, 17.0], "q4_1": [3.5, 20.0],
+       "q5_0": [2.3, 20.1], "q5_1": [3.5, 20.2], "q2_K": [286.8, 445.3], "q3_K": [28.3, 115.1], "q4_K": [356.9, 522.5],
+       "q5_K": [277.5, 419.6], "q6_K": [186.9, 285.7], "iq3_xxs": [1800.5, 4204.2], "iq4_nl": [140.6, 637.8], "iq3_s": [1281.3, 2860.3],
+       "iq2_s": [461.6, 1652.5], "iq4_xs": [145.5, 643.5], "iq1_m": [368.9, 996.0], "tq1_0": [2.3, 26.7], "tq2_0": [2.3, 24.4],
+       "mxfp4": [16.1, 88.9], "nvfp4": [16.6, 84.1], "q1_0": [1.0, 16.5], "q4_0+imx": [181.5, 251.4], "q4_1+imx": [646.9, 829.2],
+       "q5_0+imx": [181.4, 253.8], "q5_1+imx": [646.9, 831.7], "q8_0+imx": [2.4, 16.2], "q2_K+imx": [873.5, 1267.1],
+       "q3_K+imx": [346.6, 547.8], "q4_K+imx": [702.4, 940.8], "q5_K+imx": [702.3, 947.7]}
+SMS, FP32_LANES, ISSUE_SLOTS = 148, 128, 4
+
+
+def bound_of(name):
+    return "hbm" if OPS[name][0] < 30 else "fp32_issue"
+
+
 # DRAM traffic of one full-size launch (bytes read + written), from ncu captures on 1024 of the 4096 rows scaled by 4
 # (the traffic grows with the rows; profiles/quant_lattice_queue_ncu_full.md).  Writes that were still in L2 when the
 # captured kernel ended are not in the counter.
@@ -151,7 +171,7 @@ def run_reference(args):
     from oracle import ref
     threads = os.cpu_count() or 1
     rows = args.ref_rows or default_ref_rows(threads)
-    cfg = {"workload": workload_text(), "sample_rows": rows}
+    cfg = {"workload": workload_text() + ", one tensor per GPU", "l2": "flushed between launches (256 MiB memset inside the timed region)"}
     if not ref.available():
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libggmlq_ref.so not built (needs the reference tree at build time)"}))
         return
@@ -168,7 +188,7 @@ def run_reference(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": cfg,
             "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "reference",
-                             "sample": f"first {rows} of {NROWS} rows of the same tensor, all {len(CASES)} launches per step"},
+                             "sample": f"first {rows} of {NROWS} rows of the same tensor ({100 * rows / NROWS:.1f}% of it), all {len(CASES)} launches per step"},
             "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -183,7 +203,7 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = torch.device("cuda", local)
     gq = GPUQuant(local)
@@ -277,13 +297,23 @@ def run_ours(args):
         peak, peak_kind = peaks()
         per_ms = per / args.steps
         table = {}
+        clk = (clocks.get("sm_mhz") or 1965.0) * 1e6
+        fp32_peak = SMS * FP32_LANES * clk / 1e12               # T fp32 add / mul per second at the sampled clock
+        nw = NROWS * NPR
         for k, (t, use) in enumerate(CASES):
-            a = algo_bytes(t, use) / (per_ms[k] * 1e-3) / 1e9
-            table[f"{QFUN[t][0]}{'+imx' if use else ''}"] = {"ms": round(float(per_ms[k]), 4), "algo_gbs": round(a, 1),
-                                                              "gguf_gbs": round(quant_bytes(t) / (per_ms[k] * 1e-3) / 1e9, 2),
-                                                              "hbm_frac": round(a / peak, 4)}
+            name = case_name(t, use)
+            sec = per_ms[k] * 1e-3
+            a = algo_bytes(t, use) / sec / 1e9
+            row = {"ms": round(float(per_ms[k]), 4), "bound": bound_of(name), "algo_gbs": round(a, 1),
+                   "gguf_gbs": round(quant_bytes(t) / sec / 1e9, 2), "hbm_frac": round(a / peak, 4),
+                   "issue_slots_busy": round(OPS[name][1] * nw / 32 / sec / (SMS * ISSUE_SLOTS * clk), 3)}
+            if row["bound"] == "fp32_issue":
+                row["fp32_tops"] = round(OPS[name][0] * nw / sec / 1e12, 2)
+                row["fp32_frac"] = round(OPS[name][0] * nw / sec / 1e12 / fp32_peak, 3)
+            table[name] = row
         dom = int(np.argmax(per_ms))
         dt, duse = CASES[dom]
+        dname = case_name(dt, duse)
         ach = algo_bytes(dt, duse) / (per_ms[dom] * 1e-3) / 1e9
         # CPU baseline: the reference's C code on a bounded row sample, all host threads
         cpu = None
@@ -301,21 +331,17 @@ def run_ours(args):
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": workload_text() + ", one tensor per GPU",
-                           "l2": "flushed between launches (256 MiB memset inside the timed region)",
-                           "per_type": table},
+                           "l2": "flushed between launches (256 MiB memset inside the timed region)"},
+                "per_type": table,
                 "clocks": clocks,
                 "e2e": {"value": world * out_bytes / e2e_s / 1e9, "unit": "GB/s",
                         "h2d_bytes_per_step": int(world * (hx.numel() * 2 + himx.numel() * 4)), "d2h_bytes_per_step": int(world * out_bytes)},
                 "gpu_launches": int(launches),
-                "roofline": {"bound": "hbm", "kernel": f"k_quant {QFUN[dt][0]}{'+imx' if duse else ''} (largest share of the step)",
-                             "achieved": ach, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": ach / peak,
-                             "traffic": NCU_TRAFFIC.get(f"{QFUN[dt][0]}{'+imx' if duse else ''}") if NROWS == 4096 else None,
-                             "note": "search-bound kernel: the HBM fraction is small by construction; ncu shows 63 % of issue slots "
-                                     "busy and 29 of 32 lanes active (profiles/quant_lattice_queue_ncu_full.md)"},
+                "roofline": quant_roofline(dname, table[dname], ach, peak, peak_kind, fp32_peak),
                 "cpu_baseline": cpu}
-        print(json.dumps(line))
-    if world > 1:
+    if world > 1 and not getattr(args, "keep_group", False):
         dist.destroy_process_group()
+    return line
 
 
 # ------------------------------------------------------------------------------------------------------
@@ -386,6 +412,13 @@ def _reference_cli():
 
 
 PACK_METRIC = "pack/unpack GB/s of GGUF bytes"
+
+
+def pack_config(repo, gpus):
+    """the `config` object of the pack workload, the same in this library's line and in the reference arm's"""
+    return {"workload": _repo_text(repo) + (", one repository per GPU" if gpus > 1 else ""),
+            "step": "pack + test of the repository; bytes per step = 2 x repository bytes",
+            "l2": "inputs larger than L2 (base 1.2 GB, files 1.5 GB)"}
 SAMPLE = "c1-micro"
 
 
@@ -396,7 +429,7 @@ def run_reference_pack(args):
         return
     import shutil
     threads = os.cpu_count() or 1
-    cfg = {"workload": _repo_text(args.repo)}
+    cfg = pack_config(args.repo, args.gpus)
     cli = _reference_cli()
     if cli is None:
         print(json.dumps({"impl": "reference", "unavailable": "the reference package is not installed under baseline/_ref (nor $SEEDPACK_REFERENCE)"}))
@@ -523,19 +556,20 @@ def run_pack(args):
                     "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
                     "wall_ms_per_step": wall / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                     "dtype": "f32", "data": "synthetic",
-                    "config": {"workload": _repo_text(args.repo) + (", one repository per GPU" if world > 1 else ""),
-                               "step": "pack + test of the repository; bytes per step = 2 x repository bytes",
-                               "value_is": "bytes over the summed device time of the step's library calls (CUDA events around each call)",
-                               "l2": "inputs larger than L2 (base 1.2 GB, files 1.5 GB)", "repository_bytes": int(nbytes),
-                               "library_calls": per},
+                    "config": pack_config(args.repo, world),
+                    "value_is": "bytes over the summed device time of the step's library calls (CUDA events around each call); e2e is the wall clock",
+                    "repository_bytes": int(nbytes), "library_calls": per,
                     "clocks": clocks,
                     "e2e": {"value": 2 * nbytes_all * args.steps / wall / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
                             "d2h_bytes_per_step": int(d2h), "pack_gbs": nbytes_all * args.steps / tp / 1e9,
                             "unpack_gbs": nbytes_all * args.steps / tu / 1e9},
                     "bit_exact_files": f"{exact}/{total}", "archive_sha256": _file_digest(arc),
                     "gpu_launches": int(sum(v[1] for v in calls.values())),
-                    "roofline": pack_roofline(per, dom, args, peak, peak_kind, clocks)}
+                    "roofline": pack_roofline(per, dom, args, peak, peak_kind, clocks, sum(os.path.getsize(p) for p in made["base"]),
+                                              os.path.getsize(arc))}
             line["cpu_baseline"] = pack_cpu_baseline(args, tmp, quantize, cli) if world == 1 else None
+            if world == 1 and not args.no_kernels:
+                line["kernels"] = kernel_workloads(args)
             print(json.dumps(line))
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
@@ -543,12 +577,41 @@ def run_pack(args):
             dist.destroy_process_group()
 
 
-def pack_roofline(per, dom, args, peak, peak_kind, clocks):
-    """the library call with the largest share of the step's device time"""
+def kernel_workloads(args):
+    """the kernel-level workloads, a few steps each, for the default line: the quantiser sweep over one 4096 x 12288 tensor
+    (per-type table, fp32-issue roofline of its largest launch) and the three coders, each with its own clock samples"""
+    import copy
+    out = {}
+    a = copy.copy(args)
+    a.steps, a.warmup = 3, 3
+    try:
+        q = run_ours(a)
+        out["quant_sweep"] = {k: q[k] for k in ("metric", "value", "unit", "ms_per_step", "config", "per_type", "clocks", "e2e", "roofline")}
+    except Exception as e:
+        out["quant_sweep"] = {"failed": str(e)}
+    a.steps, a.warmup, a.tensors, a.qr_types = 2, 1, 4, "8,12,17"
+    for name, fn in (("rans", run_rans), ("qr", run_qr), ("r2", run_r2)):
+        try:
+            l = fn(a)
+            out[name] = {k: l[k] for k in ("metric", "value", "unit", "ms_per_step", "config", "clocks", "e2e", "roofline")}
+        except Exception as e:
+            out[name] = {"failed": str(e)}
+    return out
+
+
+def pack_roofline(per, dom, args, peak, peak_kind, clocks, base_bytes=0, coded_bytes=0):
+    """the library call with the largest share of the step's device time, against the memory roofline: the base codec's
+    calls move the BF16 base (statistics: rows, then columns twice; coders: base + coded stream)"""
     if dom is None:
         return None
-    return {"bound": "hbm", "kernel": dom, "achieved": None, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": None,
-            "traffic": None, "share_of_device_time": round(per[dom]["ms"] / max(sum(v["ms"] for v in per.values()), 1e-9), 3)}
+    algo = {"sg_r2_stats": 3 * base_bytes, "sg_r2_decode": base_bytes + coded_bytes, "sg_r2_encode": base_bytes + coded_bytes,
+            "sg_r2_hist": base_bytes, "sg_row_hash": base_bytes}.get(dom)
+    ach = algo / (per[dom]["ms"] * 1e-3) / 1e9 if algo else None
+    return {"bound": "hbm", "kernel": f"{dom} ({per[dom]['calls']} calls per step)", "achieved": ach, "peak": peak, "peak_kind": peak_kind,
+            "unit": "GB/s", "frac": ach / peak if ach else None, "traffic": None,
+            "share_of_device_time": round(per[dom]["ms"] / max(sum(v["ms"] for v in per.values()), 1e-9), 3),
+            "note": "the step is bound by the host pipeline (device time is a small part of the wall clock); the kernel-level "
+                    "rooflines are under `kernels`"}
 
 
 def pack_cpu_baseline(args, tmp, quantize, cli):
@@ -780,7 +843,7 @@ def run_rans(args):
                        f"segments of 16384, 12 probability bits; coded to {coded} bytes",
                        S, kern, e2e_s, S + S // 16 + coded, coded + S, table,
                        {"kernel": dom, "achieved": algo[dom] / (ms[dom] * 1e-3) / 1e9}, cpu, 6, clocks)
-    print(json.dumps(line))
+    return line
 
 
 def _flip_bytes(a, bs, frac, seed):
@@ -847,7 +910,7 @@ def run_qr(args):
                        {"value": None, "unit": "GB/s", "cores": 0, "kind": "port",
                         "sample": "no CPU restatement of the QR model is kept; parity is pinned on the reference's own coded batches"},
                        launches, clocks)
-    print(json.dumps(line))
+    return line
 
 
 def run_r2(args):
@@ -882,7 +945,20 @@ def run_r2(args):
                        {"value": None, "unit": "GB/s", "cores": 0, "kind": "port",
                         "sample": "no CPU restatement of the R2 codec is kept; parity is pinned on the reference's own coded parts"},
                        8, clocks)
-    print(json.dumps(line))
+    return line
+
+
+def quant_roofline(name, row, ach_gbs, hbm_peak, peak_kind, fp32_peak):
+    """the launch with the largest share of the step, against the roofline that bounds it"""
+    traffic = NCU_TRAFFIC.get(name) if NROWS == 4096 else None
+    if row["bound"] == "hbm":
+        return {"bound": "hbm", "kernel": f"k_quant {name} (largest share of the step)", "achieved": ach_gbs, "peak": hbm_peak,
+                "peak_kind": peak_kind, "unit": "GB/s", "frac": ach_gbs / hbm_peak, "traffic": traffic}
+    return {"bound": "fp32_issue", "kernel": f"k_quant {name} (largest share of the step)", "achieved": row["fp32_tops"], "peak": round(fp32_peak, 2),
+            "peak_kind": "148 SMs x 128 fp32 lanes x sampled SM clock (no FMA: one add or mul per lane and cycle)", "unit": "Tops/s",
+            "frac": row["fp32_frac"], "traffic": traffic, "hbm_gbs": round(ach_gbs, 1), "issue_slots_busy": row["issue_slots_busy"],
+            "ops_per_weight": OPS[name][0], "instructions_per_weight": OPS[name][1],
+            "counted": "fp32 add / mul thread instructions per weight from ncu (profiles/quant_fp32_ops_ncu.md)"}
 
 
 def case_name(t, use):
@@ -903,6 +979,7 @@ def main():
                     help="pack: pack + test of a synthetic repository (the headline); quant: the quantiser sweep; rans / qr / r2: the coders, one GPU")
     ap.add_argument("--shard-rows", type=int, default=8192, help="shard: rows of the 5120-column tensor (the 17408-column one has a quarter)")
     ap.add_argument("--shard-types", default="", help="shard: comma-separated ggml type ids (default: the 20 types of the reference's table)")
+    ap.add_argument("--no-kernels", action="store_true", help="pack: leave the kernel-level workloads out of the line")
     ap.add_argument("--repo", default="c1", help="pack: synthetic repository (a key of seedpack_b200.synthrepo.CONFIGS)")
     ap.add_argument("--repo-dir", default="", help="--impl reference: an existing repository directory to pack instead of making the sample")
     ap.add_argument("--symbols", type=int, default=1 << 30, help="rans: symbols in the stream")
@@ -922,9 +999,11 @@ def main():
         run_reference(args)
     elif args.workload != "quant":
         if int(os.environ.get("RANK", "0")) == 0:
-            {"rans": run_rans, "qr": run_qr, "r2": run_r2}[args.workload](args)
+            print(json.dumps({"rans": run_rans, "qr": run_qr, "r2": run_r2}[args.workload](args)))
     else:
-        run_ours(args)
+        line = run_ours(args)
+        if line is not None:
+            print(json.dumps(line))
 
 
 if __name__ == "__main__":
