@@ -730,7 +730,7 @@ def run_shard(args):
 
 
 # ------------------------------------------------------------------------------------------------------
-# Coder workloads (not the default): the rANS symbol coder on BASELINE config 3's stream, the QR residual coder and the
+# Coder workloads: the rANS symbol coder on a stream of 2^30 residual symbols, the QR residual coder and the
 # R2 BF16 base codec on the config-2 tensor.  Kernel times are CUDA-event times of the library calls
 # (seedpack_b200._lib.timed); `e2e` is wall time through the Python classes with host buffers on both sides.
 def _codec_line(args, metric, workload, unit_bytes, kern_ms, e2e_s, h2d, d2h, table, roof, cpu, launches, clocks):
@@ -763,7 +763,7 @@ def _timed_steps(args, fn):
 
 
 def synth_symbols(nsym, seed, device):
-    """BASELINE config 3's stream: blocks of 32 symbols, each block with an alphabet of 4 / 5 / 6 / 8 bits and one of
+    """the residual-codec microbenchmark's stream: blocks of 32 symbols, each block with an alphabet of 4 / 5 / 6 / 8 bits and one of
     292 context tables; 97 % zeros, the rest discrete Laplace(b = 2) folded into the alphabet"""
     import torch
     g = torch.Generator(device=device); g.manual_seed(seed)
@@ -847,7 +847,7 @@ def run_rans(args):
 
 
 def _flip_bytes(a, bs, frac, seed):
-    """one random byte XOR-flipped in `frac` of the blocks of a (BASELINE config 1's non-derivable residuals)"""
+    """one random byte XOR-flipped in `frac` of the blocks of a (residuals that no prediction explains)"""
     rng = np.random.default_rng(seed)
     nb = len(a) // bs
     pick = rng.choice(nb, max(1, int(nb * frac)), replace=False)
@@ -914,33 +914,44 @@ def run_qr(args):
 
 
 def run_r2(args):
+    """the R2 base codec on a file of K tensors of the benchmark shape: the reference's BF16v2 / R2Tensors classes over the
+    bound kernels (seedpack_b200.refbind); kernel times are CUDA-event times of the library calls"""
     import torch
-    from seedpack_b200.bf16v2 import BF16v2, R2Tensors, layout_of
+    from seedpack_b200 import _lib, refbind, synthrepo
     torch.cuda.set_device(0)
+    refbind.install()
+    from seedpack import bf16v2, codecs_gguf
     K = args.tensors
-    data = np.concatenate([synth_tensor(1 + k)[0].view(np.uint8).reshape(-1) for k in range(K)])
-    one = len(data) // K
-    layout = layout_of([(f"blk.{k}.ffn_up.weight", k * one, one, NPR) for k in range(K)], len(data))
-    codec = BF16v2(device=0)
+    tens = [synth_tensor(1 + k)[0] for k in range(K)]
+    data = synthrepo.gguf_bytes([("general.alignment", 4, 32)],
+                                [(f"blk.{k}.ffn_up.weight", (NPR, NROWS), 30, NROWS * NPR * 2, (lambda k=k: tens[k])) for k in range(K)])
+    n = K * NROWS * NPR * 2
     st = {}
 
     def step():
-        parts = codec.compress_parts(data, layout)
-        r = R2Tensors(parts, 0)
-        dev, outs = r.decode(range(len(layout["t"])))
-        st.update(parts=parts, dev=dev, outs=outs)
+        chunk = b"".join(bytes(p) for p in bf16v2.BF16v2().compress_parts(data))
+        st.update(chunk=chunk, back=bf16v2.BF16v2().decompress(chunk))
 
-    ms, wall, clocks = _timed_steps(args, step)
-    h = st["dev"].cpu().numpy()
-    for k, (off, nb, _, _) in enumerate(layout["t"]):
-        assert np.array_equal(h[st["outs"][k]:st["outs"][k] + nb], data[off:off + nb]), "round trip failed"
-    coded = len(st["parts"]["stream"])
-    n = len(data)
+    for _ in range(max(args.warmup, 1)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    _lib.timing_start(calls=True)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    torch.cuda.synchronize()
+    wall = (time.perf_counter() - t0) / args.steps
+    ms = {k[3:]: v / args.steps for k, v in _lib.timing_stop().items()}
+    clocks = sampler.summary()
+    assert np.array_equal(np.asarray(st["back"]), np.frombuffer(data, np.uint8)), "round trip failed"
+    coded = len(codecs_gguf.unpack(st["chunk"])["stream"])
     algo = {"r2_stats": 3 * n, "row_hash": n, "r2_hist": n, "r2_encode": n + coded, "scan_gather": 2 * coded, "r2_decode": coded + n}
-    table = {k: {"ms": round(v, 3), "algo_gbs": round(algo[k] / (v * 1e-3) / 1e9, 1)} for k, v in ms.items()}
-    dom = max(ms, key=ms.get)
+    table = {k: {"ms": round(v, 3), "algo_gbs": round(algo[k] / (v * 1e-3) / 1e9, 1) if k in algo else None} for k, v in ms.items()}
+    dom = max((k for k in ms if k in algo), key=ms.get)
     line = _codec_line(args, "R2 BF16 base codec GB/s of BF16 bytes, statistics + row hashes + histogram + encode + gather + decode",
-                       f"{K} BF16 tensors of {NROWS}x{NPR} of one role ({n} bytes), coded to {coded} stream bytes",
+                       f"a GGUF file of {K} BF16 tensors of {NROWS}x{NPR} of one role ({n} bytes), coded to {coded} stream bytes",
                        n, sum(ms.values()), wall, n + coded, coded + n, table, {"kernel": dom, "achieved": algo[dom] / (ms[dom] * 1e-3) / 1e9},
                        {"value": None, "unit": "GB/s", "cores": 0, "kind": "port",
                         "sample": "no CPU restatement of the R2 codec is kept; parity is pinned on the reference's own coded parts"},

@@ -97,6 +97,8 @@ def seg_blocks(T):
 
 
 def _layout(T, nblocks):
+    """tensors' block counts -> (TM rows without the seed fields, SG array, total blocks); copied from the reference
+    (seedpack/qr.py:957-968): the segmentation is part of the format"""
     sb = seg_blocks(T)
     tm = np.zeros(len(nblocks), TM_DT)
     segs, b0 = [], 0
@@ -110,7 +112,8 @@ def _layout(T, nblocks):
 
 
 def batches(T, sizes):
-    """tensor indices split into coding batches of about BATCH bytes (same split on both sides)"""
+    """tensor indices split into coding batches of about BATCH bytes (same split on both sides); copied from the
+    reference (seedpack/qr.py:971-980): the split is part of the format"""
     out, cur, n = [], [], 0
     for i, s in enumerate(sizes):
         if cur and n + s > BATCH:

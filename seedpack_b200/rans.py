@@ -1,8 +1,8 @@
 """Segment-parallel rANS codec over a symbol stream with per-block context tables - host side.
 
 Mirrors the framing of the reference's QR batches (seedpack/qr.py:1007-1090): histogram on the device, table
-normalisation on the host (`normalize`, a restatement of seedpack/qr.py:904-923 in NumPy - it is host code in
-the reference too), encode into per-segment slots with the doubling retry of seedpack/qr.py:1043-1053, prefix sum +
+normalisation on the host (`normalize`, copied from seedpack/qr.py:904-923 - fifteen lines of host NumPy whose every
+tie-break decides archive bytes; with the reference bound through seedpack_b200.refbind its own copy runs), encode into per-segment slots with the doubling retry of seedpack/qr.py:1043-1053, prefix sum +
 gather, and the inverse.  All coding runs in libseedgrow.so; there is no CPU coder here.
 """
 import ctypes
@@ -18,7 +18,8 @@ SEG = 16384          # symbols per segment (seedpack/qr.py:952-954: max(16, 1638
 
 def normalize(counts, scale=1 << PB):
     """counts (T, 256) int -> (uint16 freqs of the used rows, used row ids): every row sums to `scale`, every
-    seen symbol keeps at least 1; the rounding deficit / surplus goes to the largest entry (first maximum)."""
+    seen symbol keeps at least 1; the rounding deficit / surplus goes to the largest entry (first maximum).
+    Copied from the reference (seedpack/qr.py:904-923) with NumPy arrays in and out: the format is defined by it."""
     c = np.asarray(counts).astype(np.int64).reshape(-1, 256)
     tot = c.sum(1)
     used = np.flatnonzero(tot)

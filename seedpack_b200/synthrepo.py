@@ -155,7 +155,7 @@ def _kv(key, vtype, value):
 
 
 def write_gguf(path, meta, tensors):
-    """meta: [(key, gguf value type, value)]; tensors: [(name, dims in ggml order, ggml type, nbytes, payload())];
+    """path: a file name or a writable binary file object.  meta: [(key, gguf value type, value)]; tensors: [(name, dims in ggml order, ggml type, nbytes, payload())];
     payload() -> the tensor's bytes (called in order while the file is written, so only one is held at a time)"""
     head = bytearray(b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(meta)))
     for k, t, v in meta:
@@ -167,7 +167,8 @@ def write_gguf(path, meta, tensors):
         head += struct.pack(f"<{len(dims)}Q", *dims) + struct.pack("<IQ", ty, off)
         off += -(-nb // ALIGN) * ALIGN
     head += bytes(-len(head) % ALIGN)
-    with open(path, "wb") as f:
+    import contextlib
+    with (open(path, "wb") if isinstance(path, str) else contextlib.nullcontext(path)) as f:
         f.write(head)
         for name, dims, ty, nb, payload in tensors:
             b = payload()
@@ -176,6 +177,14 @@ def write_gguf(path, meta, tensors):
                 raise ValueError(f"{name}: {len(b)} bytes for a tensor of {nb}")
             f.write(b)
             f.write(bytes(-nb % ALIGN))
+
+
+def gguf_bytes(meta, tensors):
+    """write_gguf into memory -> bytes"""
+    import io
+    f = io.BytesIO()
+    write_gguf(f, meta, tensors)
+    return f.getvalue()
 
 
 def _flip(seed, key, q, bs, share):

@@ -76,19 +76,23 @@ def test_qr_round_trip_at_full_size(tensor, T):
 
 
 def test_r2_round_trip_and_grouping_at_full_size(tensor):
-    """the R2 parts of the full tensor decode to its bytes, and do not depend on the group size"""
-    from seedpack_b200.bf16v2 import BF16v2, R2Tensors, layout_of
+    """the R2 coding of a file holding the full tensor (as two tensors of one role) decodes to its bytes, and does not
+    depend on the group size; the reference's BF16v2 class over the bound kernels"""
+    from seedpack_b200 import refbind, synthrepo
+    if not refbind.available():
+        pytest.fail("the reference package is not here (baseline/_ref or $SEEDPACK_REFERENCE)")
+    refbind.install()
+    from seedpack import bf16v2, codecs_gguf
     bits, _, _ = tensor
-    data = bits.view(np.uint8).reshape(-1)
-    half = len(data) // 2
-    layout = layout_of([("blk.0.ffn_up.weight", 0, half, NPR), ("blk.1.ffn_up.weight", half, half, NPR)], len(data))
-    parts = BF16v2().compress_parts(data, layout)
-    small = BF16v2(group_bytes=half).compress_parts(data, layout)
-    assert parts["stream"] == small["stream"] and parts["tables"] == small["tables"] and parts["side"] == small["side"]
-    dev, outs = R2Tensors(parts).decode(range(2))
-    h = dev.cpu().numpy()
-    for k, (off, nb, _, _) in enumerate(layout["t"]):
-        assert np.array_equal(h[outs[k]:outs[k] + nb], data[off:off + nb])
+    half = NROWS // 2
+    data = synthrepo.gguf_bytes([("general.alignment", 4, 32)],
+                                [(f"blk.{k}.ffn_up.weight", (NPR, half), 30, half * NPR * 2, (lambda k=k: bits[k * half:(k + 1) * half])) for k in range(2)])
+    parts = codecs_gguf.unpack(b"".join(bytes(p) for p in bf16v2.BF16v2().compress_parts(data)))
+    small = codecs_gguf.unpack(b"".join(bytes(p) for p in bf16v2.BF16v2(group_bytes=half * NPR * 2).compress_parts(data)))
+    for k in ("stream", "tables", "side"):
+        assert bytes(parts[k]) == bytes(small[k]), k
+    back = bf16v2.BF16v2().decompress(codecs_gguf.pack({k: bytes(v) for k, v in parts.items()}))
+    assert np.array_equal(np.asarray(back), np.frombuffer(data, np.uint8))
 
 
 def test_rans_round_trip_on_a_large_stream():

@@ -8,10 +8,36 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def test_normalize_gpu_matches_reference_tables():
-    from seedpack_b200.bf16v2 import normalize_gpu
+    """the reference's own gpu2.normalize_gpu, run over the binding's array module (host-resident arrays: NumPy arithmetic,
+    stable sorts; no device is touched), gives the tables its --cpu run stored"""
+    import subprocess
+    import sys
+    from seedpack_b200 import refbind
     from seedpack_b200.qr import load_tables
+    ref = refbind.find_reference()
+    if ref is None:
+        import pytest
+        pytest.skip("needs the reference package (baseline/_ref or $SEEDPACK_REFERENCE)")
+    code = (
+        "import sys, importlib.util, numpy as np\n"
+        f"sys.path[:0] = [{os.path.dirname(HERE)!r}, {ref!r}]\n"
+        "from seedpack_b200.refbind import cupy_shim as cp\n"
+        "sys.modules['cupy'], sys.modules['cupyx'] = cp, cp.cupyx\n"
+        "if importlib.util.find_spec('zstandard') is None:\n"
+        "    from seedpack_b200 import zstd; sys.modules['zstandard'] = zstd\n"
+        "from seedpack import gpu2\n"
+        f"G = np.load({os.path.join(HERE, 'golden', 'r2_golden.npz')!r})\n"
+        "f, u = gpu2.normalize_gpu(cp._wrap(np.ascontiguousarray(G['counts'])), 1 << 15)\n"
+        "np.save(sys.argv[1], f.get()); np.save(sys.argv[2], u.get())\n"
+        "assert cp.STATS['h2d'] == 0 and cp.STATS['d2h'] == 0\n")
+    import tempfile
+    with tempfile.TemporaryDirectory() as tmp:
+        a, b = os.path.join(tmp, "f.npy"), os.path.join(tmp, "u.npy")
+        env = {k: v for k, v in os.environ.items() if k != "SEEDPACK_CPU"}
+        r = subprocess.run([sys.executable, "-c", code, a, b], capture_output=True, text=True, env=env, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        freq, used = np.load(a), np.load(b)
     G = np.load(os.path.join(HERE, "golden", "r2_golden.npz"))
-    freq, used = normalize_gpu(G["counts"], 1 << 15)
     wf, wu = load_tables(G["part_tables"].tobytes(), 15)
     assert np.array_equal(used, wu) and np.array_equal(freq, wf)
     assert (freq.astype(np.int64).sum(1) == 1 << 15).all()

@@ -1,6 +1,9 @@
-"""R2 BF16 base codec and detmath through the C ABI against parts coded by the reference's own BF16v2.compress
-(tests/golden/r2_golden.npz, written by tests/golden/make_r2_golden.py): side information, tables, segment lengths and
-stream must be byte-identical; decoding the reference's parts must restore every tensor."""
+"""R2 BF16 base codec and detmath on the GPU against parts coded by the reference's own BF16v2.compress
+(tests/golden/r2_golden.npz, written by tests/golden/make_r2_golden.py).  The host side IS the reference's: its
+BF16v2 / R2Tensors classes (seedpack/bf16v2.py:174-617) run unmodified over seedpack_b200.refbind, so what is compared
+is the reference's framing around this library's kernels (sg_r2_stats, sg_row_hash, sg_r2_hist / encode / decode,
+sg_scan_gather, sg_rans_tables): every part of the coded file must be byte-identical, and decoding the reference's
+parts must restore every tensor."""
 import json
 import os
 
@@ -15,47 +18,58 @@ def _parts():
     return {k[5:]: G[k].tobytes() for k in G.files if k.startswith("part_")}
 
 
-def _layout():
-    from seedpack_b200 import zstd
-    return json.loads(zstd.decompress(_parts()["meta"], 1 << 20))
+@pytest.fixture(scope="module")
+def ref():
+    from seedpack_b200 import refbind
+    if not refbind.available():
+        pytest.fail("the reference package is not here (baseline/_ref or $SEEDPACK_REFERENCE)")
+    refbind.install()
+    from seedpack import bf16v2, codecs_gguf
+    return bf16v2, codecs_gguf
 
 
-def test_compress_parts_are_byte_identical_to_reference():
-    from seedpack_b200 import zstd
-    from seedpack_b200.bf16v2 import BF16v2
-    meta = _layout()
-    got = BF16v2(group_bytes=150_000).compress_parts(G["data"], meta["layout"])
+def _compress(ref, group_bytes):
+    bf16v2, codecs_gguf = ref
+    parts = bf16v2.BF16v2(group_bytes=group_bytes).compress_parts(G["data"].tobytes())
+    return {k: bytes(v) for k, v in codecs_gguf.unpack(b"".join(bytes(p) for p in parts)).items()}
+
+
+def test_compress_parts_are_byte_identical_to_reference(ref):
+    got, want = _compress(ref, 150_000), _parts()
+    for k in ("meta", "side", "tables", "lens", "stream"):
+        assert got[k] == want[k], k
+    assert set(got) == set(want) | {"rest"}
+
+
+def test_decode_of_reference_parts_restores_tensors(ref):
+    bf16v2, _ = ref
     want = _parts()
-    gm = json.loads(zstd.decompress(got["meta"], 1 << 20))
-    assert gm == meta                                            # layout, duplicate rows, compact row counts
-    for k in ("side", "tables", "lens"):
-        assert zstd.decompress(got[k], 1 << 30) == zstd.decompress(want[k], 1 << 30), k
-    assert got["stream"] == want["stream"]
-    for k in ("meta", "side", "tables", "lens"):
-        assert got[k] == want[k], f"{k}: same content but different zstd framing"
+    got = _compress(ref, 150_000)                                  # (the golden file keeps no `rest` part: ours is the same function's)
+    parts = dict(want, rest=got["rest"])
+    stream = np.frombuffer(parts["stream"], np.uint8)
 
+    def read(o, n, out):
+        np.frombuffer(out, np.uint8)[:n] = stream[o:o + n]
+        return out
 
-def test_decode_of_reference_parts_restores_tensors():
-    from seedpack_b200.bf16v2 import R2Tensors
-    r = R2Tensors(_parts())
+    r = bf16v2.R2Tensors(lambda name: parts[name], read)
     t = r.layout["t"]
     dev, outs = r.decode(range(len(t)))
-    h = dev.cpu().numpy()
+    h = dev.get()
     for k, (off, nb, rl, _) in enumerate(t):
         assert np.array_equal(h[outs[k]:outs[k] + nb], G["data"][off:off + nb]), k
     dev, outs = r.decode([3, 0])                                  # random access, any order
-    h = dev.cpu().numpy()
+    h = dev.get()
     for k, i in enumerate([3, 0]):
         off, nb = t[i][0], t[i][1]
         assert np.array_equal(h[outs[k]:outs[k] + nb], G["data"][off:off + nb])
+    whole = bf16v2.BF16v2().decompress(ref[1].pack(parts))
+    assert np.array_equal(np.asarray(whole), G["data"])
 
 
-def test_group_size_does_not_change_the_bytes_of_the_tables():
+def test_group_size_does_not_change_the_bytes_of_the_tables(ref):
     """the group split changes the stream's grouping only: counts (hence tables) are sums over the whole file"""
-    from seedpack_b200.bf16v2 import BF16v2
-    meta = _layout()
-    a = BF16v2(group_bytes=150_000).compress_parts(G["data"], meta["layout"])
-    b = BF16v2(group_bytes=1 << 30).compress_parts(G["data"], meta["layout"])
+    a, b = _compress(ref, 150_000), _compress(ref, 1 << 30)
     assert a["tables"] == b["tables"] and a["side"] == b["side"] and a["stream"] == b["stream"]
 
 
