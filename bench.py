@@ -750,15 +750,20 @@ def _timed_steps(args, fn):
     for _ in range(max(args.warmup, 1)):
         fn()
     torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    fn()
+    torch.cuda.synchronize()
+    one = max(time.perf_counter() - t0, 1e-4)
+    steps = max(args.steps, int(1.0 / one) + 1)       # at least a second under load: the clock sampler must see it
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
     _lib.timing_start()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         fn()
     torch.cuda.synchronize()
-    wall = (time.perf_counter() - t0) / args.steps
-    ms = {k: v / args.steps for k, v in _lib.timing_stop().items()}
+    wall = (time.perf_counter() - t0) / steps
+    ms = {k: v / steps for k, v in _lib.timing_stop().items()}
     return ms, wall, sampler.summary()
 
 

@@ -172,7 +172,9 @@ SG_API int sg_residual_blocks(int device, void *stream, const void *file, const 
  *                 copied to dst + off[s]; an overflowed segment sets SG_ST_OVERFLOW      (cumsum + gather, qr.py:1054-1056, 880-887)
  * sg_rans_decode  inverse of encode; reads of segment s stay inside [off[s], off[s+1]) and a segment that does
  *                 not end in the initial state sets SG_ST_CORRUPT (the reference reads unchecked, qr.py:662).
- *                 `in` must be 16-byte aligned and readable up to the next multiple of 16 past off[nseg]. */
+ *                 `in` must be 16-byte aligned and readable up to the next multiple of 16 past off[nseg].
+ *                 ntab = number of tables in enc_tab / lut: with it the decoder keeps symbol 0's frequencies and the
+ *                 other slots' entries in shared memory (0: not given, every symbol costs two dependent global loads). */
 SG_API int sg_rans_hist(int device, void *stream, const unsigned char *sym, const unsigned short *block_tab,
                         int block_len, long long nsym, unsigned *counts);
 SG_API int sg_rans_tables(int device, void *stream, const unsigned short *freq, int ntab, int pb, void *enc_tab,
@@ -184,7 +186,7 @@ SG_API int sg_scan_gather(int device, void *stream, const unsigned char *slots, 
                           int nseg, unsigned char *dst, unsigned long long dst_cap, unsigned long long *off);
 SG_API int sg_rans_decode(int device, void *stream, const unsigned char *in, const unsigned long long *off,
                           const unsigned short *block_tab, int block_len, long long nsym, int seg_len, int pb,
-                          const void *enc_tab, const unsigned char *lut, unsigned char *sym_out);
+                          const void *enc_tab, const unsigned char *lut, int ntab, unsigned char *sym_out);
 
 /* ---- QR: quantiser-aware residual coder ---------------------------------------------------------------
  * Replaces qr_hist / qr_enc / qr_dec (seedpack/qr.py:674-807) for the scalar-code types (2 3 6 7 8 10 11 12 13 14
@@ -259,6 +261,32 @@ SG_API int sg_dm_exp2(int device, void *stream, const double *x, long long n, do
 SG_API int sg_dm_rows(int device, void *stream, const float *x, long long nr, long long nc, int square, double *out);
 SG_API int sg_dm_cols(int device, void *stream, const float *x, long long nr, long long nc, int square,
                       const unsigned char *mask, double *out);
+
+/* ---- M24: the earlier BF16 base codec (archives packed with --method m28) ---------------------------------------------
+ * Replaces bf_hist / bf_enc / bf_dec (seedpack/gpu_bf16.py:63-137): 12 probability bits, 160 tables per tensor (128
+ * exponent, 16 mantissa, 16 sign), quarter-octave side information.  file = the whole GGUF on the device; records
+ *   TB { int64 off; int32 rowlen, rowbase, colbase, tab }   (gpu_bf16.py:283), SG { int32 t, n; int64 i0 }   (:284).
+ * counts / enc_tab / lut cover ntensors * 160 tables addressed by raw id (sg_rans_tables with pb = 12); slots, out_len,
+ * in_off / in_end as for the R2 entry points. */
+SG_API int sg_m24_hist(int device, void *stream, const unsigned char *file, const void *tb, const void *sg, int nseg,
+                       const short *rfi, const short *cfi, const signed char *scl, unsigned *counts);
+SG_API int sg_m24_encode(int device, void *stream, const unsigned char *file, const void *tb, const void *sg, int nseg,
+                         const short *rfi, const short *cfi, const signed char *scl, const void *enc_tab,
+                         unsigned char *slots, size_t cap, unsigned *out_len);
+SG_API int sg_m24_decode(int device, void *stream, const unsigned char *in, const unsigned long long *in_off,
+                         const unsigned long long *in_end, unsigned char *file, const void *tb, const void *sg, int nseg,
+                         const short *rfi, const short *cfi, const signed char *scl, const void *enc_tab,
+                         const unsigned char *lut);
+
+/* The remaining detmath kernels (seedpack/detmath.py:86-93, 109-153: dm_rows_d, dm_gram, dm_bdot, dm_solve), which the
+ * importance fit uses (seedpack/imxfit.py:36-75): sums (of squares) along the rows of a float64 matrix; batched
+ * X[c] X[c]^T (X: nb x k x d float32 -> nb x k x k float32) and X[c] y[c] (-> nb x k) with float64 sums in index order;
+ * batched systems A[c] x = b[c] with k <= 16 unknowns (SG_ERR_LIMIT beyond) by Gaussian elimination with partial
+ * pivoting in float64. */
+SG_API int sg_dm_rows_f64(int device, void *stream, const double *x, long long nr, long long nc, int square, double *out);
+SG_API int sg_dm_gram(int device, void *stream, const float *X, long long nb, int k, long long d, float *out);
+SG_API int sg_dm_bdot(int device, void *stream, const float *X, const float *y, long long nb, int k, long long d, float *out);
+SG_API int sg_dm_solve(int device, void *stream, const float *A, const float *b, long long nb, int k, float *x);
 
 /* Diagnostic: out[i] = nearest_int(x[i]), the magic-number rounding every quantiser uses (ggml-quants.c:621-626), so that
  * the device form can be swept over its whole input range on its own (tests/test_helpers_gpu.py).  The conversions

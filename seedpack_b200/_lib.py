@@ -48,7 +48,7 @@ SIGNATURES = {
     "sg_rans_tables": (_I, [_I, _P, _P, _I, _I, _P, _P]),
     "sg_rans_encode": (_I, [_I, _P, _P, _P, _I, _L, _I, _I, _P, _P, _Z, _P]),
     "sg_scan_gather": (_I, [_I, _P, _P, _Z, _P, _I, _P, ctypes.c_uint64, _P]),
-    "sg_rans_decode": (_I, [_I, _P, _P, _P, _P, _I, _L, _I, _I, _P, _P, _P]),
+    "sg_rans_decode": (_I, [_I, _P, _P, _P, _P, _I, _L, _I, _I, _P, _P, _I, _P]),
     "sg_qr_hist": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I]),
     "sg_qr_encode": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _Z, _P, _I]),
     "sg_qr_decode": (_I, [_I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I]),
@@ -67,6 +67,13 @@ SIGNATURES = {
     "sg_dm_exp2": (_I, [_I, _P, _P, _L, _P]),
     "sg_dm_rows": (_I, [_I, _P, _P, _L, _L, _I, _P]),
     "sg_dm_cols": (_I, [_I, _P, _P, _L, _L, _I, _P, _P]),
+    "sg_m24_hist": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P]),
+    "sg_m24_encode": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _Z, _P]),
+    "sg_m24_decode": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P]),
+    "sg_dm_rows_f64": (_I, [_I, _P, _P, _L, _L, _I, _P]),
+    "sg_dm_gram": (_I, [_I, _P, _P, _L, _I, _L, _P]),
+    "sg_dm_bdot": (_I, [_I, _P, _P, _P, _L, _I, _L, _P]),
+    "sg_dm_solve": (_I, [_I, _P, _P, _P, _L, _I, _P]),
     "sg_selftest_nearest_int": (_I, [_I, _P, _P, _P, _L]),
     "sg_quantize_legacy_imx_static": (_I, [_I, _P, _I, _P, _I, _P, _P, ctypes.POINTER(sg_tensor), _I]),
 }

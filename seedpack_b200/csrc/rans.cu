@@ -88,18 +88,27 @@ __global__ void __launch_bounds__(64) k_rans_encode(const uint8_t* __restrict__ 
     ByteWriterDown w;
     w.init(slot + cap);
     unsigned x = RANS_L;
-    const RansSym* tab = nullptr;
-    long long cur_block = -1;
+    // Neither the symbols nor their table entries depend on the coder's state: the next 16 symbols and their table are
+    // fetched while the current 16 are coded, and a group's 16 entries are loaded before the chain of coding steps
+    // through x starts.
+    long long cur_block = n > 0 ? (s0 + n - 16) / block_len : 0;        // 16 | block_len: one table per 16 symbols
+    const RansSym* tab = n > 0 ? enc + (size_t)block_tab[cur_block] * 256 : enc;
+    uint4 v = n > 0 ? __ldg(reinterpret_cast<const uint4*>(sym + s0 + n - 16)) : make_uint4(0, 0, 0, 0);
     for (long long i = n - 16; i >= 0; i -= 16) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(sym + s0 + i));
         const unsigned wv[4] = {v.x, v.y, v.z, v.w};
-        const long long blk = (s0 + i) / block_len;                     // 16 | block_len: one table per 16 symbols
-        if (blk != cur_block) { cur_block = blk; tab = enc + (size_t)block_tab[blk] * 256; }
+        RansSym e[16];
 #pragma unroll
-        for (int k = 3; k >= 0; --k) {
+        for (int k = 0; k < 4; ++k) {
 #pragma unroll
-            for (int j = 3; j >= 0; --j) rans_put<PB>(x, w, tab[(wv[k] >> (8 * j)) & 0xff]);
+            for (int j = 0; j < 4; ++j) e[4 * k + j] = tab[(wv[k] >> (8 * j)) & 0xff];
         }
+        if (i >= 16) {
+            v = __ldg(reinterpret_cast<const uint4*>(sym + s0 + i - 16));
+            const long long blk = (s0 + i - 16) / block_len;
+            if (blk != cur_block) { cur_block = blk; tab = enc + (size_t)block_tab[blk] * 256; }
+        }
+#pragma unroll
+        for (int q = 15; q >= 0; --q) rans_put<PB>(x, w, e[q]);
         if (w.ptr() < slot + 64) { out_len[s] = 0xffffffffu; return; }   // 16 symbols write at most 32 bytes
     }
     rans_flush(x, w);
@@ -181,6 +190,91 @@ __global__ void __launch_bounds__(64) k_rans_decode(const uint8_t* __restrict__ 
     if (x != RANS_L || r.p != r.end) atomicOr(status, SG_ST_CORRUPT);     // a well-formed segment ends in the initial state
 }
 
+// The same decoder with the tables it needs in shared memory.  A residual stream is mostly the symbol 0, whose slots are
+// [0, freq(0)) of every table: for those the step is x = freq(0) (x >> PB) + slot with freq(0) from a small array in
+// shared memory.  The other slots of a table - [freq(0), 2^PB), few when zeros dominate - get one 4-byte entry each,
+// symbol | (freq - 1) << 8 | (slot - cum) << 20, also in shared memory as far as they fit (tables in id order; the rest
+// keep the two dependent global loads lut[slot] -> enc[symbol]).  Every CTA builds the entries from enc / lut itself
+// (a few per cent of its decoding time): the caller passes no further buffer.  One CTA of 512 lanes per SM.
+constexpr unsigned NOFIT = 0xffffffffu;
+template <int PB>
+__global__ void __launch_bounds__(512, 1) k_rans_decode_sm(const uint8_t* __restrict__ in, const unsigned long long* __restrict__ off,
+                                                           const uint16_t* __restrict__ block_tab, int block_len, long long nsym, int seg_len,
+                                                           const RansSym* __restrict__ enc, const uint8_t* __restrict__ lut,
+                                                           uint8_t* __restrict__ sym, int nseg, int ntab, unsigned cap, int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned smem[];
+    unsigned* base = smem;                                   // [ntab] first entry of the table, NOFIT if not staged
+    unsigned* ent = smem + ntab;                             // [cap]
+    unsigned short* f0 = reinterpret_cast<unsigned short*>(ent + cap);     // [ntab] freq(0)
+    constexpr unsigned SLOTS = 1u << PB;
+    for (int t = threadIdx.x; t < ntab; t += blockDim.x) {
+        const unsigned first = enc[(size_t)t * 256].fc & 0xffffu, last = enc[(size_t)t * 256 + 255].fc;
+        const bool used = (last >> 16) + (last & 0xffffu) == SLOTS;
+        f0[t] = (unsigned short)(used ? first : 0);
+        base[t] = used ? SLOTS - first : 0;                  // for now: the number of entries the table needs
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned run = 0;
+        for (int t = 0; t < ntab; ++t) {
+            const unsigned n = base[t];
+            if (n == 0 && f0[t] == 0) { base[t] = NOFIT; continue; }           // an unused table
+            if (run + n <= cap) { base[t] = run; run += n; } else base[t] = NOFIT;
+        }
+    }
+    __syncthreads();
+    for (int t = threadIdx.x >> 5; t < ntab; t += blockDim.x >> 5) {
+        const unsigned b = base[t];
+        if (b == NOFIT) continue;
+        const unsigned f = f0[t];
+        for (unsigned slot = f + (threadIdx.x & 31); slot < SLOTS; slot += 32) {
+            const unsigned s = lut[((size_t)t << PB) + slot];
+            const unsigned fc = enc[(size_t)t * 256 + s].fc;
+            ent[b + slot - f] = s | (((fc & 0xffffu) - 1u) << 8) | ((slot - (fc >> 16)) << 20);
+        }
+    }
+    __syncthreads();
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= nseg) return;
+    const long long s0 = (long long)s * seg_len;
+    const long long n = min((long long)seg_len, nsym - s0);
+    ByteReaderUp r;
+    r.init(in + off[s], in + off[s + 1]);
+    unsigned x = rans_init(r);
+    unsigned tf0 = 0, tb = NOFIT, tid = 0;
+    long long cur_block = -1;
+    for (long long i = 0; i < n; i += 16) {
+        const long long blk = (s0 + i) / block_len;
+        if (blk != cur_block) { cur_block = blk; tid = block_tab[blk]; tf0 = f0[tid]; tb = base[tid]; }
+        unsigned wv[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            unsigned word = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const unsigned slot = x & (SLOTS - 1);
+                unsigned sy = 0;
+                if (slot < tf0) x = tf0 * (x >> PB) + slot;
+                else if (tb != NOFIT) {
+                    const unsigned e = ent[tb + slot - tf0];
+                    sy = e & 0xffu;
+                    x = (((e >> 8) & 0xfffu) + 1u) * (x >> PB) + (e >> 20);
+                } else {
+                    sy = lut[((size_t)tid << PB) + slot];
+                    const unsigned fc = enc[(size_t)tid * 256 + sy].fc;
+                    x = (fc & 0xffffu) * (x >> PB) + slot - (fc >> 16);
+                }
+                if (x < RANS_L) { x = (x << 8) | r.get(); if (x < RANS_L) x = (x << 8) | r.get(); }
+                word |= sy << (8 * j);
+            }
+            wv[k] = word;
+        }
+        *reinterpret_cast<uint4*>(sym + s0 + i) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+        if (r.over) { atomicOr(status, SG_ST_CORRUPT); return; }
+    }
+    if (x != RANS_L || r.p != r.end) atomicOr(status, SG_ST_CORRUPT);     // a well-formed segment ends in the initial state
+}
+
 }  // namespace sg
 
 using namespace sg;
@@ -248,8 +342,8 @@ extern "C" int sg_scan_gather(int device, void* stream, const unsigned char* slo
 
 extern "C" int sg_rans_decode(int device, void* stream, const unsigned char* in, const unsigned long long* off,
                               const unsigned short* block_tab, int block_len, long long nsym, int seg_len, int pb,
-                              const void* enc_tab, const unsigned char* lut, unsigned char* sym_out) {
-    if (!in || !off || !enc_tab || !lut || pb != 12) return SG_ERR_ARG;
+                              const void* enc_tab, const unsigned char* lut, int ntab, unsigned char* sym_out) {
+    if (!in || !off || !enc_tab || !lut || pb != 12 || ntab < 0) return SG_ERR_ARG;
     int rc = stream_args_ok(sym_out, block_tab, block_len, nsym, seg_len);
     if (rc != SG_OK) return rc;
     if ((uintptr_t)in % 16) return SG_ERR_ALIGN;
@@ -258,8 +352,24 @@ extern "C" int sg_rans_decode(int device, void* stream, const unsigned char* in,
     if (rc != SG_OK) return rc;
     const long long nseg = (nsym + seg_len - 1) / seg_len;
     if (nseg > 0x7fffffffLL) return SG_ERR_LIMIT;
-    k_rans_decode<12><<<(unsigned)((nseg + 63) / 64), 64, 0, (cudaStream_t)stream>>>(in, off, block_tab, block_len, nsym, seg_len,
-                                                                                     (const RansSym*)enc_tab, lut, sym_out, (int)nseg,
-                                                                                     status_word(device));
+    cudaStream_t st = (cudaStream_t)stream;
+    // tables staged in shared memory when their number is given and small enough to leave room for entries
+    const size_t smem_max = 200 * 1024;
+    if (ntab > 0 && (size_t)ntab * 6 + 8192 <= smem_max) {
+        const unsigned cap = (unsigned)((smem_max - (size_t)ntab * 6 - 16) / 4);
+        const size_t smem = (size_t)ntab * 4 + (size_t)cap * 4 + (size_t)ntab * 2 + 16;
+        static bool configured[64] = {false};
+        if (device < 64 && !configured[device]) {
+            rc = cuda_ok(cudaFuncSetAttribute(k_rans_decode_sm<12>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max + 1024));
+            if (rc != SG_OK) return rc;
+            configured[device] = true;
+        }
+        k_rans_decode_sm<12><<<(unsigned)((nseg + 511) / 512), 512, smem, st>>>(in, off, block_tab, block_len, nsym, seg_len,
+                                                                            (const RansSym*)enc_tab, lut, sym_out, (int)nseg, ntab, cap,
+                                                                            status_word(device));
+        return cuda_ok(cudaGetLastError());
+    }
+    k_rans_decode<12><<<(unsigned)((nseg + 63) / 64), 64, 0, st>>>(in, off, block_tab, block_len, nsym, seg_len,
+                                                                  (const RansSym*)enc_tab, lut, sym_out, (int)nseg, status_word(device));
     return cuda_ok(cudaGetLastError());
 }

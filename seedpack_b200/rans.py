@@ -119,5 +119,5 @@ class RansCodec:
         out = torch.empty(nsym, dtype=torch.uint8, device=self.device)
         with _lib.timed("rans_decode"):
             _lib.check(self.lib.sg_rans_decode(self.device.index, self._stream(), _p(stream), _p(off), _p(block_tab), block_len, nsym,
-                                               seg_len, PB, _p(enc), _p(lut), _p(out)), "sg_rans_decode")
+                                               seg_len, PB, _p(enc), _p(lut), ntab, _p(out)), "sg_rans_decode")
         return out

@@ -7,11 +7,13 @@ raises, so nothing of the reference's CUDA source can run by accident.
 
     reference kernel (file:line)                       C-ABI entry point
     v2_hist / v2_enc / v2_dec   bf16v2.py:63-137       sg_r2_hist / sg_r2_encode / sg_r2_decode
+    bf_hist / bf_enc / bf_dec   gpu_bf16.py:63-137     sg_m24_hist / sg_m24_encode / sg_m24_decode
     row_hash                    bf16v2.py:148-155      sg_row_hash
     build_lut                   bf16v2.py:139, qr.py:889   folded into the decoders' table preparation (sg_rans_tables)
     gather                      qr.py:880-887, gpu2.py     sg_scan_gather
     qr_hist / qr_enc / qr_dec   qr.py:674-807          sg_residual_blocks + sg_qr_hist / sg_qr_encode / sg_qr_decode
     dm_log2 / dm_exp2 / dm_rows / dm_cols   detmath.py:67-106   sg_dm_log2 / sg_dm_exp2 / sg_dm_rows / sg_dm_cols
+    dm_rows_d / dm_gram / dm_bdot / dm_solve  detmath.py:86-153  sg_dm_rows_f64 / sg_dm_gram / sg_dm_bdot / sg_dm_solve
     k_dq_<type>                 gpuquant.py:215-219    sg_dequantize
     vq_bf16_to_f32 (elementwise) gpuquant.py:248-249   sg_convert_float
 
@@ -116,6 +118,31 @@ def _v2_dec(args):
     _corrupt("R2")
 
 
+# ---- M24 ----------------------------------------------------------------------------------------------------------
+def _bf_hist(args):
+    dev, tb, sg, nseg, rfi, cfi, scl, counts = args
+    _lib.check(_lib.lib().sg_m24_hist(_dev(), _st(), _p(dev.dev_in()), _p(tb.dev_in()), _p(sg.dev_in()), _i(nseg), _p(rfi.dev_in()),
+                                      _p(cfi.dev_in()), _p(scl.dev_in()), _p(counts.dev_inout())), "sg_m24_hist")
+
+
+def _bf_enc(args):
+    dev, tb, sg, nseg, rfi, cfi, scl, remap, freq, cum, out, cap, out_len = args
+    enc, _ = _tables(remap, freq, QR_PB, False)
+    _lib.check(_lib.lib().sg_m24_encode(_dev(), _st(), _p(dev.dev_in()), _p(tb.dev_in()), _p(sg.dev_in()), _i(nseg), _p(rfi.dev_in()),
+                                        _p(cfi.dev_in()), _p(scl.dev_in()), _p(enc), _p(out.dev_out()), _i(cap), _p(out_len.dev_out())),
+               "sg_m24_encode")
+
+
+def _bf_dec(args):
+    stream, offs, dev, tb, sg, nseg, rfi, cfi, scl, remap, freq, cum, lut = args
+    enc, l = _tables(remap, freq, QR_PB, True)
+    o = offs.dev_in().view(torch.int64)
+    e = _seg_ends(o, stream.size)
+    _lib.check(_lib.lib().sg_m24_decode(_dev(), _st(), _p(stream.dev_in()), _p(o), _p(e), _p(dev.dev_inout()), _p(tb.dev_in()), _p(sg.dev_in()),
+                                        _i(nseg), _p(rfi.dev_in()), _p(cfi.dev_in()), _p(scl.dev_in()), _p(enc), _p(l)), "sg_m24_decode")
+    _corrupt("M24")
+
+
 def _corrupt(what):
     bits = ctypes.c_int(0)
     _lib.check(_lib.lib().sg_status_fetch(_dev(), _st(), ctypes.byref(bits)), "sg_status_fetch")
@@ -208,6 +235,26 @@ def _dm_cols(args):
                                      _p(out.dev_out())), "sg_dm_cols")
 
 
+def _dm_rows_d(args):
+    x, nr, nc, square, out = args
+    _lib.check(_lib.lib().sg_dm_rows_f64(_dev(), _st(), _p(x.dev_in()), _i(nr), _i(nc), _i(square), _p(out.dev_out())), "sg_dm_rows_f64")
+
+
+def _dm_gram(args):
+    X, nb, k, d, out = args
+    _lib.check(_lib.lib().sg_dm_gram(_dev(), _st(), _p(X.dev_in()), _i(nb), _i(k), _i(d), _p(out.dev_out())), "sg_dm_gram")
+
+
+def _dm_bdot(args):
+    X, y, nb, k, d, out = args
+    _lib.check(_lib.lib().sg_dm_bdot(_dev(), _st(), _p(X.dev_in()), _p(y.dev_in()), _i(nb), _i(k), _i(d), _p(out.dev_out())), "sg_dm_bdot")
+
+
+def _dm_solve(args):
+    A, b, nb, k, x = args
+    _lib.check(_lib.lib().sg_dm_solve(_dev(), _st(), _p(A.dev_in()), _p(b.dev_in()), _i(nb), _i(k), _p(x.dev_out())), "sg_dm_solve")
+
+
 # ---- dequantisers, float conversion ------------------------------------------------------------------------------------
 def _dequant(T):
     qk, bs = QFUN[T][1], QFUN[T][2]
@@ -230,9 +277,10 @@ def _bf16_to_f32(a, y=None):
     return y
 
 
-_BOUND = {"v2_hist": _v2_hist, "v2_enc": _v2_enc, "v2_dec": _v2_dec, "row_hash": _row_hash, "build_lut": _build_lut,
+_BOUND = {"bf_hist": _bf_hist, "bf_enc": _bf_enc, "bf_dec": _bf_dec, "v2_hist": _v2_hist, "v2_enc": _v2_enc, "v2_dec": _v2_dec, "row_hash": _row_hash, "build_lut": _build_lut,
           "gather": _gather, "qr_hist": _qr_hist, "qr_enc": _qr_enc, "qr_dec": _qr_dec,
-          "dm_log2": _dm_log2, "dm_exp2": _dm_exp2, "dm_rows": _dm_rows, "dm_cols": _dm_cols}
+          "dm_log2": _dm_log2, "dm_exp2": _dm_exp2, "dm_rows": _dm_rows, "dm_cols": _dm_cols, "dm_rows_d": _dm_rows_d,
+          "dm_gram": _dm_gram, "dm_bdot": _dm_bdot, "dm_solve": _dm_solve}
 for _t, (_name, _, _) in QFUN.items():
     _BOUND["k_dq_" + _name[len("quantize_"):]] = _dequant(_t)
 

@@ -57,6 +57,11 @@ CONFIGS = {
     # its reduction: 2 layers, hidden 512, FFN 1536, vocabulary 2048
     "c4-mini": dict(layers=2, hidden=512, ffn=1536, q_heads=4, kv_heads=2, head_dim=128, vocab=2048, tied=False,
                     imatrix=True, shards=1, flip=0.005, alter=0.0, files="imatrix21"),
+    # two legacy quants made with ANOTHER importance matrix than the one in the repository (their metadata names 45
+    # chunks, the repository's file 100): packing fits their importance back from the files (seedpack/imxfit.py)
+    "fit-mini": dict(layers=2, hidden=512, ffn=1536, q_heads=4, kv_heads=2, head_dim=128, vocab=2048, tied=False,
+                     imatrix=True, shards=1, flip=0.0, alter=0.0, files={"Q4_0": "q4_0", "Q5_1": "q5_1", "Q4_K_S": "q4_k_s"},
+                     other_imatrix=("Q4_0", "Q5_1")),
     # 27B shape in two shards (64 layers, hidden 5120, FFN 17408, 40 q / 8 kv heads of 128), 24 imatrix quants,
     # 2 % of the tensors quantised with another type than their file's map names
     "c5": dict(layers=64, hidden=5120, ffn=17408, q_heads=40, kv_heads=8, head_dim=128, vocab=151936, tied=False,
@@ -128,7 +133,10 @@ _draw_weights = weights
 
 
 def importance(seed, name, cols):
-    return np.exp(1.5 * _rng(seed, "imx:" + name).standard_normal(cols)).astype(np.float32)
+    """the repository's importance vector of a tensor; tensors fed by the same activations (q / k / v of a layer, gate /
+    up of a layer) get the same vector, as a calibration run gives them"""
+    shared = name.replace("attn_k", "attn_q").replace("attn_v", "attn_q").replace("ffn_up", "ffn_gate")
+    return np.exp(1.5 * _rng(seed, "imx:" + shared).standard_normal(cols)).astype(np.float32)
 
 
 def file_labels(cfg):
@@ -269,6 +277,11 @@ def make_repo(root, config, quantize, seed=0, name="synth", only=None, keep_weig
 
             def payload(n=n, s=s, ty=ty, bs=bs, lab=lab):
                 w = imx.get(n)
+                if w is not None and lab in cfg.get("other_imatrix", ()):
+                    # the unpublished matrix such a file was made with; tensors with the same input (q / k / v, gate / up)
+                    # share it, as a calibration run gives them the same activations
+                    shared = n.replace("attn_k", "attn_q").replace("attn_v", "attn_q").replace("ffn_up", "ffn_gate")
+                    w = (w * np.exp(0.7 * _rng(seed, "imx2:" + shared).standard_normal(len(w)))).astype(np.float32)
                 if w is None and ty in NEEDS_IMATRIX:
                     raise ValueError(f"{n}: type {ty} needs an importance matrix")
                 q = np.array(quantize(ty, weights(seed, n, s), w), np.uint8, copy=True).reshape(-1)
@@ -280,7 +293,7 @@ def make_repo(root, config, quantize, seed=0, name="synth", only=None, keep_weig
                 ("general.file_type", 4, 7), ("general.quantization_version", 4, 2)]
         if cfg["imatrix"]:
             meta += [("quantize.imatrix.file", 8, "imatrix_synth.dat"), ("quantize.imatrix.entries_count", 5, len(imx)),
-                     ("quantize.imatrix.chunks_count", 5, 100)]
+                     ("quantize.imatrix.chunks_count", 5, 45 if lab in cfg.get("other_imatrix", ()) else 100)]
         fp = os.path.join(root, f"{name}-{lab}.gguf")
         write_gguf(fp, meta, tens)
         out["files"][lab] = fp

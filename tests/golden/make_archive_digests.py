@@ -21,7 +21,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 OUT = os.path.join(HERE, "archive_digests.json")
-CONFIGS = ["c1-nano", "c1-mini", "c4-mini", "c5-mini"]
+CONFIGS = ["c1-nano", "c1-mini", "c4-mini", "c5-mini", "fit-mini", "c1-nano@m28"]     # "@m28": packed with --method m28 (M24 base codec)
 SEED = 1
 
 
@@ -41,11 +41,13 @@ def main(configs):
         with tempfile.TemporaryDirectory() as tmp:
             repo = os.path.join(tmp, "repo")
             t0 = time.time()
-            synthrepo.make_repo(repo, cfg, lambda ty, bits, w: ref.quantize(ty, ref.bf16_to_f32(bits), w), seed=SEED)
+            name, _, method = cfg.partition("@")
+            synthrepo.make_repo(repo, name, lambda ty, bits, w: ref.quantize(ty, ref.bf16_to_f32(bits), w), seed=SEED)
             t1 = time.time()
             arc = os.path.join(tmp, "a.seedpack")
             env = dict(os.environ, SOURCE_DATE_EPOCH="1700000000")
-            r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "tools", "refcli.py"), "cpu", "pack", "--cpu", "-q", "-o", arc, repo],
+            r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "tools", "refcli.py"), "cpu", "pack", "--cpu", "-q", "-o", arc, repo]
+                               + (["--method", method] if method else []),
                                cwd=tmp, env=env, capture_output=True, text=True)
             if r.returncode:
                 sys.exit(r.stdout + r.stderr)

@@ -9,7 +9,9 @@ seedpack_b200.refbind: $SEEDPACK_REFERENCE or baseline/_ref) run with every kern
     repositories regenerated with the CUDA quantisers have the same file digests, and the archive packed on the GPU has
     the same digest as the reference's `--cpu` archive - byte-identical archives for the 0.6B-shaped repository without
     importance matrix (three quant files), the 9B-shaped one with 21 importance-matrix quants and the 27B-shaped one
-    in two shards with 24 quants and altered tensor types, at reduced sizes;
+    in two shards with 24 quants and altered tensor types, at reduced sizes; a repository whose legacy quants were
+    made with another importance matrix than the published one (the packer fits it back: seedpack/imxfit.py over
+    sg_dm_gram and friends); and the smallest repository packed with --method m28 (the M24 base codec);
   * both ways on one box: the reference's `--cpu` run packs the smallest repository here too, the archives are
     compared byte for byte, and each side unpacks the OTHER side's archive to files equal to the originals;
   * `test` / `unpack` on the GPU restore every file of every archive (the reference's own BLAKE3 check plus a
@@ -81,7 +83,7 @@ def need_reference():
         pytest.fail("the reference package is not here (baseline/_ref or $SEEDPACK_REFERENCE): archives cannot be made")
 
 
-@pytest.mark.parametrize("config", ["c1-nano", "c1-mini", "c4-mini", "c5-mini"])
+@pytest.mark.parametrize("config", ["c1-nano", "c1-mini", "c4-mini", "c5-mini", "fit-mini", "c1-nano@m28"])
 def test_archive_equals_the_references(config, tmp_path):
     need_reference()
     from seedpack_b200 import synthrepo
@@ -89,13 +91,14 @@ def test_archive_equals_the_references(config, tmp_path):
         pytest.fail(f"no golden digests for {config}")
     gold = GOLD[config]
     repo = str(tmp_path / "repo")
-    synthrepo.make_repo(repo, config, gpu_quantizer(), seed=gold["seed"])
+    name, _, method = config.partition("@")                # "@m28": packed with --method m28 (the M24 base codec)
+    synthrepo.make_repo(repo, name, gpu_quantizer(), seed=gold["seed"])
     # the repository itself: every quant file written by the CUDA quantisers equals the one the reference's C code wrote
     assert sorted(os.listdir(repo)) == sorted(gold["files"])
     for n, (size, dg) in gold["files"].items():
         assert os.path.getsize(os.path.join(repo, n)) == size and digest(os.path.join(repo, n)) == dg, n
     arc = str(tmp_path / "gpu.seedpack")
-    bound("pack", "-q", "-o", arc, repo, cwd=tmp_path)
+    bound("pack", "-q", "-o", arc, repo, *(["--method", method] if method else []), cwd=tmp_path)
     assert [os.path.getsize(arc), digest(arc)] == gold["archive"]
     bound("test", arc, cwd=tmp_path)
     out = str(tmp_path / "out")
