@@ -88,27 +88,18 @@ __global__ void __launch_bounds__(64) k_rans_encode(const uint8_t* __restrict__ 
     ByteWriterDown w;
     w.init(slot + cap);
     unsigned x = RANS_L;
-    // Neither the symbols nor their table entries depend on the coder's state: the next 16 symbols and their table are
-    // fetched while the current 16 are coded, and a group's 16 entries are loaded before the chain of coding steps
-    // through x starts.
-    long long cur_block = n > 0 ? (s0 + n - 16) / block_len : 0;        // 16 | block_len: one table per 16 symbols
-    const RansSym* tab = n > 0 ? enc + (size_t)block_tab[cur_block] * 256 : enc;
-    uint4 v = n > 0 ? __ldg(reinterpret_cast<const uint4*>(sym + s0 + n - 16)) : make_uint4(0, 0, 0, 0);
+    const RansSym* tab = nullptr;
+    long long cur_block = -1;
     for (long long i = n - 16; i >= 0; i -= 16) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(sym + s0 + i));
         const unsigned wv[4] = {v.x, v.y, v.z, v.w};
-        RansSym e[16];
+        const long long blk = (s0 + i) / block_len;                     // 16 | block_len: one table per 16 symbols
+        if (blk != cur_block) { cur_block = blk; tab = enc + (size_t)block_tab[blk] * 256; }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 3; k >= 0; --k) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) e[4 * k + j] = tab[(wv[k] >> (8 * j)) & 0xff];
+            for (int j = 3; j >= 0; --j) rans_put<PB>(x, w, tab[(wv[k] >> (8 * j)) & 0xff]);
         }
-        if (i >= 16) {
-            v = __ldg(reinterpret_cast<const uint4*>(sym + s0 + i - 16));
-            const long long blk = (s0 + i - 16) / block_len;
-            if (blk != cur_block) { cur_block = blk; tab = enc + (size_t)block_tab[blk] * 256; }
-        }
-#pragma unroll
-        for (int q = 15; q >= 0; --q) rans_put<PB>(x, w, e[q]);
         if (w.ptr() < slot + 64) { out_len[s] = 0xffffffffu; return; }   // 16 symbols write at most 32 bytes
     }
     rans_flush(x, w);
