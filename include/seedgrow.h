@@ -197,7 +197,9 @@ SG_API int sg_rans_decode(int device, void *stream, const unsigned char *in, con
  *   tm / sg = per-tensor and per-segment records with the reference's layouts
  *     TM { int64 blk0, seed_off; int32 seed_type, cols; int64 imx_off }   (qr.py:898)
  *     SG { int32 t, nb; int64 b0 }                                        (qr.py:900)
- *   seed types: 30 BF16, 0 F32, 1 F16, 98 none (per-column RMS floats), 99 explicit (x, h) float pairs.
+ *   seed types: 30 BF16, 0 F32, 1 F16, 98 none (per-column RMS floats), 99 explicit (x, h) float pairs, or one of the
+ *   scalar-code quant types (the seed buffer then holds that type's blocks: value = dequantised weight, uncertainty =
+ *   half a code step; qr.py:331-344).
  * Context tables are addressed by their raw id (0..293, qr.py:50-53): counts is [294 * 256], enc_tab / lut come from
  * sg_rans_tables on the full 294-row frequency array (unused rows zero), pb = 12.  mv = model version (1 or 2,
  * qr.py:54).  Streams, slots, out_len and offsets are those of sg_rans_encode / sg_scan_gather / sg_rans_decode.
@@ -261,6 +263,19 @@ SG_API int sg_dm_exp2(int device, void *stream, const double *x, long long n, do
 SG_API int sg_dm_rows(int device, void *stream, const float *x, long long nr, long long nc, int square, double *out);
 SG_API int sg_dm_cols(int device, void *stream, const float *x, long long nr, long long nc, int square,
                       const unsigned char *mask, double *out);
+
+/* Helpers of the QR coder for tensors coded without a BF16 seed (seedpack/qr.py:811-878: block_fields,
+ * blocks_from_fields, intervals, weq, grid_h): the blocks' scale fields as integers (nfield(T) per block, the same
+ * field vector the coder works on) and blocks rebuilt from fields with all-zero codes; per weight the interval of
+ * original values that rounds to its code, whether code and sub-block integer scale equal another tensor's, and - for
+ * the lattice types - half the step between the lattice's levels.  Scalar-code types 2 3 6 7 8 10 11 12 13 14 20 23
+ * 42, lattice types 16 17 18 19 21 22 29 where stated; SG_ERR_TYPE otherwise. */
+SG_API int sg_qr_block_fields(int device, void *stream, int T, const unsigned char *F, long long nblocks, int *out);
+SG_API int sg_qr_blocks_from_fields(int device, void *stream, int T, const int *fields, int nblocks, unsigned char *out);
+SG_API int sg_qr_intervals(int device, void *stream, int T, const unsigned char *F, long long nweights, float *lo, float *hi);
+SG_API int sg_qr_weight_equal(int device, void *stream, int T, const unsigned char *F, const unsigned char *P,
+                              long long nweights, unsigned char *out);
+SG_API int sg_qr_grid_half_step(int device, void *stream, int T, const unsigned char *F, long long nweights, float *h);
 
 /* ---- M24: the earlier BF16 base codec (archives packed with --method m28) ---------------------------------------------
  * Replaces bf_hist / bf_enc / bf_dec (seedpack/gpu_bf16.py:63-137): 12 probability bits, 160 tables per tensor (128

@@ -67,6 +67,11 @@ SIGNATURES = {
     "sg_dm_exp2": (_I, [_I, _P, _P, _L, _P]),
     "sg_dm_rows": (_I, [_I, _P, _P, _L, _L, _I, _P]),
     "sg_dm_cols": (_I, [_I, _P, _P, _L, _L, _I, _P, _P]),
+    "sg_qr_block_fields": (_I, [_I, _P, _I, _P, _L, _P]),
+    "sg_qr_blocks_from_fields": (_I, [_I, _P, _I, _P, _I, _P]),
+    "sg_qr_intervals": (_I, [_I, _P, _I, _P, _L, _P, _P]),
+    "sg_qr_weight_equal": (_I, [_I, _P, _I, _P, _P, _L, _P]),
+    "sg_qr_grid_half_step": (_I, [_I, _P, _I, _P, _L, _P]),
     "sg_m24_hist": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P]),
     "sg_m24_encode": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _Z, _P]),
     "sg_m24_decode": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P]),

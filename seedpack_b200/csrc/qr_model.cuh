@@ -261,16 +261,38 @@ SG_DEVINL void wscale(int T, const int* v, int sub, float& a, float& c) {
 }
 
 // The seed's value of weight gw of the tensor and its half uncertainty (qr.py:323-344).  Seed types: 30 BF16, 0 F32,
-// 1 F16 (exact: h = 0), 98 no seed (x = 0, h = the column's RMS), 99 explicit (x, h) pairs.  Quantised seeds
-// (a sibling quant standing in for a missing BF16 file) are not handled here; `ok` reports an unknown type.
-SG_DEVINL bool seed_known(int ST) { return ST == 30 || ST == 0 || ST == 1 || ST == 98 || ST == 99; }
+// 1 F16 (exact: h = 0), 98 no seed (x = 0, h = the column's RMS), 99 explicit (x, h) pairs, or a scalar-code quant type
+// (a sibling quant standing in for a missing BF16 file: x = its dequantised weight a code + c, h = half a code step;
+// the IQ4 level types: half the gap to the next level).  The host refuses every other type before a launch.
+SG_DEVINL bool seed_is_quant(int ST) {
+    switch (ST) { case 2: case 3: case 6: case 7: case 8: case 10: case 11: case 12: case 13: case 14: case 20: case 23: case 42: return true; }
+    return false;
+}
+SG_DEVINL bool seed_known(int ST) { return ST == 30 || ST == 0 || ST == 1 || ST == 98 || ST == 99 || seed_is_quant(ST); }
+SG_DEVINL void unpack_fields(int T, const uchar* b, int* v);
+SG_DEVINL void wscale(int T, const int* v, int sub, float& a, float& c);
 SG_DEVINL void seed_val(int ST, const uchar* sb, long long gw, float& x, float& h, int cols) {
     h = 0.f;
     if (ST == 30) { x = __uint_as_float((unsigned)reinterpret_cast<const unsigned short*>(sb)[gw] << 16); return; }
     if (ST == 0) { x = reinterpret_cast<const float*>(sb)[gw]; return; }
     if (ST == 1) { x = h2fv(reinterpret_cast<const unsigned short*>(sb)[gw]); return; }
     if (ST == 98) { x = 0.f; h = reinterpret_cast<const float*>(sb)[gw % cols]; return; }
-    const float* f = reinterpret_cast<const float*>(sb); x = f[2 * gw]; h = f[2 * gw + 1];
+    if (ST == 99) { const float* f = reinterpret_cast<const float*>(sb); x = f[2 * gw]; h = f[2 * gw + 1]; return; }
+    const int qk = qk_of(ST), w = (int)(gw % qk);
+    const uchar* blk = sb + (gw / qk) * bs_of(ST);
+    int v[34];
+    unpack_fields(ST, blk, v);
+    float a, c;
+    wscale(ST, v, w / sublen_of(ST), a, c);
+    const int q = get_code(ST, blk, w);
+    if (nonlin(ST)) {
+        x = __fmul_rn(a, kv(q));
+        const float g = q < 15 ? kv(q + 1) - kv(q) : kv(15) - kv(14);
+        h = __fmul_rn(fabsf(a), 0.5f * g);
+    } else {
+        x = __fadd_rn(__fmul_rn(a, (float)q), c);
+        h = __fmul_rn(fabsf(a), 0.5f);
+    }
 }
 
 // predicted code r, mirror sign s and context of weight w from the TRUE block scales (qr.py:348-377)

@@ -142,11 +142,15 @@ def check_records(T, nblocks, seed_offs, seed_types, cols, imx_offs, seed_bytes,
             item = SEED_ITEM[st]
             if off < 0 or off % min(item, 4) or off + nw * item > seed_bytes:
                 raise ValueError(f"tensor {i}: seed bytes {off}..{off + nw * item} (type {st}) are outside the seed buffer of {seed_bytes}")
+        elif st in SELF_TYPES:                            # a sibling quant as the seed: that type's blocks
+            need = nw // QK[st] * BS[st]
+            if nw % QK[st] or off < 0 or off % 2 or off + need > seed_bytes:
+                raise ValueError(f"tensor {i}: seed blocks {off}..{off + need} (quant type {st}) are outside the seed buffer of {seed_bytes}")
         elif st == COLRMS:
             if c <= 0 or off < 0 or off % 4 or off + 4 * c > seed_bytes:
                 raise ValueError(f"tensor {i}: column statistics {off}..{off + 4 * c} are outside the seed buffer of {seed_bytes}")
         else:
-            raise ValueError(f"tensor {i}: seed type {st} is not one the coder reads (BF16 30, F16 1, F32 0, 98, 99)")
+            raise ValueError(f"tensor {i}: seed type {st} is not one the coder reads (BF16 30, F16 1, F32 0, 98, 99, scalar-code quants)")
         if io >= 0 and (c <= 0 or io + c > imx_floats):
             raise ValueError(f"tensor {i}: importance values {io}..{io + c} are outside the {imx_floats} given")
         if io < -1:

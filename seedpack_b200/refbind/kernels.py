@@ -12,6 +12,8 @@ raises, so nothing of the reference's CUDA source can run by accident.
     build_lut                   bf16v2.py:139, qr.py:889   folded into the decoders' table preparation (sg_rans_tables)
     gather                      qr.py:880-887, gpu2.py     sg_scan_gather
     qr_hist / qr_enc / qr_dec   qr.py:674-807          sg_residual_blocks + sg_qr_hist / sg_qr_encode / sg_qr_decode
+    block_fields / blocks_from_fields / intervals / weq / grid_h   qr.py:811-878   sg_qr_block_fields / ..._from_fields /
+                                                       sg_qr_intervals / sg_qr_weight_equal / sg_qr_grid_half_step
     dm_log2 / dm_exp2 / dm_rows / dm_cols   detmath.py:67-106   sg_dm_log2 / sg_dm_exp2 / sg_dm_rows / sg_dm_cols
     dm_rows_d / dm_gram / dm_bdot / dm_solve  detmath.py:86-153  sg_dm_rows_f64 / sg_dm_gram / sg_dm_bdot / sg_dm_solve
     k_dq_<type>                 gpuquant.py:215-219    sg_dequantize
@@ -213,6 +215,35 @@ def _qr_dec(args):
     _corrupt("QR batch")
 
 
+# ---- QR helpers for tensors without a BF16 seed ------------------------------------------------------------------------
+def _block_fields(args):
+    T, F, nblk, out = args
+    _lib.check(_lib.lib().sg_qr_block_fields(_dev(), _st(), _i(T), _p(F.dev_in()), _i(nblk), _p(out.dev_out())), "sg_qr_block_fields")
+
+
+def _blocks_from_fields(args):
+    T, v, n, out = args
+    _lib.check(_lib.lib().sg_qr_blocks_from_fields(_dev(), _st(), _i(T), _p(v.dev_in()), _i(n), _p(out.dev_out())), "sg_qr_blocks_from_fields")
+
+
+def _intervals(args):
+    T, F, nw, lo, hi = args
+    _lib.check(_lib.lib().sg_qr_intervals(_dev(), _st(), _i(T), _p(F.dev_in()), _i(nw), _p(lo.dev_out()), _p(hi.dev_out())), "sg_qr_intervals")
+
+
+def _weq(args):
+    T, F, P, nw, out = args
+    _lib.check(_lib.lib().sg_qr_weight_equal(_dev(), _st(), _i(T), _p(F.dev_in()), _p(P.dev_in()), _i(nw), _p(out.dev_out())), "sg_qr_weight_equal")
+
+
+def _grid_h(args):
+    T, F, nw, h = args
+    if _i(T) in GRID_TYPES:
+        from .. import tables
+        tables.install(_dev())
+    _lib.check(_lib.lib().sg_qr_grid_half_step(_dev(), _st(), _i(T), _p(F.dev_in()), _i(nw), _p(h.dev_out())), "sg_qr_grid_half_step")
+
+
 # ---- detmath ---------------------------------------------------------------------------------------------------------
 def _dm_log2(args):
     x, n, y = args
@@ -278,7 +309,8 @@ def _bf16_to_f32(a, y=None):
 
 
 _BOUND = {"bf_hist": _bf_hist, "bf_enc": _bf_enc, "bf_dec": _bf_dec, "v2_hist": _v2_hist, "v2_enc": _v2_enc, "v2_dec": _v2_dec, "row_hash": _row_hash, "build_lut": _build_lut,
-          "gather": _gather, "qr_hist": _qr_hist, "qr_enc": _qr_enc, "qr_dec": _qr_dec,
+          "gather": _gather, "qr_hist": _qr_hist, "qr_enc": _qr_enc, "qr_dec": _qr_dec, "block_fields": _block_fields,
+          "blocks_from_fields": _blocks_from_fields, "intervals": _intervals, "weq": _weq, "grid_h": _grid_h,
           "dm_log2": _dm_log2, "dm_exp2": _dm_exp2, "dm_rows": _dm_rows, "dm_cols": _dm_cols, "dm_rows_d": _dm_rows_d,
           "dm_gram": _dm_gram, "dm_bdot": _dm_bdot, "dm_solve": _dm_solve}
 for _t, (_name, _, _) in QFUN.items():

@@ -144,8 +144,9 @@ def test_batch_records_are_bounds_checked_on_the_host():
     check_records(**ok)
     for change in (dict(seed_bytes=4096 + 4 * 256 * 2 - 2),            # the last tensor's seed runs past the buffer
                    dict(seed_offs=[0, -2]), dict(seed_offs=[1, 4096]),  # negative / odd BF16 offset
-                   dict(seed_types=[30, 12]),                           # a quantised seed: not read by these kernels
+                   dict(seed_types=[30, 17]),                           # a lattice type cannot be a seed
                    dict(seed_types=[30, 77]),
+                   dict(seed_types=[30, 8], seed_offs=[0, 5200]),       # a Q8_0 seed whose blocks run past the buffer
                    dict(cols=[1000, 1024]),                             # not whole blocks per row
                    dict(cols=[1024, 768]),                              # 4 blocks are not whole rows of 768
                    dict(imx_offs=[0, -1], imx_floats=1000),             # importance vector shorter than a row
@@ -157,3 +158,4 @@ def test_batch_records_are_bounds_checked_on_the_host():
         check_records(T, [8], [0], [98], [0], [-1], 4096, 0)         # ... needs the row length
     check_records(17, [8], [0], [0], [2048], [0], 8 * 256 * 4, 2048)  # F32 seed, lattice type with importance values
     check_records(T, [8], [0], [99], [0], [-1], 8 * 256 * 8, 0)       # explicit (x, h) pairs
+    check_records(T, [8], [0], [8], [1024], [-1], 8 * 256 // 32 * 34, 0)   # a sibling Q8_0 tensor as the seed

@@ -176,7 +176,7 @@ def test_other_seed_types_match_the_reference(T, kind, mv):
 def test_unknown_seed_type_is_refused():
     from seedpack_b200.qr import QRCodec
     enc, _ = _seed_items(12, 1)
-    bad = [it[:3] + (12,) + it[4:] for it in enc]            # a quantised seed: these kernels do not read it
+    bad = [it[:3] + (17,) + it[4:] for it in enc]            # a lattice type cannot stand in for the seed
     with pytest.raises(ValueError):
         QRCodec().encode(12, bad, GS["seed_12_1"], None)
 
