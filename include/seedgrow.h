@@ -293,6 +293,23 @@ SG_API int sg_m24_decode(int device, void *stream, const unsigned char *in, cons
                          const short *rfi, const short *cfi, const signed char *scl, const void *enc_tab,
                          const unsigned char *lut);
 
+/* ---- M6: the first GPU codec, Q8_0 files without a base ------------------------------------------------------------------
+ * Replaces hist / encode / decode of seedpack/gpu_codec.py:73-159.  blocks = the file's Q8_0 blocks back to back (34 bytes
+ * each), pos[b] = index of block b's largest magnitude, meta = per tensor { int32 first, nblocks, nb_row, grp, colbase,
+ * med } (gpu_codec.py:182-183), tfirst[t] = first block of tensor t, colmap = a class byte per column; segments of 512
+ * blocks; 770 tables per tensor group addressed by raw id (counts / enc_tab / lut cover ngroups * 770, sg_rans_tables with
+ * pb = 12, the frequency array as the reference holds it: one row per table, unused rows zero); the encoder's slot must
+ * hold a segment (the reference uses cap = 512 * 34 * 2 + 16, rounded up to 16 here by the caller). */
+SG_API int sg_m6_hist(int device, void *stream, const unsigned char *blocks, const unsigned char *pos, const void *meta,
+                      const int *tfirst, int ntens, const unsigned char *colmap, int nblocks, unsigned *counts);
+SG_API int sg_m6_encode(int device, void *stream, const unsigned char *blocks, const unsigned char *pos, const void *meta,
+                        const int *tfirst, int ntens, const unsigned char *colmap, int nblocks, const void *enc_tab,
+                        unsigned char *slots, size_t cap, unsigned *out_len);
+SG_API int sg_m6_decode(int device, void *stream, const unsigned char *in, const unsigned long long *in_off,
+                        const unsigned long long *in_end, const void *meta, const int *tfirst, int ntens,
+                        const unsigned char *colmap, int nblocks, const void *enc_tab, const unsigned char *lut,
+                        unsigned char *blocks);
+
 /* The remaining detmath kernels (seedpack/detmath.py:86-93, 109-153: dm_rows_d, dm_gram, dm_bdot, dm_solve), which the
  * importance fit uses (seedpack/imxfit.py:36-75): sums (of squares) along the rows of a float64 matrix; batched
  * X[c] X[c]^T (X: nb x k x d float32 -> nb x k x k float32) and X[c] y[c] (-> nb x k) with float64 sums in index order;

@@ -72,6 +72,9 @@ SIGNATURES = {
     "sg_qr_intervals": (_I, [_I, _P, _I, _P, _L, _P, _P]),
     "sg_qr_weight_equal": (_I, [_I, _P, _I, _P, _P, _L, _P]),
     "sg_qr_grid_half_step": (_I, [_I, _P, _I, _P, _L, _P]),
+    "sg_m6_hist": (_I, [_I, _P, _P, _P, _P, _P, _I, _P, _I, _P]),
+    "sg_m6_encode": (_I, [_I, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _Z, _P]),
+    "sg_m6_decode": (_I, [_I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P]),
     "sg_m24_hist": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P]),
     "sg_m24_encode": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _Z, _P]),
     "sg_m24_decode": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P]),

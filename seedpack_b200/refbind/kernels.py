@@ -145,6 +145,54 @@ def _bf_dec(args):
     _corrupt("M24")
 
 
+# ---- M6 (gpu_codec.py: Q8_0 files without a base) ---------------------------------------------------------------------
+def _m6_tables(freq, lut):
+    """the reference's full frequency array (a row per table, unused rows zero) -> encoder entries and symbol table"""
+    key = ("m6", id(freq.st), freq.off)
+    hit = _TABS.get(key)
+    if hit is not None and (hit[1] is not None or not lut):
+        _TABS.move_to_end(key)
+        return hit[0], hit[1]
+    sums = freq._h().reshape(-1, 256).sum(1, dtype=np.int64)
+    if ((sums != 0) & (sums != (1 << QR_PB))).any():
+        raise ValueError("coder tables: a row of frequencies does not sum to 2^PB (damaged table part)")
+    ntab = sums.size
+    f = freq.dev_in()
+    enc = torch.empty(ntab * 256 * 2, dtype=torch.int32, device=f.device)
+    l = torch.zeros(ntab << QR_PB, dtype=torch.uint8, device=f.device) if lut else None
+    _lib.check(_lib.lib().sg_rans_tables(_dev(), _st(), _p(f), ntab, QR_PB, _p(enc), _p(l)), "sg_rans_tables")
+    _TABS[key] = (enc, l, freq)
+    while len(_TABS) > 6:
+        _TABS.popitem(last=False)
+    return enc, l
+
+
+def _m6_hist(args):
+    blocks, pos, meta, tfirst, ntens, colmap, n, counts = args
+    _lib.check(_lib.lib().sg_m6_hist(_dev(), _st(), _p(blocks.dev_in()), _p(pos.dev_in()), _p(meta.dev_in()), _p(tfirst.dev_in()), _i(ntens),
+                                     _p(colmap.dev_in()), _i(n), _p(counts.dev_inout())), "sg_m6_hist")
+
+
+def _m6_enc(args):
+    blocks, pos, meta, tfirst, ntens, colmap, n, freq, cum, out, cap, out_len = args
+    enc, _ = _m6_tables(freq, False)
+    _lib.check(_lib.lib().sg_m6_encode(_dev(), _st(), _p(blocks.dev_in()), _p(pos.dev_in()), _p(meta.dev_in()), _p(tfirst.dev_in()), _i(ntens),
+                                       _p(colmap.dev_in()), _i(n), _p(enc), _p(out.dev_out()), _i(cap), _p(out_len.dev_out())), "sg_m6_encode")
+    lens = out_len._h()
+    if (lens == 0xffffffff).any():
+        raise ValueError("M6: a segment's code outgrew its slot")
+
+
+def _m6_dec(args):
+    stream, offs, meta, tfirst, ntens, colmap, n, freq, cum, lut, blocks = args
+    enc, l = _m6_tables(freq, True)
+    o = offs.dev_in().view(torch.int64)
+    e = _seg_ends(o, stream.size)
+    _lib.check(_lib.lib().sg_m6_decode(_dev(), _st(), _p(stream.dev_in()), _p(o), _p(e), _p(meta.dev_in()), _p(tfirst.dev_in()), _i(ntens),
+                                       _p(colmap.dev_in()), _i(n), _p(enc), _p(l), _p(blocks.dev_out())), "sg_m6_decode")
+    _corrupt("M6")
+
+
 def _corrupt(what):
     bits = ctypes.c_int(0)
     _lib.check(_lib.lib().sg_status_fetch(_dev(), _st(), ctypes.byref(bits)), "sg_status_fetch")
@@ -312,7 +360,8 @@ _BOUND = {"bf_hist": _bf_hist, "bf_enc": _bf_enc, "bf_dec": _bf_dec, "v2_hist": 
           "gather": _gather, "qr_hist": _qr_hist, "qr_enc": _qr_enc, "qr_dec": _qr_dec, "block_fields": _block_fields,
           "blocks_from_fields": _blocks_from_fields, "intervals": _intervals, "weq": _weq, "grid_h": _grid_h,
           "dm_log2": _dm_log2, "dm_exp2": _dm_exp2, "dm_rows": _dm_rows, "dm_cols": _dm_cols, "dm_rows_d": _dm_rows_d,
-          "dm_gram": _dm_gram, "dm_bdot": _dm_bdot, "dm_solve": _dm_solve}
+          "dm_gram": _dm_gram, "dm_bdot": _dm_bdot, "dm_solve": _dm_solve,
+          "hist": _m6_hist, "encode": _m6_enc, "decode": _m6_dec}
 for _t, (_name, _, _) in QFUN.items():
     _BOUND["k_dq_" + _name[len("quantize_"):]] = _dequant(_t)
 
