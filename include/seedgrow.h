@@ -310,6 +310,23 @@ SG_API int sg_m6_decode(int device, void *stream, const unsigned char *in, const
                         const unsigned char *colmap, int nblocks, const void *enc_tab, const unsigned char *lut,
                         unsigned char *blocks);
 
+/* ---- the scalar stream coder of the first codec generations -------------------------------------------------------------
+ * Replaces _encode / _decode of seedpack/rans.py:54-105 (one rANS state per stream, 14 probability bits, a table number
+ * per symbol from the caller), as M22's BF16 codec uses them (seedpack/bf16codec.py:56-58, 88-92).  A launch codes
+ * nchain streams that share tables, one lane each: stream c covers the symbols [sym_off[c], sym_off[c + 1]) of sym and
+ * ctx (ctx elements of 1, 2 or 4 bytes, unsigned; a value >= ntab marks the stream).  Encode writes stream c at the END
+ * of slots[slot_off[c] .. slot_off[c + 1]) (16-byte aligned offsets; the reference sizes a slot 2 * symbols + 16) and
+ * out_len[c] = its bytes, 0xffffffff when the slot was too small, 0xfffffffe for a symbol without frequency.  Decode
+ * reads stream c from in[in_off[c] .. in_end[c]) and, when `used` is given, stores how many bytes it consumed (what
+ * rans.py's _decode returns); enc_tab / lut from sg_rans_tables with pb = 14. */
+SG_API int sg_rans_chain_encode(int device, void *stream, const unsigned char *sym, const void *ctx, int ctx_bytes,
+                                const unsigned long long *sym_off, int nchain, int ntab, const void *enc_tab,
+                                unsigned char *slots, const unsigned long long *slot_off, unsigned long long *out_len);
+SG_API int sg_rans_chain_decode(int device, void *stream, const unsigned char *in, const unsigned long long *in_off,
+                                const unsigned long long *in_end, const void *ctx, int ctx_bytes,
+                                const unsigned long long *sym_off, int nchain, int ntab, const void *enc_tab,
+                                const unsigned char *lut, unsigned char *sym_out, unsigned long long *used);
+
 /* The remaining detmath kernels (seedpack/detmath.py:86-93, 109-153: dm_rows_d, dm_gram, dm_bdot, dm_solve), which the
  * importance fit uses (seedpack/imxfit.py:36-75): sums (of squares) along the rows of a float64 matrix; batched
  * X[c] X[c]^T (X: nb x k x d float32 -> nb x k x k float32) and X[c] y[c] (-> nb x k) with float64 sums in index order;

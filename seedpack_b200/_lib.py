@@ -75,6 +75,8 @@ SIGNATURES = {
     "sg_m6_hist": (_I, [_I, _P, _P, _P, _P, _P, _I, _P, _I, _P]),
     "sg_m6_encode": (_I, [_I, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _Z, _P]),
     "sg_m6_decode": (_I, [_I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P]),
+    "sg_rans_chain_encode": (_I, [_I, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P]),
+    "sg_rans_chain_decode": (_I, [_I, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P]),
     "sg_m24_hist": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P]),
     "sg_m24_encode": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _Z, _P]),
     "sg_m24_decode": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P]),

@@ -86,6 +86,8 @@ def install(reference=None, staged_qr=None):
     _bind_qr(qr, staged_qr)
     _bind_r2(bf16v2)
     _bind_float(repo3)
+    from seedpack import rans
+    _bind_rans(rans)
     _state["pkg"] = seedpack
     return seedpack
 
@@ -150,6 +152,82 @@ def _bind_r2(bf16v2):
         return rfi, cfi, scl
 
     bf16v2.BF16v2._stats = _stats
+
+
+# ---- the scalar stream coder (rans.py) -------------------------------------------------------------------------------------
+def _bind_rans(rans):
+    """rans.encode / rans.decode (seedpack/rans.py:152-164: host arrays in, host bytes / symbols out; numba loops) run
+    as one stream = one lane of sg_rans_chain_encode / sg_rans_chain_decode.  M22 (bf16codec.py) is their caller"""
+    import ctypes
+    import numpy as np
+    import torch
+    from .. import _lib
+    from . import cupy_shim as cp
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+
+    def _setup(ctx, freqs):
+        d = cp.device_index()
+        dev = torch.device("cuda", d)
+        st = ctypes.c_void_p(torch.cuda.current_stream(d).cuda_stream)
+        f = np.ascontiguousarray(freqs, np.uint16)
+        if f.ndim != 2 or f.shape[1] != 256:
+            raise ValueError("rans: tables of 256 symbols expected")
+        sums = f.sum(1, dtype=np.int64)
+        if ((sums != 0) & (sums != rans.PROB_SCALE)).any():
+            raise ValueError("coder tables: a row of frequencies does not sum to 2^PB (damaged table part)")
+        c = np.ascontiguousarray(ctx)
+        if c.dtype.kind not in "iu" or c.dtype.itemsize > 4:
+            c = c.astype(np.int32)
+        if c.size and (int(c.min()) < 0 or int(c.max()) >= f.shape[0]):
+            raise ValueError("rans: a context outside the tables")
+        ntab = f.shape[0]
+        enc = torch.empty(ntab * 256 * 2, dtype=torch.int32, device=dev)
+        lut = torch.zeros(ntab << rans.PROB_BITS, dtype=torch.uint8, device=dev)
+        fd = torch.from_numpy(f.view(np.int16)).to(dev)
+        _lib.check(_lib.lib().sg_rans_tables(d, st, p(fd), ntab, rans.PROB_BITS, p(enc), p(lut)), "sg_rans_tables")
+        cd = torch.from_numpy(c.view(np.uint8).reshape(-1)).to(dev)
+        _lib.count_h2d(f.nbytes + c.nbytes)
+        return d, dev, st, ntab, enc, lut, cd, c.dtype.itemsize, (fd,)
+
+    def encode(sym, ctx, freqs):
+        s = np.ascontiguousarray(sym, np.uint8).reshape(-1)
+        n = s.size
+        d, dev, st, ntab, enc, lut, cd, cb, keep = _setup(ctx, freqs)
+        cap = (2 * n + 16 + 15) // 16 * 16
+        sd = torch.from_numpy(s).to(dev) if n else torch.zeros(16, dtype=torch.uint8, device=dev)
+        slots = torch.empty(cap, dtype=torch.uint8, device=dev)
+        offs = torch.tensor([0, n, 0, cap], dtype=torch.int64, device=dev)
+        ln = torch.zeros(1, dtype=torch.int64, device=dev)
+        _lib.check(_lib.lib().sg_rans_chain_encode(d, st, p(sd), p(cd) if n else p(sd), cb, p(offs), 1, ntab, p(enc), p(slots), p(offs[2:]), p(ln)),
+                   "sg_rans_chain_encode")
+        k = int(ln.item())
+        if k == 0xfffffffe:
+            raise ValueError("rANS encoder: a coded symbol has frequency 0 in its table")
+        if k == 0xffffffff:
+            raise ValueError("rANS encoder: the stream outgrew its slot")
+        _lib.count_h2d(n); _lib.count_d2h(k)
+        return slots[cap - k:].cpu().numpy().tobytes()
+
+    def decode(buf, ctx, freqs):
+        n = int(np.asarray(ctx).shape[0])
+        b = np.frombuffer(buf, np.uint8)
+        d, dev, st, ntab, enc, lut, cd, cb, keep = _setup(ctx, freqs)
+        if n == 0:
+            return np.empty(0, np.uint8)
+        bd = torch.zeros(b.size + 16, dtype=torch.uint8, device=dev)
+        bd[:b.size] = torch.from_numpy(b.copy()).to(dev)
+        offs = torch.tensor([0, n, 0, b.size], dtype=torch.int64, device=dev)
+        out = torch.empty(n, dtype=torch.uint8, device=dev)
+        _lib.check(_lib.lib().sg_rans_chain_decode(d, st, p(bd), p(offs[2:]), p(offs[3:]), p(cd), cb, p(offs), 1, ntab, p(enc), p(lut), p(out), None),
+                   "sg_rans_chain_decode")
+        bits = ctypes.c_int(0)
+        _lib.check(_lib.lib().sg_status_fetch(d, st, ctypes.byref(bits)), "sg_status_fetch")
+        if bits.value & 4:
+            raise ValueError("rans: corrupt coded stream")
+        _lib.count_h2d(b.size); _lib.count_d2h(n)
+        return out.cpu().numpy()
+
+    rans.encode, rans.decode = encode, decode
 
 
 # ---- float tensors -----------------------------------------------------------------------------------------------------
