@@ -86,6 +86,7 @@ def install(reference=None, staged_qr=None):
     _bind_qr(qr, staged_qr)
     _bind_r2(bf16v2)
     _bind_float(repo3)
+    _bind_residual(repo3)
     from seedpack import rans
     _bind_rans(rans)
     _state["pkg"] = seedpack
@@ -100,6 +101,7 @@ def _bind_qr(qr, staged):
     import torch
     from .. import qr as own
     from . import cupy_shim as cp
+    from . import twins
     from .quant import from_torch
     if not staged:
         return
@@ -112,8 +114,12 @@ def _bind_qr(qr, staged):
         return codecs[d]
 
     def arr(a):
-        """host or device bytes of a tensor as QRCodec takes them"""
-        return a.dev_in() if isinstance(a, cp.ndarray) else a
+        """host or device bytes of a tensor as QRCodec takes them; a host array whose bytes are on the device already
+        (refbind.twins) is taken from there"""
+        if isinstance(a, cp.ndarray):
+            return a.dev_in()
+        t = twins.find(a)
+        return a if t is None else t
 
     def encode(T, items, seed_dev, imx_dev=None, mv=None):
         its = [(arr(it[0]), arr(it[1])) + tuple(it[2:]) for it in items]
@@ -152,6 +158,74 @@ def _bind_r2(bf16v2):
         return rfi, cfi, scl
 
     bf16v2.BF16v2._stats = _stats
+
+
+# ---- residual against the stored quant --------------------------------------------------------------------------------
+def _bind_residual(repo3):
+    """The comparisons of a stored tensor with its prediction (repo3.py:476-497: `_diff_async`, `_count_diff`) on the
+    device (sg_residual_xor, counting only).  The reference compares on the host, in 2 MiB chunks handed to a thread
+    pool, after downloading every prediction.  Here the prediction is still on the device when its host copy arrives
+    (refbind.quant._download registers it), and the span of the file that `_residual_tensors` works on is uploaded once,
+    when it starts: each comparison is then one launch and one 8-byte read, and the QR coder later takes the same device
+    bytes as its inputs.  Operands without a device copy go to the reference's own functions.  The in-place XOR of
+    float tensors (`_xor_async`, `_xor3`) stays on the host: its result is wanted there, by zstd"""
+    import numpy as np
+    import torch
+    from .. import residual
+    from . import cupy_shim as cp
+    from . import quant, twins, xfer
+    ref_diff, ref_count, ref_tensors = repo3._diff_async, repo3._count_diff, repo3.M28RepoGPU._residual_tensors
+    MIN_SPAN = 1 << 20
+
+    class _Done:
+        def __init__(self, v):
+            self.v = v
+
+        def result(self, timeout=None):
+            return self.v
+
+        def done(self):
+            return True
+
+    def _pair(a, b):
+        if b is None or not isinstance(a, np.ndarray) or not isinstance(b, np.ndarray) or a.nbytes != b.nbytes:
+            return None, None
+        da = twins.find(a)
+        if da is None:
+            return None, None
+        db = twins.find(b)
+        if db is None:
+            return None, None
+        cp.device_index()
+        return da, db
+
+    def _diff_async(r, p):
+        da, db = _pair(r, p)
+        if da is None:
+            return ref_diff(r, p)
+        return [_Done(residual.count_diff(da, db) > 0)]
+
+    def _count_diff(a, b=None):
+        da, db = _pair(a, b)
+        if da is None:
+            return ref_count(a, b)
+        return residual.count_diff(da, db)
+
+    def _residual_tensors(self, view, at, ts, held, memo=None, hashes=None):
+        if isinstance(view, np.ndarray) and view.flags.c_contiguous and view.nbytes >= MIN_SPAN and any(k == "rq" for _, k in ts) \
+                and twins.find(view[:1]) is None:
+            d = cp.device_index()
+            lead = int(at) % 16                 # tensors start on 32-byte file offsets: keep them 16-byte aligned on the device
+            buf = torch.empty(view.nbytes + 16 + 64, dtype=torch.uint8, device=torch.device("cuda", d))
+            dev = buf[lead:lead + view.nbytes]
+            xfer.h2d(dev, view.reshape(-1).view(np.uint8))
+            cp.STATS["h2d"] += view.nbytes
+            twins.register(view, dev)
+        return ref_tensors(self, view, at, ts, held, memo, hashes)
+
+    repo3._diff_async, repo3._count_diff = _diff_async, _count_diff
+    repo3.M28RepoGPU._residual_tensors = _residual_tensors
+    repo3._pcopy = quant.pcopy(repo3._pcopy)
 
 
 # ---- the scalar stream coder (rans.py) -------------------------------------------------------------------------------------

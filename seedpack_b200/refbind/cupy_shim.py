@@ -27,6 +27,8 @@ import weakref
 import numpy as np
 import torch
 
+from . import xfer
+
 _BIG = 1 << 16                     # arrays from this size on are created on the device
 _SLACK = 64                        # device allocations are padded: vector loads may read up to the next 16 bytes
 _DEBUG = os.environ.get("SEEDGROW_BIND_DEBUG") == "1"
@@ -84,7 +86,7 @@ class _Storage:
                 self.hv = True
         if not self.hv:
             if self.dv and self.n:
-                torch.from_numpy(self.host).copy_(self.dev[:self.n])
+                xfer.d2h(self.host, self.dev[:self.n])
                 STATS["d2h"] += self.n
             self.hv = True
         return self.host
@@ -100,7 +102,7 @@ class _Storage:
                 self.dv = True
         if not self.dv:
             if self.hv and self.n:
-                self.dev[:self.n].copy_(torch.from_numpy(self.host))
+                xfer.h2d(self.dev[:self.n], self.host)
                 STATS["h2d"] += self.n
             self.dv = True
         return self.dev
@@ -301,7 +303,7 @@ class ndarray:
         if isinstance(value, np.ndarray):
             if value.dtype != self.dtype or value.size != self.size or not (self._big_dev() or n >= _BIG):
                 return False
-            self.dev_out().copy_(_from_numpy(np.ascontiguousarray(value).reshape(-1).view(np.uint8)))
+            xfer.h2d(self.dev_out(), np.ascontiguousarray(value).reshape(-1).view(np.uint8))
             STATS["h2d"] += n
             return True
         if isinstance(value, (int, np.integer)) and int(value) == 0 and self._big_dev():
@@ -324,7 +326,7 @@ class ndarray:
             if flat is None:
                 out[...] = self._h()
             else:
-                torch.from_numpy(flat).copy_(self.dev_in())
+                xfer.d2h(flat, self.dev_in())
                 STATS["d2h"] += self.nbytes
         return out
 
@@ -503,6 +505,10 @@ def zeros_like(a, dtype=None):
 def asarray(a, dtype=None, order=None, blocking=False):
     if isinstance(a, ndarray):
         return a if dtype is None or a.dtype == np.dtype(dtype) else a.astype(dtype)
+    if isinstance(a, np.ndarray) and a.nbytes >= _BIG and a.flags.c_contiguous and (dtype is None or a.dtype == np.dtype(dtype)):
+        out = empty(a.shape, a.dtype)                # (copied to the device before this returns: no host copy first)
+        out.set(a)
+        return out
     h = np.array(a, dtype=dtype, order="C", copy=True)
     if h.nbytes >= _BIG:
         out = empty(h.shape, h.dtype)
@@ -697,10 +703,21 @@ class _PinnedPool:
     """page-locked staging buffers, kept and reused by size class: locking pages is slow"""
 
     def __init__(self):
-        self.free, self.lock, self.held = {}, threading.Lock(), 0
+        self.free, self.lock, self.held, self.roots = {}, threading.Lock(), 0, {}
+
+    @staticmethod
+    def size_class(n):
+        """n rounded up to an eighth of its power of two (at least 64 KiB): at most 12.5 % of a block is unused"""
+        n = max(int(n), 1 << 16)
+        step = max(1 << 13, (1 << (n - 1).bit_length()) >> 3)
+        return -(-n // step) * step
+
+    def owns(self, a):
+        """whether NumPy array a is a block of this pool (not a view of one)"""
+        return id(a) in self.roots
 
     def take(self, n):
-        cls = max(1 << 16, 1 << (int(n) - 1).bit_length())
+        cls = self.size_class(n)
         with self.lock:
             lst = self.free.get(cls)
             t = lst.pop() if lst else None
@@ -710,11 +727,13 @@ class _PinnedPool:
             except RuntimeError as e:
                 raise CUDARuntimeError(str(e))
         a = t.numpy()
-        weakref.finalize(a, self._give, cls, t)
+        self.roots[id(a)] = True
+        weakref.finalize(a, self._give, cls, t, id(a))
         return a
 
-    def _give(self, cls, t):
+    def _give(self, cls, t, key):
         with self.lock:
+            self.roots.pop(key, None)
             self.free.setdefault(cls, []).append(t)
 
     def free_all_blocks(self, stream=None):

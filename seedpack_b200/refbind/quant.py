@@ -13,6 +13,7 @@ import torch
 from .. import gpuquant as _gq
 from ..requant import QFUN
 from . import cupy_shim as cp
+from . import twins
 
 _TORCH = {np.dtype(np.uint16): torch.int16, np.dtype(np.float16): torch.float16, np.dtype(np.float32): torch.float32}
 
@@ -36,6 +37,34 @@ def to_host(a):
         return a.get()
     a.get(out=host)
     return host
+
+
+def _download(ys):
+    """the tensors of a launch -> one page-locked NumPy array each (a block of its own: the caller may keep it without
+    holding the launch's other outputs), copied side by side and waited for once.  The device copy stays registered as
+    the array's twin: what the host array is compared with or coded against next is served from it"""
+    try:
+        hosts = [cp.empty_pinned(y.numel(), np.uint8) for y in ys]
+    except cp.CUDARuntimeError:
+        return [to_host(from_torch(y)) for y in ys]
+    for h, y in zip(hosts, ys):
+        torch.from_numpy(h).copy_(y, non_blocking=True)
+    torch.cuda.current_stream(ys[0].device).synchronize() if ys else None
+    for h, y in zip(hosts, ys):
+        cp.STATS["d2h"] += h.nbytes
+        twins.register(h, y)
+    return hosts
+
+
+def pcopy(reference_pcopy):
+    """repo3._pcopy (repo3.py:516-525: the copy a prediction is cached as, made because a prediction may be a view of
+    a launch's whole output): an array that is a page-locked block of its own already is kept as it is"""
+    def _pcopy(a):
+        r = twins.root(a)
+        if cp._PINNED.owns(r) and 8 * a.nbytes >= 7 * r.nbytes:
+            return a
+        return reference_pcopy(a)
+    return _pcopy
 
 
 def from_torch(t, n=None):
@@ -94,13 +123,7 @@ class GPUQuant:
             if device:
                 res = [from_torch(y) for y in ys]
             else:
-                whole = ys[0]._base if ys and ys[0]._base is not None else None
-                if whole is not None and all(y._base is whole for y in ys):
-                    end = max(y.storage_offset() + y.numel() for y in ys)
-                    host = to_host(from_torch(whole, end))
-                    res = [host[y.storage_offset():y.storage_offset() + y.numel()] for y in ys]
-                else:
-                    res = [to_host(from_torch(y)) for y in ys]
+                res = _download(ys)
             for k, r in enumerate(res):
                 if on_result:
                     on_result(i + k, r)
