@@ -256,22 +256,43 @@ __global__ void __launch_bounds__(128) k_r2_rowstat(const unsigned short* __rest
         rfi[r] = (short)fmin(fmax(rint(rf * 8.0), -32768.0), 32767.0);
     }
 }
-// per (row chunk, column): float64 sums of v^2 and v over the chunk's rows in row order, v = weight / rfa[row] in float32
+// per (row chunk, column): float64 sums of v^2 and v over the chunk's rows in row order, v = weight / rfa[row] in float32.
+// The sums are one dependent chain per column by format; what does not depend on the chain (load, the IEEE division,
+// the conversion) is done by all 256 threads of a CTA for a tile of 64 rows x 32 columns into shared memory, and the
+// first warp then extends its 32 columns' chains over the tile while the other warps fetch the next one.
 __global__ void __launch_bounds__(256) k_r2_colpart(const unsigned short* __restrict__ w, int nrows, int rowlen, int step,
                                                     const float* __restrict__ rfa, double* __restrict__ part) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    constexpr int TR = 64, TC = 32;
+    __shared__ float tile[2][TR][TC + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * TC + lane;
     const int q = blockIdx.y;
-    if (c >= rowlen) return;
     const int r0 = q * step, r1 = min(nrows, r0 + step);
+    const bool live = c < rowlen;
     double s2 = 0.0, s1 = 0.0;
-    for (int r = r0; r < r1; ++r) {
-        const float f = __fdiv_rn(__uint_as_float((unsigned)w[(size_t)r * rowlen + c] << 16), rfa[r]);
-        const double v = (double)f;
-        s2 = s2 + v * v;
-        s1 = s1 + v;
+    int buf = 0;
+    for (int t0 = r0; t0 < r1; t0 += TR, buf ^= 1) {
+#pragma unroll
+        for (int j = 0; j < TR / 8; ++j) {
+            const int r = t0 + warp + 8 * j;
+            float f = 0.0f;
+            if (live && r < r1) f = __fdiv_rn(__uint_as_float((unsigned)w[(size_t)r * rowlen + c] << 16), rfa[r]);
+            tile[buf][warp + 8 * j][lane] = f;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            const int n = min(TR, r1 - t0);
+            for (int i = 0; i < n; ++i) {
+                const double v = (double)tile[buf][i][lane];
+                s2 = s2 + v * v;
+                s1 = s1 + v;
+            }
+        }
     }
-    part[((size_t)q * rowlen + c) * 2] = s2;
-    part[((size_t)q * rowlen + c) * 2 + 1] = s1;
+    if (warp == 0 && live) {
+        part[((size_t)q * rowlen + c) * 2] = s2;
+        part[((size_t)q * rowlen + c) * 2 + 1] = s1;
+    }
 }
 __global__ void __launch_bounds__(256) k_r2_colfinal(const double* __restrict__ part, int nchunks, int nrows, int rowlen,
                                                      short* __restrict__ cfi, signed char* __restrict__ scl) {
@@ -415,7 +436,7 @@ extern "C" int sg_r2_stats(int device, void* stream, const void* w, int nrows, i
     float* rfa = (float*)scratch;
     double* part = (double*)((unsigned char*)scratch + ((size_t)nrows * 4 + 255) / 256 * 256);
     k_r2_rowstat<<<(nrows + 3) / 4, 128, 0, st>>>((const unsigned short*)w, nrows, rowlen, rfi, rfa);
-    k_r2_colpart<<<dim3((rowlen + 255) / 256, nchunks), 256, 0, st>>>((const unsigned short*)w, nrows, rowlen, step, rfa, part);
+    k_r2_colpart<<<dim3((rowlen + 31) / 32, nchunks), 256, 0, st>>>((const unsigned short*)w, nrows, rowlen, step, rfa, part);
     k_r2_colfinal<<<(rowlen + 255) / 256, 256, 0, st>>>(part, nchunks, nrows, rowlen, cfi, scl);
     return cuda_ok(cudaGetLastError());
 }
