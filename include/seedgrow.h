@@ -166,6 +166,10 @@ SG_API int sg_residual_blocks(int device, void *stream, const void *file, const 
  * sg_rans_tables  frequencies [ntab][256] (each used row summing to 2^pb) -> encoder entries enc_tab
  *                 (8 bytes per (table, symbol): reciprocal, freq | cum << 16) and, if lut != NULL, the decoder's
  *                 symbol-per-slot table [ntab << pb]                                     (cum_of gpu2.py:483-486, build_lut qr.py:889-895)
+ *                 For pb = 15 `lut` is the R2 decoder's compact table instead, 1280 bytes per table [ntab * 1280]:
+ *                 256 coarse entries (entry b = the symbol whose range holds slot 128 * b) and the 256 symbols'
+ *                 freq | cum << 16 words; the decoder walks on from the coarse entry (32 KiB of slots per table would
+ *                 not stay in the SM's cache, this does).
  * sg_rans_encode  every segment into its private slot of `cap` bytes (multiple of 16, >= 128), written from the
  *                 slot's end downwards; out_len[s] = bytes used, 0xffffffff = slot too small   (qr_enc's framing, qr.py:712-758)
  * sg_scan_gather  off[0..nseg] = exclusive prefix sum of out_len (off[nseg] = total), then the segments' bytes

@@ -44,7 +44,7 @@ struct Cursor {
 SG_DEVINL void contexts(const Ctx& c, const TB& T, int orow, int j, int& pred, int& pe, int& sc) {
     pred = c.rfi[T.rowbase + orow] + c.cfi[T.colbase + j];
     pe = clampi(pred + 256, 0, 511);
-    sc = c.scl[T.colbase + j];
+    sc = clampi(c.scl[T.colbase + j], 0, 15);         // (0..15 by construction, bf16v2.py:243; a damaged side part must not index past the tables)
 }
 SG_DEVINL int mctx(int ex, int pred) { return clampi(8 * ex - pred - 1016 + 64, 0, 127); }
 
@@ -167,29 +167,75 @@ __global__ void __launch_bounds__(TPB) k_r2_enc(const unsigned char* __restrict_
     out_len[s] = wr.bad ? LEN_NOFREQ : (unsigned)(slot + cap - wr.ptr());
 }
 
-__global__ void __launch_bounds__(TPB) k_r2_dec(const unsigned char* __restrict__ in, const unsigned long long* __restrict__ in_off,
-                                                const unsigned long long* __restrict__ in_end, unsigned char* __restrict__ dev,
-                                                const TB* __restrict__ tb, const SG* __restrict__ sg, int nseg, Ctx c,
-                                                const RansSym* __restrict__ enc, const unsigned char* __restrict__ lut, int* __restrict__ status) {
-    const int s = blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= nseg) return;
-    const SG g = sg[s];
-    Cursor q; q.seek(dev, tb[g.t], g.i0, c.rowmap);
-    ByteReaderUp rd; rd.init(in + in_off[s], in + in_end[s]);
-    unsigned x = rans_init(rd);
-    for (int k = 0; k < g.n; ++k) {
-        int pred, pe, sc; contexts(c, q.T, q.orow, q.j, pred, pe, sc);
-        const int t0 = q.T.tab + pe;
-        const int ex = (int)rans_get<PB>(x, rd, lut + ((size_t)t0 << PB), enc + (size_t)t0 * 256);
-        const int t1 = q.T.tab + 512 + mctx(ex, pred);
-        const int man = (int)rans_get<PB>(x, rd, lut + ((size_t)t1 << PB), enc + (size_t)t1 * 256);
-        const int t2 = q.T.tab + 640 + sc;
-        const int sgn = (int)rans_get<PB>(x, rd, lut + ((size_t)t2 << PB), enc + (size_t)t2 * 256);
-        const_cast<unsigned short*>(q.w)[q.j] = (unsigned short)((sgn << 15) | (ex << 7) | man);
-        if (rd.over) break;
-        if (++q.j == q.T.rowlen) { q.j = 0; ++q.rc; if (k + 1 < g.n) q.row(dev, c.rowmap); }
+// Decoder: a segment is one rANS chain by format, but what a weight's symbols are decoded WITH - the exponent's and the
+// sign's tables, the prediction the mantissa's table is picked by - depends on its row and column only.  Eight lanes
+// share a segment: for every 32 weights they look the contexts up side by side (four weights each) into shared memory,
+// lane 0 then runs the chain over the staged contexts - three table walks per weight and nothing else - and all eight
+// store the 32 decoded weights.  Four segments per warp decode in lockstep.
+constexpr int DG = 8, DB = 32, DSEG = 16;          // lanes per segment, weights per batch, segments per CTA
+__global__ void __launch_bounds__(DG * DSEG) k_r2_dec(const unsigned char* __restrict__ in, const unsigned long long* __restrict__ in_off,
+                                                      const unsigned long long* __restrict__ in_end, unsigned char* __restrict__ dev,
+                                                      const TB* __restrict__ tb, const SG* __restrict__ sg, int nseg, Ctx c,
+                                                      const RansSym* __restrict__ enc, const unsigned char* __restrict__ lut, int* __restrict__ status) {
+    __shared__ int s_t0[DSEG][DB], s_pred[DSEG][DB], s_t2[DSEG][DB];
+    __shared__ unsigned short s_out[DSEG][DB];
+    const int grp = threadIdx.x / DG, gl = threadIdx.x % DG;
+    const int s = blockIdx.x * DSEG + grp;
+    const bool live = s < nseg;
+    SG g; g.t = 0; g.n = 0; g.i0 = 0;
+    if (live) g = sg[s];
+    const TB T = tb[g.t];
+    int nmax = g.n;
+    for (int o = 16; o; o >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, o));
+    ByteReaderUp rd; rd.over = false; rd.p = rd.end = nullptr;
+    unsigned x = RANS_L;
+    if (live && gl == 0) { rd.init(in + in_off[s], in + in_end[s]); x = rans_init(rd); }
+    unsigned short* base = reinterpret_cast<unsigned short*>(dev + T.doff);
+    // this lane's first weight of the batch: compact row rc, column j; 32 weights further every batch
+    int rc = 0, j = 0;
+    if (live) { const long long i = g.i0 + 4 * gl; rc = (int)(i / T.rowlen); j = (int)(i % T.rowlen); }
+    bool bad = false;
+    for (int k0 = 0; k0 < nmax; k0 += DB) {
+        size_t at[4];
+        {
+            int r = rc, col = j, have = -1, orow = 0;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const int k = k0 + 4 * gl + v;
+                at[v] = 0;
+                if (live && k < g.n) {
+                    if (r != have) { orow = T.rmap >= 0 ? c.rowmap[T.rmap + r] : r; have = r; }
+                    int pred, pe, sc; contexts(c, T, orow, col, pred, pe, sc);
+                    s_t0[grp][4 * gl + v] = T.tab + pe; s_pred[grp][4 * gl + v] = pred; s_t2[grp][4 * gl + v] = T.tab + 640 + sc;
+                    at[v] = (size_t)orow * T.rowlen + col;
+                    if (++col == T.rowlen) { col = 0; ++r; }
+                }
+            }
+        }
+        __syncwarp();
+        if (live && gl == 0 && !bad) {
+            const int n = min(DB, g.n - k0);
+#pragma unroll 2
+            for (int w = 0; w < n; ++w) {
+                const int t0 = s_t0[grp][w], pred = s_pred[grp][w], t2 = s_t2[grp][w];
+                const int ex = (int)rans_get_compact<PB>(x, rd, lut + (size_t)t0 * RANS_COMPACT);
+                const int t1 = T.tab + 512 + mctx(ex, pred);
+                const int man = (int)rans_get_compact<PB>(x, rd, lut + (size_t)t1 * RANS_COMPACT);
+                const int sgn = (int)rans_get_bit<PB>(x, rd, lut + (size_t)t2 * RANS_COMPACT);
+                s_out[grp][w] = (unsigned short)((sgn << 15) | (ex << 7) | man);
+            }
+            bad = rd.over;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            const int k = k0 + 4 * gl + v;
+            if (live && k < g.n) base[at[v]] = s_out[grp][4 * gl + v];
+        }
+        j += DB;
+        if (live) while (j >= T.rowlen) { j -= T.rowlen; ++rc; }
     }
-    if (rd.over || x != RANS_L || rd.p != rd.end) atomicOr(status, SG_ST_CORRUPT);
+    if (live && gl == 0 && (bad || rd.over || x != RANS_L || rd.p != rd.end)) atomicOr(status, SG_ST_CORRUPT);
 }
 
 // 64-bit row fingerprints for duplicate-row detection (bf16v2.py:148-155): an order-dependent integer recurrence, one
@@ -388,12 +434,12 @@ extern "C" int sg_r2_decode(int device, void* stream, const unsigned char* in, c
     int rc = r2_common(dev, tb, sgp, nseg, rfi, cfi, scl);
     if (rc != SG_OK) return rc;
     if (!in || !in_off || !in_end || !enc_tab || !lut) return SG_ERR_ARG;
-    if ((uintptr_t)in % 16) return SG_ERR_ALIGN;
+    if ((uintptr_t)in % 16 || (uintptr_t)lut % 8) return SG_ERR_ALIGN;           // (the sign tables' two words are one 8-byte load)
     if (nseg == 0) return SG_OK;
     rc = use_device(device);
     if (rc != SG_OK) return rc;
     Ctx c = {rfi, cfi, scl, rowmap};
-    k_r2_dec<<<(nseg + TPB - 1) / TPB, TPB, 0, (cudaStream_t)stream>>>(in, in_off, in_end, dev, (const TB*)tb, (const SG*)sgp, nseg, c,
+    k_r2_dec<<<(nseg + DSEG - 1) / DSEG, DG * DSEG, 0, (cudaStream_t)stream>>>(in, in_off, in_end, dev, (const TB*)tb, (const SG*)sgp, nseg, c,
                                                                        (const RansSym*)enc_tab, lut, status_word(device));
     return cuda_ok(cudaGetLastError());
 }

@@ -41,8 +41,14 @@ __global__ void __launch_bounds__(256) k_rans_tables(const uint16_t* __restrict_
     } else e.rcp = 0xffffffffu;
     enc[t * 256 + s] = e;
     if (lut && whole) {               // any other row would write outside its 2^PB slots: its LUT is left alone
-        uint8_t* l = lut + ((size_t)t << pb);
-        for (unsigned i = c; i < incl; ++i) l[i] = (uint8_t)s;
+        if (pb == 15) {               // compact: one entry per 128 slots (the decoder scans on from it), then the symbols' words
+            uint8_t* l = lut + (size_t)t * RANS_COMPACT;
+            for (unsigned b = (c + 127) >> 7; (b << 7) < incl; ++b) l[b] = (uint8_t)s;
+            reinterpret_cast<unsigned*>(l + 256)[s] = e.fc;
+        } else {
+            uint8_t* l = lut + ((size_t)t << pb);
+            for (unsigned i = c; i < incl; ++i) l[i] = (uint8_t)s;
+        }
     }
 }
 

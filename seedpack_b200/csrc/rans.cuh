@@ -67,26 +67,33 @@ struct ByteWriterDown {
 // and set `over`.
 struct ByteReaderUp {
     const uint8_t* win;            // aligned address of the loaded window
-    unsigned long long lo, hi;
+    unsigned long long lo, hi;     // the window
+    unsigned long long nlo, nhi;   // the window after it, fetched when this one was entered (its latency is off the chain)
     const uint8_t* p;
     const uint8_t* end;
     bool over;
-    SG_DEVINL void load() {
-        const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(win);
-        lo = v.x; hi = v.y;
+    SG_DEVINL void fetch_next() {
+        if (win + 16 < end) {
+            const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(win + 16);
+            nlo = v.x; nhi = v.y;
+        }
     }
     SG_DEVINL void init(const uint8_t* begin, const uint8_t* e) {
         p = begin; end = e; over = false;
         win = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(begin) & ~(uintptr_t)15);
-        lo = hi = 0;
-        if (begin < e) load();
+        lo = hi = nlo = nhi = 0;
+        if (begin < e) {
+            const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(win);
+            lo = v.x; hi = v.y;
+            fetch_next();
+        }
     }
     SG_DEVINL unsigned get() {
         if (p >= end) { over = true; return 0; }
         const int k = (int)(p - win);
         const unsigned b = (unsigned)((k >= 8 ? hi >> (8 * (k - 8)) : lo >> (8 * k)) & 0xff);
         ++p;
-        if (k == 15) { win += 16; if (win < end) load(); }
+        if (k == 15) { win += 16; lo = nlo; hi = nhi; fetch_next(); }
         return b;
     }
 };
@@ -119,6 +126,36 @@ SG_DEVINL unsigned rans_get(unsigned& x, R& r, const uint8_t* __restrict__ lut, 
     const unsigned slot = x & ((1u << PB) - 1);
     const unsigned s = lut[slot];
     const unsigned fc = tab[s].fc;
+    x = (fc & 0xffffu) * (x >> PB) + slot - (fc >> 16);
+#pragma unroll 1
+    for (int guard = 0; guard < 4 && x < RANS_L; ++guard) x = (x << 8) | r.get();
+    return s;
+}
+
+// The same through a compact table (RANS_COMPACT bytes per context: 256 coarse entries, one per 2^(PB - 8) slots = the
+// symbol whose range holds the bucket's first slot, then the 256 symbols' freq | cum << 16 words) and a walk over the
+// words from the coarse entry: 1.25 KiB per context instead of 2^PB + 2 KiB.
+constexpr int RANS_COMPACT = 256 + 256 * 4;
+template <int PB, class R>
+SG_DEVINL unsigned rans_get_compact(unsigned& x, R& r, const uint8_t* __restrict__ ct) {
+    const unsigned* __restrict__ words = reinterpret_cast<const unsigned*>(ct + 256);
+    const unsigned slot = x & ((1u << PB) - 1);
+    unsigned s = ct[slot >> (PB - 8)];
+    unsigned fc = words[s];
+#pragma unroll 1
+    while (slot >= (fc >> 16) + (fc & 0xffffu) && s < 255u) fc = words[++s];
+    x = (fc & 0xffffu) * (x >> PB) + slot - (fc >> 16);
+#pragma unroll 1
+    for (int guard = 0; guard < 4 && x < RANS_L; ++guard) x = (x << 8) | r.get();
+    return s;
+}
+// a table of two symbols (a sign): both words in one 8-byte load, no coarse entry
+template <int PB, class R>
+SG_DEVINL unsigned rans_get_bit(unsigned& x, R& r, const uint8_t* __restrict__ ct) {
+    const unsigned slot = x & ((1u << PB) - 1);
+    const uint2 e = *reinterpret_cast<const uint2*>(ct + 256);
+    const unsigned s = slot >= (e.x & 0xffffu) ? 1u : 0u;
+    const unsigned fc = s ? e.y : e.x;
     x = (fc & 0xffffu) * (x >> PB) + slot - (fc >> 16);
 #pragma unroll 1
     for (int guard = 0; guard < 4 && x < RANS_L; ++guard) x = (x << 8) | r.get();

@@ -77,7 +77,7 @@ def _tables(remap, freq, pb, lut):
     if used.numel():
         full[used] = f[r[used]]
     enc = torch.empty(ntab * 256 * 2, dtype=torch.int32, device=f.device)
-    l = torch.empty(ntab << pb, dtype=torch.uint8, device=f.device) if lut else None
+    l = torch.zeros(ntab * 1280 if pb == 15 else ntab << pb, dtype=torch.uint8, device=f.device) if lut else None
     _lib.check(_lib.lib().sg_rans_tables(_dev(), _st(), _p(full), ntab, pb, _p(enc), _p(l)), "sg_rans_tables")
     _TABS[key] = (enc, l, remap, freq)           # the source arrays stay alive with the entry: their ids stay theirs
     while len(_TABS) > 6:
