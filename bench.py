@@ -354,7 +354,8 @@ def _bench_tmp():
     d = os.environ.get("SEEDGROW_BENCH_TMP")
     if not d:
         try:
-            d = "/dev/shm" if shutil.disk_usage("/dev/shm").free > (12 << 30) else None
+            world = int(os.environ.get("WORLD_SIZE", "1"))          # every rank keeps a repository, its archive and an unpacked copy
+            d = "/dev/shm" if shutil.disk_usage("/dev/shm").free > (8 << 30) * world + (4 << 30) else None
         except OSError:
             d = None
     return tempfile.mkdtemp(prefix="seedgrow-bench-", dir=d)
