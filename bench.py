@@ -682,15 +682,26 @@ def run_shard(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    from concurrent.futures import ThreadPoolExecutor
+    pool = ThreadPoolExecutor(2)
+
     def step():
-        h = hashlib.sha256()
-        nd = 0
-        for T in types:
-            buf, d = batches[T].run()
+        """every batch of the window; batch k is framed by rank k mod N, in a thread beside the next batch's GPU work.
+        -> (SHA-256 over the batches' SHA-256 digests in batch order: the same at every N, bytes that differ)"""
+        mine, nd = {}, 0
+        for k, T in enumerate(types):
+            fut, d = batches[T].run(root=k % world, pool=pool)
             nd += d
-            if buf is not None:
-                h.update(buf)
-        return h.hexdigest(), nd
+            if fut is not None:
+                mine[k] = fut
+        mine = {k: hashlib.sha256(f.result()).digest() for k, f in mine.items()}
+        if world > 1:
+            parts = [None] * world if rank == 0 else None
+            dist.gather_object(mine, parts, dst=0, group=group)
+            if rank != 0:
+                return None, nd
+            mine = {k: v for p in parts for k, v in p.items()}
+        return hashlib.sha256(b"".join(mine[k] for k in range(len(types)))).hexdigest(), nd
 
     for _ in range(args.warmup):
         step()

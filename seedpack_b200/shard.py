@@ -53,14 +53,15 @@ def sum_counts(counts, group=None):
     return t.numpy()
 
 
-def gather_segments(lens, stream, group=None):
-    """this rank's segment lengths (uint32 array, in segment order) and their bytes -> on rank 0 the lengths and the
-    stream of the whole batch in rank order (ranks own contiguous segment ranges), elsewhere (None, None)"""
+def gather_segments(lens, stream, group=None, dst=0):
+    """this rank's segment lengths (uint32 array, in segment order) and their bytes -> on rank `dst` (of the group) the
+    lengths and the stream of the whole batch in rank order (ranks own contiguous segment ranges), elsewhere (None, None)"""
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return np.asarray(lens, np.uint32), bytes(stream)
     world, rank = dist.get_world_size(group), dist.get_rank(group)
-    gathered = [None] * world if rank == 0 else None
-    dist.gather_object((np.asarray(lens, np.uint32), bytes(stream)), gathered, dst=0, group=group)
-    if rank != 0:
+    gathered = [None] * world if rank == dst else None
+    dist.gather_object((np.asarray(lens, np.uint32), bytes(stream)), gathered,
+                       dst=dist.get_global_rank(group, dst) if group is not None else dst, group=group)
+    if rank != dst:
         return None, None
     return np.concatenate([g[0] for g in gathered]), b"".join(g[1] for g in gathered)

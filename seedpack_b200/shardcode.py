@@ -127,8 +127,11 @@ class ShardedBatch:
         torch.cuda.synchronize(self.device)
         return self
 
-    def run(self):
-        """-> (the batch's bytes on rank 0, None elsewhere; bytes of this rank's blocks that differ from their prediction)"""
+    def run(self, root=0, pool=None):
+        """-> (the batch's bytes on rank `root`, None elsewhere; bytes of this rank's blocks that differ from their
+        prediction).  With `pool` (a thread pool) the framing of the batch - level-19 zstd of its tables, host work that
+        no other rank can help with - is handed to it and a future of the bytes comes back, so that the caller can go
+        on to the next batch's GPU work; giving successive batches different roots spreads that work over the ranks"""
         T, bs, qk = self.T, BS[self.T], QK[self.T]
         use_imx = T in GRID_TYPES
         imxs = [self.imx[o:o + len(w)] for o, w in zip(self.imx_offs, self.case["imx"])]
@@ -146,10 +149,12 @@ class ShardedBatch:
         state, counts = self.qc.hist(T, items, self.seed.view(torch.uint8), self.imx if use_imx else None, MODEL, self.segs)
         freq, used = normalize(shard.sum_counts(counts, self.group))
         lens, stream = self.qc.code(state, freq, used)
-        lens, stream = shard.gather_segments(lens, stream, self.group)
+        lens, stream = shard.gather_segments(lens, stream, self.group, dst=root)
         ndiff = int(sum(int(d.item()) for d in differ))
         if lens is None:
             return None, ndiff
+        if pool is not None:
+            return pool.submit(self.qc.finish, freq, used, lens, stream, MODEL), ndiff
         return self.qc.finish(freq, used, lens, stream, MODEL), ndiff
 
 
