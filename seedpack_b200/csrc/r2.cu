@@ -129,42 +129,75 @@ __global__ void __launch_bounds__(R2H_WARPS * 32) k_r2_hist(const unsigned char*
         }
 }
 
-__global__ void __launch_bounds__(TPB) k_r2_enc(const unsigned char* __restrict__ dev, const TB* __restrict__ tb, const SG* __restrict__ sg,
-                                                int nseg, Ctx c, const RansSym* __restrict__ enc, unsigned char* __restrict__ out, size_t cap,
-                                                unsigned* __restrict__ out_len) {
-    const int s = blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= nseg) return;
-    const SG g = sg[s];
-    Cursor q; q.seek(dev, tb[g.t], g.i0 + g.n - 1, c.rowmap);
-    unsigned char* slot = out + (size_t)s * cap;
+// Encoder: eight lanes per segment, like the decoder below.  The table entries of a weight's three symbols depend on the
+// data only, not on the coder state: for every 32 weights (taken from the segment's end backwards) the eight lanes look
+// them up side by side into shared memory, and lane 0 runs the chain over the 96 staged entries.
+constexpr int EG = 8, EB = 32, ESEG = 16;          // lanes per segment, weights per batch, segments per CTA
+__global__ void __launch_bounds__(EG * ESEG) k_r2_enc(const unsigned char* __restrict__ dev, const TB* __restrict__ tb, const SG* __restrict__ sg,
+                                                      int nseg, Ctx c, const RansSym* __restrict__ enc, unsigned char* __restrict__ out, size_t cap,
+                                                      unsigned* __restrict__ out_len) {
+    __shared__ RansSym s_e[ESEG][EB][3];           // per weight of the batch: sign, mantissa, exponent entries (coding order)
+    const int grp = threadIdx.x / EG, gl = threadIdx.x % EG;
+    const int s = blockIdx.x * ESEG + grp;
+    const bool live = s < nseg;
+    SG g; g.t = 0; g.n = 0; g.i0 = 0;
+    if (live) g = sg[s];
+    const TB T = tb[g.t];
+    int nmax = g.n;
+    for (int o = 16; o; o >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, o));
+    unsigned char* slot = out + (size_t)(live ? s : 0) * cap;
     ByteWriterDown wr; wr.init(slot + cap);
     unsigned x = RANS_L;
-    // four weights at a time: their table entries depend on the data only, not on the coder state, so the twelve loads
-    // are issued before the twelve coding steps that chain through x
-    for (int k = g.n - 1; k >= 0; k -= 4) {
-        RansSym e[4][3];
-        const int nv = k + 1 < 4 ? k + 1 : 4;
+    bool full = false;
+    const unsigned short* base = reinterpret_cast<const unsigned short*>(dev + T.doff);
+    // batches of 32 weights, the last one first; this lane's first weight of the batch: compact row rc, column j
+    const int nb_max = (nmax + EB - 1) / EB;
+    int rc = 0, j = 0;
+    {
+        const long long i = g.i0 + (long long)(nb_max - 1) * EB + 4 * gl;
+        if (live) { rc = (int)(i / T.rowlen); j = (int)(i % T.rowlen); }
+    }
+    for (int b = nb_max - 1; b >= 0; --b) {
+        const int k0 = b * EB;
+        {
+            int r = rc, col = j, have = -1, orow = 0;
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-            if (v < nv) {
-                const unsigned u = q.w[q.j];
-                const int ex = (u >> 7) & 255, man = u & 127, sgn = u >> 15;
-                int pred, pe, sc; contexts(c, q.T, q.orow, q.j, pred, pe, sc);
-                e[v][0] = enc[(size_t)(q.T.tab + 640 + sc) * 256 + sgn];
-                e[v][1] = enc[(size_t)(q.T.tab + 512 + mctx(ex, pred)) * 256 + man];
-                e[v][2] = enc[(size_t)(q.T.tab + pe) * 256 + ex];
-                if (--q.j < 0) { q.j = q.T.rowlen - 1; --q.rc; if (k - v > 0) q.row(dev, c.rowmap); }
+            for (int v = 0; v < 4; ++v) {
+                const int k = k0 + 4 * gl + v;
+                if (live && k < g.n) {
+                    if (r != have) { orow = T.rmap >= 0 ? c.rowmap[T.rmap + r] : r; have = r; }
+                    const unsigned u = base[(size_t)orow * T.rowlen + col];
+                    const int ex = (u >> 7) & 255, man = u & 127, sgn = u >> 15;
+                    int pred, pe, sc; contexts(c, T, orow, col, pred, pe, sc);
+                    s_e[grp][4 * gl + v][0] = enc[(size_t)(T.tab + 640 + sc) * 256 + sgn];
+                    s_e[grp][4 * gl + v][1] = enc[(size_t)(T.tab + 512 + mctx(ex, pred)) * 256 + man];
+                    s_e[grp][4 * gl + v][2] = enc[(size_t)(T.tab + pe) * 256 + ex];
+                    if (++col == T.rowlen) { col = 0; ++r; }
+                }
             }
         }
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-            if (v < nv) { rans_put<PB>(x, wr, e[v][0]); rans_put<PB>(x, wr, e[v][1]); rans_put<PB>(x, wr, e[v][2]); }
+        __syncwarp();
+        if (live && gl == 0 && !full && k0 < g.n) {
+            const int n = min(EB, g.n - k0);
+            for (int w = n - 1; w >= 0; --w) {
+                rans_put<PB>(x, wr, s_e[grp][w][0]);
+                rans_put<PB>(x, wr, s_e[grp][w][1]);
+                rans_put<PB>(x, wr, s_e[grp][w][2]);
+                if ((w & 3) == 0 && wr.ptr() < slot + 64) { full = true; break; }
+            }
         }
-        if (wr.ptr() < slot + 64) { out_len[s] = 0xffffffffu; return; }
+        __syncwarp();
+        j -= EB;
+        if (live) while (j < 0) { j += T.rowlen; --rc; }
     }
-    rans_flush(x, wr);
-    wr.flush(slot);
-    out_len[s] = wr.bad ? LEN_NOFREQ : (unsigned)(slot + cap - wr.ptr());
+    if (live && gl == 0) {
+        if (full) out_len[s] = LEN_OVERFLOW;
+        else {
+            rans_flush(x, wr);
+            wr.flush(slot);
+            out_len[s] = wr.bad ? LEN_NOFREQ : (unsigned)(slot + cap - wr.ptr());
+        }
+    }
 }
 
 // Decoder: a segment is one rANS chain by format, but what a weight's symbols are decoded WITH - the exponent's and the
@@ -423,7 +456,7 @@ extern "C" int sg_r2_encode(int device, void* stream, const unsigned char* dev, 
     rc = use_device(device);
     if (rc != SG_OK) return rc;
     Ctx c = {rfi, cfi, scl, rowmap};
-    k_r2_enc<<<(nseg + TPB - 1) / TPB, TPB, 0, (cudaStream_t)stream>>>(dev, (const TB*)tb, (const SG*)sgp, nseg, c, (const RansSym*)enc_tab,
+    k_r2_enc<<<(nseg + ESEG - 1) / ESEG, EG * ESEG, 0, (cudaStream_t)stream>>>(dev, (const TB*)tb, (const SG*)sgp, nseg, c, (const RansSym*)enc_tab,
                                                                        slots, cap, out_len);
     return cuda_ok(cudaGetLastError());
 }
