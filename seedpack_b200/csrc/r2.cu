@@ -129,10 +129,11 @@ __global__ void __launch_bounds__(R2H_WARPS * 32) k_r2_hist(const unsigned char*
         }
 }
 
-// Encoder: eight lanes per segment, like the decoder below.  The table entries of a weight's three symbols depend on the
-// data only, not on the coder state: for every 32 weights (taken from the segment's end backwards) the eight lanes look
-// them up side by side into shared memory, and lane 0 runs the chain over the 96 staged entries.
-constexpr int EG = 8, EB = 32, ESEG = 16;          // lanes per segment, weights per batch, segments per CTA
+// Encoder: a few lanes per segment, like the decoder below.  The table entries of a weight's three symbols depend on the
+// data only, not on the coder state: for every 32 weights (taken from the segment's end backwards) the lanes look
+// them up side by side into shared memory, and lane 0 runs the chain over the 96 staged entries.  Four lanes per segment:
+// the chain is what a warp spends its issue slots on, and a warp instruction of the chain then serves eight segments.
+constexpr int EG = 4, EB = 32, ESEG = 32, EW = EB / EG;          // lanes per segment, weights per batch, segments per CTA, weights per lane
 __global__ void __launch_bounds__(EG * ESEG) k_r2_enc(const unsigned char* __restrict__ dev, const TB* __restrict__ tb, const SG* __restrict__ sg,
                                                       int nseg, Ctx c, const RansSym* __restrict__ enc, unsigned char* __restrict__ out, size_t cap,
                                                       unsigned* __restrict__ out_len) {
@@ -154,7 +155,7 @@ __global__ void __launch_bounds__(EG * ESEG) k_r2_enc(const unsigned char* __res
     const int nb_max = (nmax + EB - 1) / EB;
     int rc = 0, j = 0;
     {
-        const long long i = g.i0 + (long long)(nb_max - 1) * EB + 4 * gl;
+        const long long i = g.i0 + (long long)(nb_max - 1) * EB + EW * gl;
         if (live) { rc = (int)(i / T.rowlen); j = (int)(i % T.rowlen); }
     }
     for (int b = nb_max - 1; b >= 0; --b) {
@@ -162,16 +163,16 @@ __global__ void __launch_bounds__(EG * ESEG) k_r2_enc(const unsigned char* __res
         {
             int r = rc, col = j, have = -1, orow = 0;
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-                const int k = k0 + 4 * gl + v;
+            for (int v = 0; v < EW; ++v) {
+                const int k = k0 + EW * gl + v;
                 if (live && k < g.n) {
                     if (r != have) { orow = T.rmap >= 0 ? c.rowmap[T.rmap + r] : r; have = r; }
                     const unsigned u = base[(size_t)orow * T.rowlen + col];
                     const int ex = (u >> 7) & 255, man = u & 127, sgn = u >> 15;
                     int pred, pe, sc; contexts(c, T, orow, col, pred, pe, sc);
-                    s_e[grp][4 * gl + v][0] = enc[(size_t)(T.tab + 640 + sc) * 256 + sgn];
-                    s_e[grp][4 * gl + v][1] = enc[(size_t)(T.tab + 512 + mctx(ex, pred)) * 256 + man];
-                    s_e[grp][4 * gl + v][2] = enc[(size_t)(T.tab + pe) * 256 + ex];
+                    s_e[grp][EW * gl + v][0] = enc[(size_t)(T.tab + 640 + sc) * 256 + sgn];
+                    s_e[grp][EW * gl + v][1] = enc[(size_t)(T.tab + 512 + mctx(ex, pred)) * 256 + man];
+                    s_e[grp][EW * gl + v][2] = enc[(size_t)(T.tab + pe) * 256 + ex];
                     if (++col == T.rowlen) { col = 0; ++r; }
                 }
             }
@@ -201,11 +202,11 @@ __global__ void __launch_bounds__(EG * ESEG) k_r2_enc(const unsigned char* __res
 }
 
 // Decoder: a segment is one rANS chain by format, but what a weight's symbols are decoded WITH - the exponent's and the
-// sign's tables, the prediction the mantissa's table is picked by - depends on its row and column only.  Eight lanes
-// share a segment: for every 32 weights they look the contexts up side by side (four weights each) into shared memory,
-// lane 0 then runs the chain over the staged contexts - three table walks per weight and nothing else - and all eight
-// store the 32 decoded weights.  Four segments per warp decode in lockstep.
-constexpr int DG = 8, DB = 32, DSEG = 16;          // lanes per segment, weights per batch, segments per CTA
+// sign's tables, the prediction the mantissa's table is picked by - depends on its row and column only.  Four lanes
+// share a segment: for every 32 weights they look the contexts up side by side (eight weights each) into shared memory,
+// lane 0 then runs the chain over the staged contexts - three table walks per weight and nothing else - and all four
+// store the 32 decoded weights.  Eight segments per warp decode in lockstep.
+constexpr int DG = 4, DB = 32, DSEG = 32, DW = DB / DG;          // lanes per segment, weights per batch, segments per CTA, weights per lane
 __global__ void __launch_bounds__(DG * DSEG) k_r2_dec(const unsigned char* __restrict__ in, const unsigned long long* __restrict__ in_off,
                                                       const unsigned long long* __restrict__ in_end, unsigned char* __restrict__ dev,
                                                       const TB* __restrict__ tb, const SG* __restrict__ sg, int nseg, Ctx c,
@@ -226,20 +227,20 @@ __global__ void __launch_bounds__(DG * DSEG) k_r2_dec(const unsigned char* __res
     unsigned short* base = reinterpret_cast<unsigned short*>(dev + T.doff);
     // this lane's first weight of the batch: compact row rc, column j; 32 weights further every batch
     int rc = 0, j = 0;
-    if (live) { const long long i = g.i0 + 4 * gl; rc = (int)(i / T.rowlen); j = (int)(i % T.rowlen); }
+    if (live) { const long long i = g.i0 + DW * gl; rc = (int)(i / T.rowlen); j = (int)(i % T.rowlen); }
     bool bad = false;
     for (int k0 = 0; k0 < nmax; k0 += DB) {
-        size_t at[4];
+        size_t at[DW];
         {
             int r = rc, col = j, have = -1, orow = 0;
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-                const int k = k0 + 4 * gl + v;
+            for (int v = 0; v < DW; ++v) {
+                const int k = k0 + DW * gl + v;
                 at[v] = 0;
                 if (live && k < g.n) {
                     if (r != have) { orow = T.rmap >= 0 ? c.rowmap[T.rmap + r] : r; have = r; }
                     int pred, pe, sc; contexts(c, T, orow, col, pred, pe, sc);
-                    s_t0[grp][4 * gl + v] = T.tab + pe; s_pred[grp][4 * gl + v] = pred; s_t2[grp][4 * gl + v] = T.tab + 640 + sc;
+                    s_t0[grp][DW * gl + v] = T.tab + pe; s_pred[grp][DW * gl + v] = pred; s_t2[grp][DW * gl + v] = T.tab + 640 + sc;
                     at[v] = (size_t)orow * T.rowlen + col;
                     if (++col == T.rowlen) { col = 0; ++r; }
                 }
@@ -261,9 +262,9 @@ __global__ void __launch_bounds__(DG * DSEG) k_r2_dec(const unsigned char* __res
         }
         __syncwarp();
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-            const int k = k0 + 4 * gl + v;
-            if (live && k < g.n) base[at[v]] = s_out[grp][4 * gl + v];
+        for (int v = 0; v < DW; ++v) {
+            const int k = k0 + DW * gl + v;
+            if (live && k < g.n) base[at[v]] = s_out[grp][DW * gl + v];
         }
         j += DB;
         if (live) while (j >= T.rowlen) { j -= T.rowlen; ++rc; }
