@@ -608,8 +608,14 @@ def pack_roofline(per, dom, args, peak, peak_kind, clocks, base_bytes=0, coded_b
     algo = {"sg_r2_stats": 3 * base_bytes, "sg_r2_decode": base_bytes + coded_bytes, "sg_r2_encode": base_bytes + coded_bytes,
             "sg_r2_hist": base_bytes, "sg_row_hash": base_bytes}.get(dom)
     ach = algo / (per[dom]["ms"] * 1e-3) / 1e9 if algo else None
+    # DRAM bytes per algorithmic byte from the ncu capture of a smaller case of the same kernel (profiles/), scaled to
+    # this step's launches by the bytes they process
+    ratio = {"sg_r2_decode": 0.742}.get(dom)
+    traffic = ratio * algo / per[dom]["calls"] if ratio and algo else None
     return {"bound": "hbm", "kernel": f"{dom} ({per[dom]['calls']} calls per step)", "achieved": ach, "peak": peak, "peak_kind": peak_kind,
-            "unit": "GB/s", "frac": ach / peak if ach else None, "traffic": None,
+            "unit": "GB/s", "frac": ach / peak if ach else None, "traffic": traffic,
+            "traffic_from": "profiles/r2_decode_ncu_full.md: 123.5 MB of DRAM traffic for 166.6 MB of algorithmic bytes on one 4096 x 12288 "
+                            "tensor, scaled by the bytes of a launch here" if traffic else None,
             "share_of_device_time": round(per[dom]["ms"] / max(sum(v["ms"] for v in per.values()), 1e-9), 3),
             "note": "the step is bound by the host pipeline (device time is a small part of the wall clock); the kernel-level "
                     "rooflines are under `kernels`"}
