@@ -18,9 +18,9 @@ test.  Metric: GB/s of GGUF bytes, pack and unpack.
     python bench.py --workload quant | rans | qr | r2      (kernel-level workloads: the quantiser sweep over one
                                                             4096 x 12288 tensor and 25 types; the coders)
 
-Multi-GPU (`pack`): the repository's derived files are dealt out to the ranks (a file's chunks depend only on the
-base and on that file), every rank packs and tests its share, timed by wall clock, maximum over ranks; rank 0's
-line carries a digest over all ranks' per-file chunks, which does not depend on N.
+Multi-GPU (`pack`): every rank packs and tests a repository of its own (seed 1 + rank) on its GPU - weak scaling, the
+maximum over the ranks' times; no collective on the data path.  `--workload shard` cuts ONE window of tensors over the
+ranks by rANS segment (strong scaling; the digest of the coded batches does not depend on N).
 """
 import argparse
 import json
