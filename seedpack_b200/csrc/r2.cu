@@ -137,7 +137,9 @@ constexpr int EG = 4, EB = 32, ESEG = 32, EW = EB / EG;          // lanes per se
 __global__ void __launch_bounds__(EG * ESEG) k_r2_enc(const unsigned char* __restrict__ dev, const TB* __restrict__ tb, const SG* __restrict__ sg,
                                                       int nseg, Ctx c, const RansSym* __restrict__ enc, unsigned char* __restrict__ out, size_t cap,
                                                       unsigned* __restrict__ out_len) {
-    __shared__ RansSym s_e[ESEG][EB][3];           // per weight of the batch: sign, mantissa, exponent entries (coding order)
+    // per weight of the batch: sign, mantissa, exponent entries (coding order); a row is padded by one entry so that the
+    // chain lanes of a warp's segments, which read the same weight of their rows together, hit different banks
+    __shared__ RansSym s_e[ESEG][EB * 3 + 1];
     const int grp = threadIdx.x / EG, gl = threadIdx.x % EG;
     const int s = blockIdx.x * ESEG + grp;
     const bool live = s < nseg;
@@ -170,9 +172,9 @@ __global__ void __launch_bounds__(EG * ESEG) k_r2_enc(const unsigned char* __res
                     const unsigned u = base[(size_t)orow * T.rowlen + col];
                     const int ex = (u >> 7) & 255, man = u & 127, sgn = u >> 15;
                     int pred, pe, sc; contexts(c, T, orow, col, pred, pe, sc);
-                    s_e[grp][EW * gl + v][0] = enc[(size_t)(T.tab + 640 + sc) * 256 + sgn];
-                    s_e[grp][EW * gl + v][1] = enc[(size_t)(T.tab + 512 + mctx(ex, pred)) * 256 + man];
-                    s_e[grp][EW * gl + v][2] = enc[(size_t)(T.tab + pe) * 256 + ex];
+                    s_e[grp][3 * (EW * gl + v)] = enc[(size_t)(T.tab + 640 + sc) * 256 + sgn];
+                    s_e[grp][3 * (EW * gl + v) + 1] = enc[(size_t)(T.tab + 512 + mctx(ex, pred)) * 256 + man];
+                    s_e[grp][3 * (EW * gl + v) + 2] = enc[(size_t)(T.tab + pe) * 256 + ex];
                     if (++col == T.rowlen) { col = 0; ++r; }
                 }
             }
@@ -181,9 +183,9 @@ __global__ void __launch_bounds__(EG * ESEG) k_r2_enc(const unsigned char* __res
         if (live && gl == 0 && !full && k0 < g.n) {
             const int n = min(EB, g.n - k0);
             for (int w = n - 1; w >= 0; --w) {
-                rans_put<PB>(x, wr, s_e[grp][w][0]);
-                rans_put<PB>(x, wr, s_e[grp][w][1]);
-                rans_put<PB>(x, wr, s_e[grp][w][2]);
+                rans_put<PB>(x, wr, s_e[grp][3 * w]);
+                rans_put<PB>(x, wr, s_e[grp][3 * w + 1]);
+                rans_put<PB>(x, wr, s_e[grp][3 * w + 2]);
                 if ((w & 3) == 0 && wr.ptr() < slot + 64) { full = true; break; }
             }
         }
@@ -211,8 +213,9 @@ __global__ void __launch_bounds__(DG * DSEG) k_r2_dec(const unsigned char* __res
                                                       const unsigned long long* __restrict__ in_end, unsigned char* __restrict__ dev,
                                                       const TB* __restrict__ tb, const SG* __restrict__ sg, int nseg, Ctx c,
                                                       const RansSym* __restrict__ enc, const unsigned char* __restrict__ lut, int* __restrict__ status) {
-    __shared__ int s_t0[DSEG][DB], s_pred[DSEG][DB], s_t2[DSEG][DB];
-    __shared__ unsigned short s_out[DSEG][DB];
+    // rows padded: the chain lanes of a warp's segments touch the same weight of their rows together
+    __shared__ int s_t0[DSEG][DB + 1], s_pred[DSEG][DB + 1], s_t2[DSEG][DB + 1];
+    __shared__ unsigned short s_out[DSEG][DB + 2];
     const int grp = threadIdx.x / DG, gl = threadIdx.x % DG;
     const int s = blockIdx.x * DSEG + grp;
     const bool live = s < nseg;
