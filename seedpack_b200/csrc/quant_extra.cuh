@@ -218,18 +218,18 @@ __global__ void __launch_bounds__(EX_TPB) k_quant_extra(const __grid_constant__ 
         }
         const float d = e8m0_half(e);
         // this lane's sixteen codes, weight j in bits 4j..4j+3; byte j of the block = code j of the even lane | code j of the odd lane << 4
-        unsigned long long codes = 0;
+        unsigned codes[2] = {0, 0};                               // weights 0..7, 8..15
         if (fp4_fast_ok(d, amax)) {
             Fp4Mid mid; mid.set(d);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) codes |= (unsigned long long)mid.pick(v[j]) << (4 * j);
+            for (int j = 0; j < 16; ++j) codes[j >> 3] |= mid.pick(v[j]) << (4 * (j & 7));
         } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) codes |= (unsigned long long)best_fp4(v[j], d) << (4 * j);
+            for (int j = 0; j < 16; ++j) codes[j >> 3] |= best_fp4(v[j], d) << (4 * (j & 7));
         }
         // the even lane writes bytes 0..7, the odd lane bytes 8..15: each needs that half of the other lane's codes
-        const unsigned mine = hf ? (unsigned)(codes >> 32) : (unsigned)codes;
-        const unsigned give = hf ? (unsigned)codes : (unsigned)(codes >> 32);
+        const unsigned mine = hf ? codes[1] : codes[0];
+        const unsigned give = hf ? codes[0] : codes[1];
         const unsigned got = __shfl_xor_sync(0xffffffffu, give, 1);
         const unsigned lo = hf ? got : mine, hi = hf ? mine : got;           // low nibbles come from the even lane
         if (hf == 0) o[17 * b] = (unsigned char)e;
