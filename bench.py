@@ -56,8 +56,8 @@ OPS = {"q6_K+imx": [186.2, 286.2], "iq2_xxs+imx": [695.1, 2780.0], "iq2_xs+imx":
        "iq4_xs+imx": [144.3, 650.9], "iq1_m+imx": [379.4, 1044.6], "q2_0+imx": [2.1, 13.7], "q4_0": [2.3, 17.0], "q4_1": [3.5, 20.0],
        "q5_0": [2.3, 20.1], "q5_1": [3.5, 20.2], "q2_K": [286.8, 445.3], "q3_K": [28.3, 115.1], "q4_K": [356.9, 522.5],
        "q5_K": [277.5, 419.6], "q6_K": [186.9, 285.7], "iq3_xxs": [1800.5, 4204.2], "iq4_nl": [140.6, 637.8], "iq3_s": [1281.3, 2860.3],
-       "iq2_s": [461.6, 1652.5], "iq4_xs": [145.5, 643.5], "iq1_m": [368.9, 996.0], "tq1_0": [2.3, 26.7], "tq2_0": [2.3, 24.4],
-       "mxfp4": [16.1, 88.9], "nvfp4": [16.6, 84.1], "q1_0": [1.0, 16.5], "q4_0+imx": [181.5, 251.4], "q4_1+imx": [646.9, 829.2],
+       "iq2_s": [461.6, 1652.5], "iq4_xs": [145.5, 643.5], "iq1_m": [368.9, 996.0], "tq1_0": [2.3, 25.7], "tq2_0": [2.3, 22.7],
+       "mxfp4": [0.6, 33.8], "nvfp4": [1.1, 33.2], "q1_0": [1.0, 17.8], "q4_0+imx": [181.5, 251.4], "q4_1+imx": [646.9, 829.2],
        "q5_0+imx": [181.4, 253.8], "q5_1+imx": [646.9, 831.7], "q8_0+imx": [2.4, 16.2], "q2_K+imx": [873.5, 1267.1],
        "q3_K+imx": [346.6, 547.8], "q4_K+imx": [702.4, 940.8], "q5_K+imx": [702.3, 947.7]}
 SMS, FP32_LANES, ISSUE_SLOTS = 148, 128, 4
