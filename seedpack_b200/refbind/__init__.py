@@ -177,12 +177,16 @@ def _bind_residual(repo3):
     ref_diff, ref_count, ref_tensors = repo3._diff_async, repo3._count_diff, repo3.M28RepoGPU._residual_tensors
     MIN_SPAN = 1 << 20
 
-    class _Done:
-        def __init__(self, v):
-            self.v = v
+    class _Flag:
+        """what `_diff_async` hands back: a future-like whose result is whether the device counter is non-zero; the
+        counter is read when the result is asked for (repo3.py:1120 asks after all of a file's predictions are made),
+        so the comparisons of a file queue up behind one another without a synchronisation each"""
+
+        def __init__(self, counter):
+            self.counter = counter
 
         def result(self, timeout=None):
-            return self.v
+            return int(self.counter.item()) > 0
 
         def done(self):
             return True
@@ -203,7 +207,7 @@ def _bind_residual(repo3):
         da, db = _pair(r, p)
         if da is None:
             return ref_diff(r, p)
-        return [_Done(residual.count_diff(da, db) > 0)]
+        return [_Flag(residual.count_diff(da, db, sync=False))]
 
     def _count_diff(a, b=None):
         da, db = _pair(a, b)
