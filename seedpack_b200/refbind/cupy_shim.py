@@ -703,7 +703,7 @@ class _PinnedPool:
     """page-locked staging buffers, kept and reused by size class: locking pages is slow"""
 
     def __init__(self):
-        self.free, self.lock, self.held, self.roots = {}, threading.Lock(), 0, {}
+        self.free, self.lock, self.held, self.roots = {}, threading.RLock(), 0, {}      # (re-entrant: _give is a finalizer)
 
     @staticmethod
     def size_class(n):

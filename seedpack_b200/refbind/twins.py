@@ -19,7 +19,7 @@ from collections import OrderedDict
 import numpy as np
 
 CAP = 12 << 30
-_lock = threading.Lock()
+_lock = threading.RLock()          # re-entrant: a finalizer (_drop) may run inside register() when the collector wakes there
 _starts = []                       # sorted start addresses
 _ents = OrderedDict()              # start -> (end, device uint8 tensor), oldest first
 _bytes = [0]
@@ -66,7 +66,8 @@ def register(host, dev):
             if s0 == s:
                 break
             evict.append((s0, d0))
-            del _ents[s0]
+            if _ents.pop(s0, None) is None:
+                continue
             _bytes[0] -= e0 - s0
             i = bisect.bisect_left(_starts, s0)
             if i < len(_starts) and _starts[i] == s0:
