@@ -95,16 +95,25 @@ __global__ void __launch_bounds__(64) k_rans_encode(const uint8_t* __restrict__ 
     w.init(slot + cap);
     unsigned x = RANS_L;
     const RansSym* tab = nullptr;
+    RansSym e0 = {0, 0};
     long long cur_block = -1;
+    // The lanes of a warp sit in different segments, hence different tables: a table look-up by all lanes touches 32
+    // cache lines, and with one per symbol the kernel is bound by the L1's line rate, not by its chains.  Most residual
+    // symbols are 0: the current table's entry for 0 is kept in registers, and only the lanes with another symbol load.
     for (long long i = n - 16; i >= 0; i -= 16) {
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(sym + s0 + i));
         const unsigned wv[4] = {v.x, v.y, v.z, v.w};
         const long long blk = (s0 + i) / block_len;                     // 16 | block_len: one table per 16 symbols
-        if (blk != cur_block) { cur_block = blk; tab = enc + (size_t)block_tab[blk] * 256; }
+        if (blk != cur_block) { cur_block = blk; tab = enc + (size_t)block_tab[blk] * 256; e0 = tab[0]; }
 #pragma unroll
         for (int k = 3; k >= 0; --k) {
 #pragma unroll
-            for (int j = 3; j >= 0; --j) rans_put<PB>(x, w, tab[(wv[k] >> (8 * j)) & 0xff]);
+            for (int j = 3; j >= 0; --j) {
+                const unsigned sy = (wv[k] >> (8 * j)) & 0xff;
+                RansSym e = e0;
+                if (sy) e = tab[sy];
+                rans_put<PB>(x, w, e);
+            }
         }
         if (w.ptr() < slot + 64) { out_len[s] = 0xffffffffu; return; }   // 16 symbols write at most 32 bytes
     }
