@@ -281,6 +281,15 @@ SG_API int sg_qr_weight_equal(int device, void *stream, int T, const unsigned ch
                               long long nweights, unsigned char *out);
 SG_API int sg_qr_grid_half_step(int device, void *stream, int T, const unsigned char *F, long long nweights, float *h);
 
+/* M30, sibling quantisations without the model (seedpack/siblings.py:51-77: half_step, est_add, est_seed): element-wise
+ * over n weights.  half_step: h = half the width of [lo, hi] (from sg_qr_intervals), the distance to the finite side when
+ * one is infinite, -1 when both are.  est_add: a version (x, h) into the running sums ws += 1 / max(h^2, 1e-30),
+ * wx += x * that (h < 0: skipped).  est_seed: the explicit QR seed, out[2i] = wx / ws, out[2i + 1] = 1 / sqrt(ws); where
+ * ws is 0: (x0[i], 0). */
+SG_API int sg_sib_half_step(int device, void *stream, const float *x, const float *lo, const float *hi, long long n, float *h);
+SG_API int sg_sib_est_add(int device, void *stream, const float *x, const float *h, long long n, float *ws, float *wx);
+SG_API int sg_sib_est_seed(int device, void *stream, const float *ws, const float *wx, const float *x0, long long n, float *out);
+
 /* ---- M24: the earlier BF16 base codec (archives packed with --method m28) ---------------------------------------------
  * Replaces bf_hist / bf_enc / bf_dec (seedpack/gpu_bf16.py:63-137): 12 probability bits, 160 tables per tensor (128
  * exponent, 16 mantissa, 16 sign), quarter-octave side information.  file = the whole GGUF on the device; records

@@ -77,6 +77,9 @@ SIGNATURES = {
     "sg_m6_decode": (_I, [_I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P]),
     "sg_rans_chain_encode": (_I, [_I, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P]),
     "sg_rans_chain_decode": (_I, [_I, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P]),
+    "sg_sib_half_step": (_I, [_I, _P, _P, _P, _P, _L, _P]),
+    "sg_sib_est_add": (_I, [_I, _P, _P, _P, _L, _P, _P]),
+    "sg_sib_est_seed": (_I, [_I, _P, _P, _P, _P, _L, _P]),
     "sg_m24_hist": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P]),
     "sg_m24_encode": (_I, [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _Z, _P]),
     "sg_m24_decode": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P]),

@@ -16,6 +16,8 @@ raises, so nothing of the reference's CUDA source can run by accident.
                                                        sg_qr_intervals / sg_qr_weight_equal / sg_qr_grid_half_step
     dm_log2 / dm_exp2 / dm_rows / dm_cols   detmath.py:67-106   sg_dm_log2 / sg_dm_exp2 / sg_dm_rows / sg_dm_cols
     dm_rows_d / dm_gram / dm_bdot / dm_solve  detmath.py:86-153  sg_dm_rows_f64 / sg_dm_gram / sg_dm_bdot / sg_dm_solve
+    hist / encode / decode      gpu_codec.py:73-159    sg_m6_hist / sg_m6_encode / sg_m6_decode
+    half_step / est_add / est_seed   siblings.py:51-77   sg_sib_half_step / sg_sib_est_add / sg_sib_est_seed
     k_dq_<type>                 gpuquant.py:215-219    sg_dequantize
     vq_bf16_to_f32 (elementwise) gpuquant.py:248-249   sg_convert_float
 
@@ -292,6 +294,25 @@ def _grid_h(args):
     _lib.check(_lib.lib().sg_qr_grid_half_step(_dev(), _st(), _i(T), _p(F.dev_in()), _i(nw), _p(h.dev_out())), "sg_qr_grid_half_step")
 
 
+# ---- M30 (siblings.py) -----------------------------------------------------------------------------------------------
+def _half_step(args):
+    x, lo, hi, n, h = args
+    _lib.check(_lib.lib().sg_sib_half_step(_dev(), _st(), _p(x.dev_in()), _p(lo.dev_in()), _p(hi.dev_in()), _i(n), _p(h.dev_out())),
+               "sg_sib_half_step")
+
+
+def _est_add(args):
+    x, h, n, ws, wx = args
+    _lib.check(_lib.lib().sg_sib_est_add(_dev(), _st(), _p(x.dev_in()), _p(h.dev_in()), _i(n), _p(ws.dev_inout()), _p(wx.dev_inout())),
+               "sg_sib_est_add")
+
+
+def _est_seed(args):
+    ws, wx, x0, n, out = args
+    _lib.check(_lib.lib().sg_sib_est_seed(_dev(), _st(), _p(ws.dev_in()), _p(wx.dev_in()), _p(x0.dev_in()), _i(n), _p(out.dev_out())),
+               "sg_sib_est_seed")
+
+
 # ---- detmath ---------------------------------------------------------------------------------------------------------
 def _dm_log2(args):
     x, n, y = args
@@ -361,7 +382,8 @@ _BOUND = {"bf_hist": _bf_hist, "bf_enc": _bf_enc, "bf_dec": _bf_dec, "v2_hist": 
           "blocks_from_fields": _blocks_from_fields, "intervals": _intervals, "weq": _weq, "grid_h": _grid_h,
           "dm_log2": _dm_log2, "dm_exp2": _dm_exp2, "dm_rows": _dm_rows, "dm_cols": _dm_cols, "dm_rows_d": _dm_rows_d,
           "dm_gram": _dm_gram, "dm_bdot": _dm_bdot, "dm_solve": _dm_solve,
-          "hist": _m6_hist, "encode": _m6_enc, "decode": _m6_dec}
+          "hist": _m6_hist, "encode": _m6_enc, "decode": _m6_dec,
+          "half_step": _half_step, "est_add": _est_add, "est_seed": _est_seed}
 for _t, (_name, _, _) in QFUN.items():
     _BOUND["k_dq_" + _name[len("quantize_"):]] = _dequant(_t)
 

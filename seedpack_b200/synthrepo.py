@@ -43,6 +43,12 @@ CONFIGS = {
     "c1-mini": dict(layers=4, hidden=1024, ffn=3072, q_heads=16, kv_heads=8, head_dim=128, vocab=4096, tied=True,
                     imatrix=False, shards=1, flip=0.005, alter=0.0,
                     files={"Q8_0": "q8_0", "Q4_K_M": "q4_k_m", "Q6_K": "q6_k"}),
+    # the same without disturbed blocks, for sibling coding without the BF16 file (--method m30): a flipped byte can turn
+    # a block's fp16 scale into a NaN, M30's column statistics over the FILES then hold NaNs, and the payload bits of a
+    # NaN that arithmetic hands on differ between x86 and the GPU (the side information differs in those bits only)
+    "sib-mini": dict(layers=4, hidden=1024, ffn=3072, q_heads=16, kv_heads=8, head_dim=128, vocab=4096, tied=True,
+                     imatrix=False, shards=1, flip=0.0, alter=0.0,
+                     files={"Q8_0": "q8_0", "Q4_K_M": "q4_k_m", "Q6_K": "q6_k"}),
     # one layer of the 0.6B shape and a 4096-token vocabulary: the bounded sample the CPU baseline is timed on
     "c1-micro": dict(layers=1, hidden=1024, ffn=3072, q_heads=16, kv_heads=8, head_dim=128, vocab=4096, tied=True,
                      imatrix=False, shards=1, flip=0.005, alter=0.0,

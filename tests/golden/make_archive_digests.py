@@ -21,7 +21,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 OUT = os.path.join(HERE, "archive_digests.json")
-CONFIGS = ["c1-nano", "c1-mini", "c4-mini", "c5-mini", "fit-mini", "c1-nano@m28"]     # "@m28": packed with --method m28 (M24 base codec)
+# "@m28": packed with --method m28 (M24 base codec); "~nobase@m30": the BF16 file removed, packed with --method m30 (sibling quants)
+CONFIGS = ["c1-nano", "c1-mini", "c4-mini", "c5-mini", "fit-mini", "c1-nano@m28", "sib-mini~nobase@m30"]
 SEED = 1
 
 
@@ -42,7 +43,11 @@ def main(configs):
             repo = os.path.join(tmp, "repo")
             t0 = time.time()
             name, _, method = cfg.partition("@")
-            synthrepo.make_repo(repo, name, lambda ty, bits, w: ref.quantize(ty, ref.bf16_to_f32(bits), w), seed=SEED)
+            name, _, variant = name.partition("~")
+            made = synthrepo.make_repo(repo, name, lambda ty, bits, w: ref.quantize(ty, ref.bf16_to_f32(bits), w), seed=SEED)
+            if variant == "nobase":
+                for p in made["base"]:
+                    os.remove(p)
             t1 = time.time()
             arc = os.path.join(tmp, "a.seedpack")
             env = dict(os.environ, SOURCE_DATE_EPOCH="1700000000")

@@ -11,7 +11,10 @@ seedpack_b200.refbind: $SEEDPACK_REFERENCE or baseline/_ref) run with every kern
     importance matrix (three quant files), the 9B-shaped one with 21 importance-matrix quants and the 27B-shaped one
     in two shards with 24 quants and altered tensor types, at reduced sizes; a repository whose legacy quants were
     made with another importance matrix than the published one (the packer fits it back: seedpack/imxfit.py over
-    sg_dm_gram and friends); and the smallest repository packed with --method m28 (the M24 base codec);
+    sg_dm_gram and friends); the smallest repository packed with --method m28 (the M24 base codec); and the 0.6B shape at reduced size
+    repository WITHOUT its BF16 file packed with --method m30 (seedpack/siblings.py: the quants of a tensor coded in a
+    chain, each predicted from the precision-weighted mean of those before it: sg_sib_* and the QR coder's seedless and
+    explicit-seed paths);
   * both ways on one box: the reference's `--cpu` run packs the smallest repository here too, the archives are
     compared byte for byte, and each side unpacks the OTHER side's archive to files equal to the originals;
   * `test` / `unpack` on the GPU restore every file of every archive (the reference's own BLAKE3 check plus a
@@ -83,7 +86,7 @@ def need_reference():
         pytest.fail("the reference package is not here (baseline/_ref or $SEEDPACK_REFERENCE): archives cannot be made")
 
 
-@pytest.mark.parametrize("config", ["c1-nano", "c1-mini", "c4-mini", "c5-mini", "fit-mini", "c1-nano@m28"])
+@pytest.mark.parametrize("config", ["c1-nano", "c1-mini", "c4-mini", "c5-mini", "fit-mini", "c1-nano@m28", "sib-mini~nobase@m30"])
 def test_archive_equals_the_references(config, tmp_path):
     need_reference()
     from seedpack_b200 import synthrepo
@@ -92,7 +95,11 @@ def test_archive_equals_the_references(config, tmp_path):
     gold = GOLD[config]
     repo = str(tmp_path / "repo")
     name, _, method = config.partition("@")                # "@m28": packed with --method m28 (the M24 base codec)
-    synthrepo.make_repo(repo, name, gpu_quantizer(), seed=gold["seed"])
+    name, _, variant = name.partition("~")                 # "~nobase": the BF16 file removed ("@m30": the quants code one another)
+    made = synthrepo.make_repo(repo, name, gpu_quantizer(), seed=gold["seed"])
+    if variant == "nobase":
+        for p in made["base"]:
+            os.remove(p)
     # the repository itself: every quant file written by the CUDA quantisers equals the one the reference's C code wrote
     assert sorted(os.listdir(repo)) == sorted(gold["files"])
     for n, (size, dg) in gold["files"].items():
