@@ -281,6 +281,68 @@ SG_API int sg_qr_weight_equal(int device, void *stream, int T, const unsigned ch
                               long long nweights, unsigned char *out);
 SG_API int sg_qr_grid_half_step(int device, void *stream, int T, const unsigned char *F, long long nweights, float *h);
 
+/* ---- M21: Q8_0 GGUFs that no base predicts (the seed of a repository without its BF16 model) ----------------------------
+ * Replaces hist_a / enc_a / dec_a / hist_b / enc_b / dec_b (seedpack/gpu2.py:100-262) and predict / predict_multi /
+ * hist_c / enc_c / dec_c (seedpack/gpu3.py:90-232); arguments in the reference's order and meaning.  blocks = Q8_0 blocks
+ * of all tensors back to back, pos[b] = index of block b's largest magnitude, skip[b] = bit 0: not coded, bit 1: its 31
+ * codes belong to phase C, bit 2: so do position and largest code; meta = per tensor { int32 first, nblocks, nb_row, grp,
+ * colbase, rowbase, off, qset } (gpu2.py:56).  flags = the reference module's compile-time switches: bit 0 SIGN, bit 1
+ * RANK, bit 2 HICF, bit 3 PREDA; seg = blocks per segment (SEGA / SEGB).  Tables by raw id (counts / enc_tab / lut from
+ * sg_rans_tables with pb = 12 over the id space of the call); encoders write segment s at the end of slot s of `cap` bytes
+ * (a multiple of 16) and out_len[s] = its bytes, 0xffffffff if the slot was too small (the reference does not look);
+ * decoders take the first and one-past-last stream byte of every segment and report damage through SG_ST_CORRUPT. */
+SG_API int sg_m21_hist_a(int device, void *stream, const unsigned char *blocks, const unsigned char *pos,
+                         const unsigned char *skip, const void *meta, int ntens, int nblocks, const unsigned char *bcf,
+                         const unsigned char *spread, const unsigned char *perm, const unsigned char *rankof,
+                         const unsigned char *scls, int flags, int seg, unsigned *counts);
+SG_API int sg_m21_encode_a(int device, void *stream, const unsigned char *blocks, const unsigned char *pos,
+                           const unsigned char *skip, const void *meta, int ntens, int nblocks, const unsigned char *bcf,
+                           const unsigned char *spread, const unsigned char *perm, const unsigned char *rankof,
+                           const unsigned char *scls, int flags, int seg, const void *enc_tab, unsigned char *slots,
+                           size_t cap, unsigned *out_len);
+SG_API int sg_m21_decode_a(int device, void *stream, const unsigned char *in, const unsigned long long *in_off,
+                           const unsigned long long *in_end, const unsigned char *skip, const void *meta, int ntens,
+                           int nblocks, const unsigned char *bcf, const unsigned char *spread, const unsigned char *perm,
+                           const unsigned char *rankof, const unsigned char *scls, int flags, int seg,
+                           const void *enc_tab, const unsigned char *lut, unsigned char *blocks, unsigned char *pos);
+SG_API int sg_m21_hist_b(int device, void *stream, const unsigned char *blocks, const unsigned char *pos,
+                         const unsigned char *skip, const void *meta, int ntens, int nblocks, const short *cfi,
+                         const unsigned char *scls, const int *row_m, int qbase, int G, int flags, int seg,
+                         unsigned *counts);
+SG_API int sg_m21_encode_b(int device, void *stream, const unsigned char *blocks, const unsigned char *pos,
+                           const unsigned char *skip, const void *meta, int ntens, int nblocks, const short *cfi,
+                           const unsigned char *scls, const int *row_m, int qbase, int flags, int seg,
+                           const void *enc_tab, unsigned char *slots, size_t cap, unsigned *out_len);
+SG_API int sg_m21_decode_b(int device, void *stream, const unsigned char *in, const unsigned long long *in_off,
+                           const unsigned long long *in_end, const unsigned char *skip, const void *meta, int ntens,
+                           int nblocks, const short *cfi, const unsigned char *scls, const int *row_m, int qbase,
+                           int flags, int seg, const void *enc_tab, const unsigned char *lut, unsigned char *blocks,
+                           const unsigned char *pos);
+SG_API int sg_m21_predict(int device, void *stream, const unsigned char *blocks, int first, int nbr, int C,
+                          const int *rows, int nrw, const int *par, const float *coef, int K, const float *mu,
+                          signed char *pint);
+SG_API int sg_m21_predict_multi(int device, void *stream, const unsigned char *blocks, const int *ent_slot,
+                                const int *ent_row, int nent, int CMAX, const int *s_first, const int *s_nbr,
+                                const long long *s_rbase, const long long *s_pbase, const int *s_mubase,
+                                const int *par, const float *coef, int K, const float *mu, signed char *pint);
+SG_API int sg_m21_hist_c(int device, void *stream, const unsigned char *blocks, const unsigned char *pos,
+                         const unsigned char *skip, const void *meta, const int *seg_t, const int *seg_r0,
+                         const int *seg_nr, const int *seg_slot, int nseg, const short *cfi, const int *row_m,
+                         const signed char *fbin, const long long *rbase, const signed char *pint,
+                         const long long *pbase, int flags, unsigned *counts);
+SG_API int sg_m21_encode_c(int device, void *stream, const unsigned char *blocks, const unsigned char *pos,
+                           const unsigned char *skip, const void *meta, const int *seg_t, const int *seg_r0,
+                           const int *seg_nr, const int *seg_slot, int nseg, const short *cfi, const int *row_m,
+                           const signed char *fbin, const long long *rbase, const signed char *pint,
+                           const long long *pbase, int flags, const void *enc_tab, unsigned char *slots, size_t cap,
+                           unsigned *out_len);
+SG_API int sg_m21_decode_c(int device, void *stream, const unsigned char *in, const unsigned long long *in_off,
+                           const unsigned long long *in_end, int seg0, unsigned char *pos, const unsigned char *skip,
+                           const void *meta, const int *seg_t, const int *seg_r0, const int *seg_nr,
+                           const int *seg_slot, int nseg, const short *cfi, const int *row_m, const signed char *fbin,
+                           const long long *rbase, const signed char *pint, const long long *pbase, int flags,
+                           const void *enc_tab, const unsigned char *lut, unsigned char *blocks);
+
 /* M30, sibling quantisations without the model (seedpack/siblings.py:51-77: half_step, est_add, est_seed): element-wise
  * over n weights.  half_step: h = half the width of [lo, hi] (from sg_qr_intervals), the distance to the finite side when
  * one is infinite, -1 when both are.  est_add: a version (x, h) into the running sums ws += 1 / max(h^2, 1e-30),

@@ -77,6 +77,17 @@ SIGNATURES = {
     "sg_m6_decode": (_I, [_I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P]),
     "sg_rans_chain_encode": (_I, [_I, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P]),
     "sg_rans_chain_decode": (_I, [_I, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P]),
+    "sg_m21_hist_a": (_I, [_I, _P] + [_P] * 4 + [_I, _I] + [_P] * 5 + [_I, _I, _P]),
+    "sg_m21_encode_a": (_I, [_I, _P] + [_P] * 4 + [_I, _I] + [_P] * 5 + [_I, _I, _P, _P, _Z, _P]),
+    "sg_m21_decode_a": (_I, [_I, _P] + [_P] * 5 + [_I, _I] + [_P] * 5 + [_I, _I, _P, _P, _P, _P]),
+    "sg_m21_hist_b": (_I, [_I, _P] + [_P] * 4 + [_I, _I] + [_P] * 3 + [_I, _I, _I, _I, _P]),
+    "sg_m21_encode_b": (_I, [_I, _P] + [_P] * 4 + [_I, _I] + [_P] * 3 + [_I, _I, _I, _P, _P, _Z, _P]),
+    "sg_m21_decode_b": (_I, [_I, _P] + [_P] * 5 + [_I, _I] + [_P] * 3 + [_I, _I, _I, _P, _P, _P, _P]),
+    "sg_m21_predict": (_I, [_I, _P, _P, _I, _I, _I, _P, _I, _P, _P, _I, _P, _P]),
+    "sg_m21_predict_multi": (_I, [_I, _P, _P, _P, _P, _I, _I] + [_P] * 7 + [_I, _P, _P]),
+    "sg_m21_hist_c": (_I, [_I, _P] + [_P] * 8 + [_I] + [_P] * 6 + [_I, _P]),
+    "sg_m21_encode_c": (_I, [_I, _P] + [_P] * 8 + [_I] + [_P] * 6 + [_I, _P, _P, _Z, _P]),
+    "sg_m21_decode_c": (_I, [_I, _P, _P, _P, _P, _I] + [_P] * 7 + [_I] + [_P] * 6 + [_I, _P, _P, _P]),
     "sg_sib_half_step": (_I, [_I, _P, _P, _P, _P, _L, _P]),
     "sg_sib_est_add": (_I, [_I, _P, _P, _P, _L, _P, _P]),
     "sg_sib_est_seed": (_I, [_I, _P, _P, _P, _P, _L, _P]),

@@ -776,11 +776,14 @@ class RawModule:
     """nothing is compiled: a function is the C-ABI binding of the reference kernel of that name"""
 
     def __init__(self, code=None, path=None, options=(), **kw):
-        pass
+        # the integer #defines of the reference's source: switches its modules are compiled with (SIGN, RANK, SEGA ...),
+        # which the bindings hand to the library as run-time arguments
+        import re
+        self.defines = {k: int(v) for k, v in re.findall(r"^#define[ \t]+(\w+)[ \t]+(-?\d+)[ \t]*(?://.*)?$", code or "", re.M)}
 
     def get_function(self, name):
         from . import kernels
-        return kernels.function(name)
+        return kernels.function(name, self.defines)
 
     def get_global(self, name):
         raise NotImplementedError(f"device global {name}: the reference's modules are not loaded here")

@@ -18,6 +18,9 @@ raises, so nothing of the reference's CUDA source can run by accident.
     dm_rows_d / dm_gram / dm_bdot / dm_solve  detmath.py:86-153  sg_dm_rows_f64 / sg_dm_gram / sg_dm_bdot / sg_dm_solve
     hist / encode / decode      gpu_codec.py:73-159    sg_m6_hist / sg_m6_encode / sg_m6_decode
     half_step / est_add / est_seed   siblings.py:51-77   sg_sib_half_step / sg_sib_est_add / sg_sib_est_seed
+    hist_a / enc_a / dec_a / hist_b / enc_b / dec_b   gpu2.py:100-262   sg_m21_hist_a / ... / sg_m21_decode_b
+    predict / predict_multi / hist_c / enc_c / dec_c  gpu3.py:90-232    sg_m21_predict / ... / sg_m21_decode_c
+                                (their modules' #define switches - SIGN, RANK, HICF, PREDA, SEGA, SEGB - become arguments)
     k_dq_<type>                 gpuquant.py:215-219    sg_dequantize
     vq_bf16_to_f32 (elementwise) gpuquant.py:248-249   sg_convert_float
 
@@ -294,6 +297,127 @@ def _grid_h(args):
     _lib.check(_lib.lib().sg_qr_grid_half_step(_dev(), _st(), _i(T), _p(F.dev_in()), _i(nw), _p(h.dev_out())), "sg_qr_grid_half_step")
 
 
+# ---- M21 (gpu2.py / gpu3.py: Q8_0 files without a base) -------------------------------------------------------------------
+def _m21_flags(d):
+    return (1 if d.get("SIGN") else 0) | (2 if d.get("RANK") else 0) | (4 if d.get("HICF") else 0) | (8 if d.get("PREDA") else 0)
+
+
+def _m21_tables(remap, freq, lut):
+    return _tables(remap, freq, QR_PB, lut)
+
+
+def _m21_lens(out_len, what):
+    if (out_len._h() == 0xffffffff).any():
+        raise RuntimeError(f"{what}: a segment's code outgrew its slot")
+
+
+def _m21_hist_a(args, d):
+    blocks, pos, skip, meta, ntens, n, bcf, spread, perm, rankof, scls, counts = args
+    _lib.check(_lib.lib().sg_m21_hist_a(_dev(), _st(), _p(blocks.dev_in()), _p(pos.dev_in()), _p(skip.dev_in()), _p(meta.dev_in()), _i(ntens), _i(n),
+                                        _p(bcf.dev_in()), _p(spread.dev_in()), _p(perm.dev_in()), _p(rankof.dev_in()), _p(scls.dev_in()),
+                                        _m21_flags(d), d["SEGA"], _p(counts.dev_inout())), "sg_m21_hist_a")
+
+
+def _m21_enc_a(args, d):
+    blocks, pos, skip, meta, ntens, n, bcf, spread, perm, rankof, scls, remap, freq, cum, out, cap, out_len = args
+    enc, _ = _m21_tables(remap, freq, False)
+    _lib.check(_lib.lib().sg_m21_encode_a(_dev(), _st(), _p(blocks.dev_in()), _p(pos.dev_in()), _p(skip.dev_in()), _p(meta.dev_in()), _i(ntens), _i(n),
+                                          _p(bcf.dev_in()), _p(spread.dev_in()), _p(perm.dev_in()), _p(rankof.dev_in()), _p(scls.dev_in()),
+                                          _m21_flags(d), d["SEGA"], _p(enc), _p(out.dev_out()), _i(cap), _p(out_len.dev_out())), "sg_m21_encode_a")
+    _m21_lens(out_len, "M21 phase A")
+
+
+def _m21_dec_a(args, d):
+    stream, offs, skip, meta, ntens, n, bcf, spread, perm, rankof, scls, remap, freq, cum, lut, blocks, pos = args
+    enc, l = _m21_tables(remap, freq, True)
+    o = offs.dev_in().view(torch.int64)
+    e = _seg_ends(o, stream.size)
+    _lib.check(_lib.lib().sg_m21_decode_a(_dev(), _st(), _p(stream.dev_in()), _p(o), _p(e), _p(skip.dev_in()), _p(meta.dev_in()), _i(ntens), _i(n),
+                                          _p(bcf.dev_in()), _p(spread.dev_in()), _p(perm.dev_in()), _p(rankof.dev_in()), _p(scls.dev_in()),
+                                          _m21_flags(d), d["SEGA"], _p(enc), _p(l), _p(blocks.dev_inout()), _p(pos.dev_inout())), "sg_m21_decode_a")
+    _corrupt("M21 phase A")
+
+
+def _m21_hist_b(args, d):
+    blocks, pos, skip, meta, ntens, n, cfi, scls, row_m, qbase, G, counts = args
+    _lib.check(_lib.lib().sg_m21_hist_b(_dev(), _st(), _p(blocks.dev_in()), _p(pos.dev_in()), _p(skip.dev_in()), _p(meta.dev_in()), _i(ntens), _i(n),
+                                        _p(cfi.dev_in()), _p(scls.dev_in()), _p(row_m.dev_in()), _i(qbase), _i(G), _m21_flags(d), d["SEGB"],
+                                        _p(counts.dev_inout())), "sg_m21_hist_b")
+
+
+def _m21_enc_b(args, d):
+    blocks, pos, skip, meta, ntens, n, cfi, scls, row_m, qbase, G, remap, freq, cum, out, cap, out_len = args
+    enc, _ = _m21_tables(remap, freq, False)
+    _lib.check(_lib.lib().sg_m21_encode_b(_dev(), _st(), _p(blocks.dev_in()), _p(pos.dev_in()), _p(skip.dev_in()), _p(meta.dev_in()), _i(ntens), _i(n),
+                                          _p(cfi.dev_in()), _p(scls.dev_in()), _p(row_m.dev_in()), _i(qbase), _m21_flags(d), d["SEGB"], _p(enc),
+                                          _p(out.dev_out()), _i(cap), _p(out_len.dev_out())), "sg_m21_encode_b")
+    _m21_lens(out_len, "M21 phase B")
+
+
+def _m21_dec_b(args, d):
+    stream, offs, skip, meta, ntens, n, cfi, scls, row_m, qbase, G, remap, freq, cum, lut, blocks, pos = args
+    enc, l = _m21_tables(remap, freq, True)
+    o = offs.dev_in().view(torch.int64)
+    e = _seg_ends(o, stream.size)
+    _lib.check(_lib.lib().sg_m21_decode_b(_dev(), _st(), _p(stream.dev_in()), _p(o), _p(e), _p(skip.dev_in()), _p(meta.dev_in()), _i(ntens), _i(n),
+                                          _p(cfi.dev_in()), _p(scls.dev_in()), _p(row_m.dev_in()), _i(qbase), _m21_flags(d), d["SEGB"], _p(enc), _p(l),
+                                          _p(blocks.dev_inout()), _p(pos.dev_in())), "sg_m21_decode_b")
+    _corrupt("M21 phase B")
+
+
+def _m21_predict(args, d):
+    blocks, first, nbr, C, rows, nrw, par, coef, K, mu, pint = args
+    _lib.check(_lib.lib().sg_m21_predict(_dev(), _st(), _p(blocks.dev_in()), _i(first), _i(nbr), _i(C), _p(rows.dev_in()), _i(nrw), _p(par.dev_in()),
+                                         _p(coef.dev_in()), _i(K), _p(mu.dev_in()), _p(pint.dev_inout())), "sg_m21_predict")
+
+
+def _m21_predict_multi(args, d):
+    blocks, ent_slot, ent_row, nent, CMAX, s_first, s_nbr, s_rbase, s_pbase, s_mubase, par, coef, K, mu, pint = args
+    _lib.check(_lib.lib().sg_m21_predict_multi(_dev(), _st(), _p(blocks.dev_in()), _p(ent_slot.dev_in()), _p(ent_row.dev_in()), _i(nent), _i(CMAX),
+                                               _p(s_first.dev_in()), _p(s_nbr.dev_in()), _p(s_rbase.dev_in()), _p(s_pbase.dev_in()),
+                                               _p(s_mubase.dev_in()), _p(par.dev_in()), _p(coef.dev_in()), _i(K), _p(mu.dev_in()),
+                                               _p(pint.dev_inout())), "sg_m21_predict_multi")
+
+
+def _m21_c_common(a):
+    skip, meta, st, sr, sn, ss, nseg, cfi, row_m, fbin, rbase, pint, pbase = a
+    return (_p(skip.dev_in()), _p(meta.dev_in()), _p(st.dev_in()), _p(sr.dev_in()), _p(sn.dev_in()), _p(ss.dev_in()), _i(nseg), _p(cfi.dev_in()),
+            _p(row_m.dev_in()), _p(fbin.dev_in()), _p(rbase.dev_in()), _p(pint.dev_in()), _p(pbase.dev_in()))
+
+
+def _m21_hist_c(args, d):
+    blocks, pos = args[:2]
+    _lib.check(_lib.lib().sg_m21_hist_c(_dev(), _st(), _p(blocks.dev_in()), _p(pos.dev_in()), *_m21_c_common(args[2:15]), _m21_flags(d),
+                                        _p(args[15].dev_inout())), "sg_m21_hist_c")
+
+
+def _m21_enc_c(args, d):
+    blocks, pos = args[:2]
+    remap, freq, cum, out, cap, out_len = args[15:]
+    enc, _ = _m21_tables(remap, freq, False)
+    _lib.check(_lib.lib().sg_m21_encode_c(_dev(), _st(), _p(blocks.dev_in()), _p(pos.dev_in()), *_m21_c_common(args[2:15]), _m21_flags(d), _p(enc),
+                                          _p(out.dev_out()), _i(cap), _p(out_len.dev_out())), "sg_m21_encode_c")
+    _m21_lens(out_len, "M21 phase C")
+
+
+def _m21_dec_c(args, d):
+    stream, offs, seg0, pos = args[:4]
+    remap, freq, cum, lut, blocks = args[17:]
+    enc, l = _m21_tables(remap, freq, True)
+    o = offs.dev_in().view(torch.int64)
+    e = _DEC_C_ENDS.get(id(offs.st))
+    if e is None or e[0] is not offs.st:
+        _DEC_C_ENDS.clear()
+        e = (offs.st, _seg_ends(o, stream.size))
+        _DEC_C_ENDS[id(offs.st)] = e
+    _lib.check(_lib.lib().sg_m21_decode_c(_dev(), _st(), _p(stream.dev_in()), _p(o), _p(e[1]), _i(seg0), _p(pos.dev_inout()),
+                                          *_m21_c_common(args[4:17]), _m21_flags(d), _p(enc), _p(l), _p(blocks.dev_inout())), "sg_m21_decode_c")
+    _corrupt("M21 phase C")
+
+
+_DEC_C_ENDS = {}           # the segment ends of the stream being decoded wave by wave (256 launches share them)
+
+
 # ---- M30 (siblings.py) -----------------------------------------------------------------------------------------------
 def _half_step(args):
     x, lo, hi, n, h = args
@@ -384,15 +508,21 @@ _BOUND = {"bf_hist": _bf_hist, "bf_enc": _bf_enc, "bf_dec": _bf_dec, "v2_hist": 
           "dm_gram": _dm_gram, "dm_bdot": _dm_bdot, "dm_solve": _dm_solve,
           "hist": _m6_hist, "encode": _m6_enc, "decode": _m6_dec,
           "half_step": _half_step, "est_add": _est_add, "est_seed": _est_seed}
+_BOUND_WITH_DEFINES = {"hist_a": _m21_hist_a, "enc_a": _m21_enc_a, "dec_a": _m21_dec_a, "hist_b": _m21_hist_b, "enc_b": _m21_enc_b,
+                       "dec_b": _m21_dec_b, "predict": _m21_predict, "predict_multi": _m21_predict_multi, "hist_c": _m21_hist_c,
+                       "enc_c": _m21_enc_c, "dec_c": _m21_dec_c}
 for _t, (_name, _, _) in QFUN.items():
     _BOUND["k_dq_" + _name[len("quantize_"):]] = _dequant(_t)
 
 
-def function(name):
+def function(name, defines=None):
     f = _BOUND.get(name)
-    if f is None:
+    g = _BOUND_WITH_DEFINES.get(name)
+    if f is None and g is None:
         raise NotImplementedError(f"kernel '{name}' of the reference has no binding to libseedgrow.so "
                                   "(its CUDA source is never compiled here)")
+    if g is not None:
+        f = lambda args: g(args, defines or {})
 
     def launch(grid, block, args, shared_mem=0):
         f(args)

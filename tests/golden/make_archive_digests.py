@@ -21,8 +21,13 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 OUT = os.path.join(HERE, "archive_digests.json")
-# "@m28": packed with --method m28 (M24 base codec); "~nobase@m30": the BF16 file removed, packed with --method m30 (sibling quants)
-CONFIGS = ["c1-nano", "c1-mini", "c4-mini", "c5-mini", "fit-mini", "c1-nano@m28", "sib-mini~nobase@m30"]
+# "@m28": packed with --method m28 (M24 base codec); "~nobase@m30": the BF16 file removed, packed with --method m30 (sibling quants);
+# "~q8only": the Q8_0 file alone, no BF16 file (the M21 codec of Q8_0 blocks: seed.py, gpu2.py, gpu3.py)
+CONFIGS = ["c1-nano", "c1-mini", "c4-mini", "c5-mini", "fit-mini", "c1-nano@m28", "sib-mini~nobase@m30", "c1-nano~q8only", "c1-mini~q8only",
+           # no BF16 file, default method: the Q8_0 file becomes the seed (seed.py).  The larger case has no disturbed blocks: a
+           # flipped byte that makes a Q8_0 scale infinite or NaN puts non-finite weights into the seed, and quantising those
+           # runs through float -> int conversions that C leaves undefined (x86 and the GPU give different bytes)
+           "c1-nano~nobase", "sib-mini~nobase"]
 SEED = 1
 
 
@@ -44,8 +49,9 @@ def main(configs):
             t0 = time.time()
             name, _, method = cfg.partition("@")
             name, _, variant = name.partition("~")
-            made = synthrepo.make_repo(repo, name, lambda ty, bits, w: ref.quantize(ty, ref.bf16_to_f32(bits), w), seed=SEED)
-            if variant == "nobase":
+            made = synthrepo.make_repo(repo, name, lambda ty, bits, w: ref.quantize(ty, ref.bf16_to_f32(bits), w), seed=SEED,
+                                       only=["Q8_0"] if variant == "q8only" else None)
+            if variant in ("nobase", "q8only"):
                 for p in made["base"]:
                     os.remove(p)
             t1 = time.time()

@@ -86,7 +86,8 @@ def need_reference():
         pytest.fail("the reference package is not here (baseline/_ref or $SEEDPACK_REFERENCE): archives cannot be made")
 
 
-@pytest.mark.parametrize("config", ["c1-nano", "c1-mini", "c4-mini", "c5-mini", "fit-mini", "c1-nano@m28", "sib-mini~nobase@m30"])
+@pytest.mark.parametrize("config", ["c1-nano", "c1-mini", "c4-mini", "c5-mini", "fit-mini", "c1-nano@m28", "sib-mini~nobase@m30",
+                                    "c1-nano~q8only", "c1-mini~q8only", "c1-nano~nobase", "sib-mini~nobase"])
 def test_archive_equals_the_references(config, tmp_path):
     need_reference()
     from seedpack_b200 import synthrepo
@@ -96,8 +97,10 @@ def test_archive_equals_the_references(config, tmp_path):
     repo = str(tmp_path / "repo")
     name, _, method = config.partition("@")                # "@m28": packed with --method m28 (the M24 base codec)
     name, _, variant = name.partition("~")                 # "~nobase": the BF16 file removed ("@m30": the quants code one another)
-    made = synthrepo.make_repo(repo, name, gpu_quantizer(), seed=gold["seed"])
-    if variant == "nobase":
+    # "~nobase" with no method: the Q8_0 file takes the BF16 file's place as the seed the other files are predicted from (seed.py);
+    # "~q8only": the Q8_0 file alone with no BF16 file, which the reference packs with its M21 codec of Q8_0 blocks
+    made = synthrepo.make_repo(repo, name, gpu_quantizer(), seed=gold["seed"], only=["Q8_0"] if variant == "q8only" else None)
+    if variant in ("nobase", "q8only"):
         for p in made["base"]:
             os.remove(p)
     # the repository itself: every quant file written by the CUDA quantisers equals the one the reference's C code wrote
@@ -146,3 +149,21 @@ def test_single_pass_kernel_bindings_give_the_same_archive(tmp_path):
     r = subprocess.run([sys.executable, "-m", "seedpack_b200.refbind", "test", arc], cwd=tmp_path, env=env, capture_output=True, text=True,
                        timeout=1500)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_disturbed_seed_round_trips(tmp_path):
+    """a repository without its BF16 file whose Q8_0 seed has disturbed blocks (some scales infinite or NaN, so the weights
+    the other files are re-quantised from are not finite): the archive is not compared with x86's - C leaves the float ->
+    int conversions of such values undefined - but packing, testing and unpacking on the GPU give the files back"""
+    need_reference()
+    from seedpack_b200 import synthrepo
+    repo = str(tmp_path / "repo")
+    made = synthrepo.make_repo(repo, "c1-mini", gpu_quantizer(), seed=1)
+    for p in made["base"]:
+        os.remove(p)
+    arc = str(tmp_path / "gpu.seedpack")
+    bound("pack", "-q", "-o", arc, repo, cwd=tmp_path)
+    bound("test", arc, cwd=tmp_path)
+    out = str(tmp_path / "out")
+    bound("unpack", "-o", out, arc, cwd=tmp_path)
+    same_tree(repo, out)

@@ -100,4 +100,9 @@ def test_array_module_residency_and_views():
     assert z.get().tolist() == [[0, 1, 1], [0, 1, 1]]
     with pytest.raises(NotImplementedError):
         cp.RawModule(code="").get_function("some_kernel_of_the_reference")
+    # the integer switches a module's source is compiled with travel to the bindings (M21: SIGN, RANK, SEGA ...)
+    m = cp.RawModule(code="#define PB 12\n#define SEGA 4096   // blocks a segment\n#define SIGN 1\n#define TWICE (2 * PB)\nextern \"C\" {}\n")
+    assert m.defines == {"PB": 12, "SEGA": 4096, "SIGN": 1}
+    from seedpack_b200.refbind import kernels
+    assert kernels._m21_flags({"SIGN": 1, "HICF": 1, "RANK": 0}) == 5 and kernels._m21_flags({"PREDA": 1, "RANK": 1}) == 10
     assert cp.uint8 is np.uint8 and isinstance(a, cp.ndarray)
