@@ -89,6 +89,10 @@ def install(reference=None, staged_qr=None):
     _bind_residual(repo3)
     from seedpack import rans
     _bind_rans(rans)
+    from seedpack import detmath, gpu3
+    from . import plan
+    gpu3.GPU3._row_matrix = plan.row_matrix       # M21's row planner: device twins of two chains of array operations
+    gpu3.GPU3._plan_tensor = plan.make(detmath)
     _state["pkg"] = seedpack
     return seedpack
 

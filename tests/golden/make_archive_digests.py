@@ -23,7 +23,7 @@ sys.path.insert(0, ROOT)
 OUT = os.path.join(HERE, "archive_digests.json")
 # "@m28": packed with --method m28 (M24 base codec); "~nobase@m30": the BF16 file removed, packed with --method m30 (sibling quants);
 # "~q8only": the Q8_0 file alone, no BF16 file (the M21 codec of Q8_0 blocks: seed.py, gpu2.py, gpu3.py)
-CONFIGS = ["c1-nano", "c1-mini", "c4-mini", "c5-mini", "fit-mini", "c1-nano@m28", "sib-mini~nobase@m30", "c1-nano~q8only", "c1-mini~q8only",
+CONFIGS = ["c1-nano", "c1-mini", "c4-mini", "c5-mini", "fit-mini", "c1-nano@m28", "sib-mini~nobase@m30", "c1-nano~q8only", "sib-mini~q8only",
            # no BF16 file, default method: the Q8_0 file becomes the seed (seed.py).  The larger case has no disturbed blocks: a
            # flipped byte that makes a Q8_0 scale infinite or NaN puts non-finite weights into the seed, and quantising those
            # runs through float -> int conversions that C leaves undefined (x86 and the GPU give different bytes)

@@ -87,7 +87,7 @@ def need_reference():
 
 
 @pytest.mark.parametrize("config", ["c1-nano", "c1-mini", "c4-mini", "c5-mini", "fit-mini", "c1-nano@m28", "sib-mini~nobase@m30",
-                                    "c1-nano~q8only", "c1-mini~q8only", "c1-nano~nobase", "sib-mini~nobase"])
+                                    "c1-nano~q8only", "sib-mini~q8only", "c1-nano~nobase", "sib-mini~nobase"])
 def test_archive_equals_the_references(config, tmp_path):
     need_reference()
     from seedpack_b200 import synthrepo
