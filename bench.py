@@ -415,9 +415,11 @@ def _reference_cli():
 PACK_METRIC = "pack/unpack GB/s of GGUF bytes"
 
 
-def pack_config(repo, gpus):
+def pack_config(repo, gpus, without_base="no"):
     """the `config` object of the pack workload, the same in this library's line and in the reference arm's"""
-    return {"workload": _repo_text(repo) + (", one repository per GPU" if gpus > 1 else ""),
+    less = {"no": "", "all": "; the BF16 file removed before packing (the Q8_0 file is the seed)",
+            "q8": "; the Q8_0 file alone, no BF16 file (M21)"}[without_base]
+    return {"workload": _repo_text(repo) + less + (", one repository per GPU" if gpus > 1 else ""),
             "step": "pack + test of the repository; bytes per step = 2 x repository bytes",
             "l2": "inputs larger than L2 (base 1.2 GB, files 1.5 GB)"}
 SAMPLE = "c1-micro"
@@ -495,8 +497,14 @@ def run_pack(args):
     try:
         os.environ.setdefault("SOURCE_DATE_EPOCH", "1700000000")
         repo = os.path.join(tmp, "repo")
-        made = synthrepo.make_repo(repo, args.repo, quantize, seed=1 + rank, keep_weights=True)
+        made = synthrepo.make_repo(repo, args.repo, quantize, seed=1 + rank, keep_weights=args.without_base == "no",
+                                   only=["Q8_0"] if args.without_base == "q8" else None)
         nbytes = made["bytes"]
+        base_bytes = sum(os.path.getsize(p) for p in made["base"])
+        if args.without_base != "no":               # the Q8_0 file becomes the seed: M21 codes it, the others follow from it
+            for p in made["base"]:
+                os.remove(p)
+            nbytes = sum(os.path.getsize(os.path.join(repo, n)) for n in os.listdir(repo))
         arc = os.path.join(tmp, "a.seedpack")
         refbind.install()
         from seedpack import cli
@@ -557,7 +565,7 @@ def run_pack(args):
                     "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
                     "wall_ms_per_step": wall / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                     "dtype": "f32", "data": "synthetic",
-                    "config": pack_config(args.repo, world),
+                    "config": pack_config(args.repo, world, args.without_base),
                     "value_is": "bytes over the summed device time of the step's library calls (CUDA events around each call); e2e is the wall clock",
                     "repository_bytes": int(nbytes), "library_calls": per,
                     "clocks": clocks,
@@ -566,9 +574,9 @@ def run_pack(args):
                             "unpack_gbs": nbytes_all * args.steps / tu / 1e9},
                     "bit_exact_files": f"{exact}/{total}", "archive_sha256": _file_digest(arc),
                     "gpu_launches": int(sum(v[1] for v in calls.values())),
-                    "roofline": pack_roofline(per, dom, args, peak, peak_kind, clocks, sum(os.path.getsize(p) for p in made["base"]),
+                    "roofline": pack_roofline(per, dom, args, peak, peak_kind, clocks, base_bytes if args.without_base == "no" else 0,
                                               os.path.getsize(arc))}
-            line["cpu_baseline"] = pack_cpu_baseline(args, tmp, quantize, cli) if world == 1 else None
+            line["cpu_baseline"] = pack_cpu_baseline(args, tmp, quantize, cli) if world == 1 and args.without_base == "no" else None
             if world == 1 and not args.no_kernels:
                 line["kernels"] = kernel_workloads(args)
             print(json.dumps(line))
@@ -1015,6 +1023,9 @@ def main():
     ap.add_argument("--shard-types", default="", help="shard: comma-separated ggml type ids (default: the 20 types of the reference's table)")
     ap.add_argument("--no-kernels", action="store_true", help="pack: leave the kernel-level workloads out of the line")
     ap.add_argument("--repo", default="c1", help="pack: synthetic repository (a key of seedpack_b200.synthrepo.CONFIGS)")
+    ap.add_argument("--without-base", default="no", choices=["no", "all", "q8"],
+                    help="pack: remove the BF16 file before packing (all: every quant file stays; q8: the Q8_0 file alone) - a side line, "
+                         "not the benchmark's workload")
     ap.add_argument("--repo-dir", default="", help="--impl reference: an existing repository directory to pack instead of making the sample")
     ap.add_argument("--symbols", type=int, default=1 << 30, help="rans: symbols in the stream")
     ap.add_argument("--tensors", type=int, default=4, help="qr / r2: tensors of the benchmark shape in the batch / file")

@@ -290,7 +290,9 @@ SG_API int sg_qr_grid_half_step(int device, void *stream, int T, const unsigned 
  * RANK, bit 2 HICF, bit 3 PREDA; seg = blocks per segment (SEGA / SEGB).  Tables by raw id (counts / enc_tab / lut from
  * sg_rans_tables with pb = 12 over the id space of the call); encoders write segment s at the end of slot s of `cap` bytes
  * (a multiple of 16) and out_len[s] = its bytes, 0xffffffff if the slot was too small (the reference does not look);
- * decoders take the first and one-past-last stream byte of every segment and report damage through SG_ST_CORRUPT. */
+ * decoders take the first and one-past-last stream byte of every segment and report damage through SG_ST_CORRUPT.
+ * sg_m21_decode_c decodes segments seg0 .. nseg - 1 (one wave of the format per call), one segment per CTA with the
+ * tables of its 64 (88 with PREDA) contexts rebuilt in shared memory from enc_tab; its `lut` is not read and may be NULL. */
 SG_API int sg_m21_hist_a(int device, void *stream, const unsigned char *blocks, const unsigned char *pos,
                          const unsigned char *skip, const void *meta, int ntens, int nblocks, const unsigned char *bcf,
                          const unsigned char *spread, const unsigned char *perm, const unsigned char *rankof,

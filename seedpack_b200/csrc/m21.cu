@@ -394,39 +394,107 @@ __global__ void __launch_bounds__(64) k_enc_c(const unsigned char* __restrict__ 
     out_len[s] = wr.finish(sl + cap);
 }
 
-__global__ void __launch_bounds__(64) k_dec_c(const unsigned char* __restrict__ in, const unsigned long long* __restrict__ in_off,
-                                              const unsigned long long* __restrict__ in_end, int seg0, unsigned char* __restrict__ pos,
-                                              const unsigned char* __restrict__ skip, const Meta* __restrict__ M, SegC sg, int nseg, SideC sd, Opt o,
-                                              const RansSym* __restrict__ enc, const unsigned char* __restrict__ lut, unsigned char* __restrict__ blocks,
-                                              int* __restrict__ status) {
-    const int s = seg0 + blockIdx.x * blockDim.x + threadIdx.x;
+// Phase C decoder: ONE segment per CTA.  A wave of the format has a few hundred segments at most and waves decode one
+// after another, so the launch is as long as one segment's chain; what shortens it is taking the loads off the chain:
+//   * the slot's tables go to shared memory in the compact form of rans.cuh (256 coarse entries + the symbols' freq | cum
+//     words, 1.25 KiB a table), built here by the whole CTA from the encoder entries, so that a symbol costs two or three
+//     shared-memory reads instead of two dependent global ones;
+//   * the 32 lanes of warp 0 fetch a block's predictions and contexts side by side (and rank the predictions, where the
+//     largest code's position is coded by rank) and hand them to lane 0, which runs the chain; all lanes store the codes.
+constexpr int DEC_C_THREADS = 128;
+static inline size_t dec_c_smem(int ntab) { return (size_t)ntab * RANS_COMPACT + 96; }
+
+__global__ void __launch_bounds__(DEC_C_THREADS) k_dec_c(const unsigned char* __restrict__ in, const unsigned long long* __restrict__ in_off,
+                                                         const unsigned long long* __restrict__ in_end, int seg0, unsigned char* __restrict__ pos,
+                                                         const unsigned char* __restrict__ skip, const Meta* __restrict__ M, SegC sg, int nseg, SideC sd,
+                                                         Opt o, const RansSym* __restrict__ enc, unsigned char* __restrict__ blocks,
+                                                         int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char sm[];
+    const int s = seg0 + blockIdx.x;
     if (s >= nseg) return;
-    const int t = sg.t[s], slot = sg.slot[s], nbr = M[t].nb_row, C = nbr * 32, tb = slot * tables_c(o);
+    const int t = sg.t[s], slot = sg.slot[s], ntab = tables_c(o), tb = slot * ntab;
+    unsigned char* ct = sm;
+    unsigned char* st_ctx = sm + (size_t)ntab * RANS_COMPACT;       // 32 contexts, 32 predictions, 32 decoded codes
+    unsigned char* st_pr = st_ctx + 32;
+    unsigned char* st_out = st_ctx + 64;
+    for (int i = threadIdx.x; i < ntab * 64; i += blockDim.x)
+        reinterpret_cast<unsigned*>(ct + (size_t)(i >> 6) * RANS_COMPACT)[i & 63] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < ntab * 256; i += blockDim.x) {
+        const int tt = i >> 8, sy = i & 255;
+        const unsigned fc = enc[(size_t)(tb + tt) * 256 + sy].fc, f = fc & 0xffffu, cu = fc >> 16;
+        unsigned char* c = ct + (size_t)tt * RANS_COMPACT;
+        reinterpret_cast<unsigned*>(c + 256)[sy] = fc;
+        if (f) for (unsigned bk = (cu + 15) >> 4; bk < 256 && (bk << 4) < cu + f; ++bk) c[bk] = (unsigned char)sy;   // buckets that begin in the range
+    }
+    __syncthreads();
+    if (threadIdx.x >= 32) return;
+    const unsigned FULL = 0xffffffffu;
+    const int lane = threadIdx.x;
+    const Meta mt = M[t];
+    const int nbr = mt.nb_row, C = nbr * 32;
     const signed char* fb = sd.fbin + sd.rbase[slot];
     const signed char* pi = sd.pint + sd.pbase[slot];
-    ByteReaderUp rd; rd.init(in + in_off[s], in + in_end[s]);
-    unsigned x = rans_init(rd);
-    auto get = [&](int tab) { return (int)rans_get<12>(x, rd, lut + ((size_t)tab << 12), enc + (size_t)tab * 256); };
-    for (int r = sg.r0[s]; r < sg.r0[s] + sg.nr[s] && !rd.over; ++r)
-        for (int kk = 0; kk < nbr; ++kk) {
-            const size_t b = (size_t)M[t].first + (size_t)r * nbr + kk;
+    ByteReaderUp rd;
+    unsigned x = RANS_L;
+    if (lane == 0) { rd.init(in + in_off[s], in + in_end[s]); x = rans_init(rd); }
+    else rd.init(in, in);
+    bool stop = false;
+    for (int r = sg.r0[s]; r < sg.r0[s] + sg.nr[s] && !stop; ++r) {
+        const int fbr = fb[r], rm = sd.row_m[mt.rowbase + r];
+        for (int kk = 0; kk < nbr && !stop; ++kk) {
+            const size_t b = (size_t)mt.first + (size_t)r * nbr + kk;
             if (skip[b] & 1) continue;
             unsigned char* blk = blocks + b * 34;
-            const int sh = sd.row_m[M[t].rowbase + r] - (blk[0] | (blk[1] << 8)) - M[t].off;
-            const signed char* pr = pi + (size_t)r * C + kk * 32;
+            const int sh = rm - (blk[0] | (blk[1] << 8)) - mt.off;
+            const int prj = pi[(size_t)r * C + kk * 32 + lane];
+            st_ctx[lane] = (unsigned char)clamp63(magnitude_bin(sd.cfi[mt.colbase + kk * 32 + lane], sh) + fbr);
+            st_pr[lane] = (unsigned char)prj;
             int p;
             if (o.preda) {
-                p = pos_of_rank(pr, get(tb + 64 + rank_ctx(pr)));
-                blk[2 + p] = (unsigned char)get(tb + 72 + mx_ctx(pr, p));
-                pos[b] = (unsigned char)p;
+                const int ap = abs(prj);
+                int rk = 0, mx = ap;                    // rank of this position among the |predictions|: descending, ties by index
+                for (int k = 0; k < 32; ++k) {
+                    const int a = __shfl_sync(FULL, ap, k);
+                    rk += (a > ap) || (a == ap && k < lane);
+                    mx = max(mx, a);
+                }
+                int sym = 0;
+                if (lane == 0) sym = (int)rans_get_compact<12>(x, rd, ct + (size_t)(64 + min(mx / 16, 7)) * RANS_COMPACT);
+                sym = __shfl_sync(FULL, sym, 0);
+                const unsigned hit = __ballot_sync(FULL, rk == sym);
+                p = hit ? __ffs(hit) - 1 : 0;
+                const int vp = __shfl_sync(FULL, prj, p);
+                int val = 0;
+                if (lane == 0) val = (int)rans_get_compact<12>(x, rd, ct + (size_t)(72 + (vp < 0) * 8 + min(abs(vp) / 16, 7)) * RANS_COMPACT);
+                val = __shfl_sync(FULL, val, 0);
+                if (lane == p) blk[2 + p] = (unsigned char)val;
+                if (lane == 0) pos[b] = (unsigned char)p;
             } else p = pos[b];
-            for (int j = 0; j < 32; ++j) {
-                if (j == p) continue;
-                const int ctx = clamp63(magnitude_bin(sd.cfi[M[t].colbase + kk * 32 + j], sh) + fb[r]);
-                blk[2 + j] = (unsigned char)((pr[j] + get(tb + ctx)) & 255);
+            __syncwarp();
+            if (lane == 0) {
+                const uint4 c0 = reinterpret_cast<const uint4*>(st_ctx)[0], c1 = reinterpret_cast<const uint4*>(st_ctx)[1];
+                const uint4 p0 = reinterpret_cast<const uint4*>(st_pr)[0], p1 = reinterpret_cast<const uint4*>(st_pr)[1];
+                const unsigned cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                const unsigned pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+                unsigned ow[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if (j == p) continue;
+                    const unsigned cx = (cw[j >> 2] >> (8 * (j & 3))) & 0xffu;
+                    const int pv = (int)(signed char)((pw[j >> 2] >> (8 * (j & 3))) & 0xffu);
+                    const unsigned sy = rans_get_compact<12>(x, rd, ct + (size_t)cx * RANS_COMPACT);
+                    ow[j >> 2] |= ((unsigned)(pv + (int)sy) & 255u) << (8 * (j & 3));
+                }
+                reinterpret_cast<uint4*>(st_out)[0] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                reinterpret_cast<uint4*>(st_out)[1] = make_uint4(ow[4], ow[5], ow[6], ow[7]);
             }
+            __syncwarp();
+            if (lane != p) blk[2 + lane] = st_out[lane];
+            stop = __shfl_sync(FULL, (int)rd.over, 0) != 0;
         }
-    if (rd.over || x != RANS_L || rd.p != rd.end) atomicOr(status, SG_ST_CORRUPT);
+    }
+    if (lane == 0 && (rd.over || x != RANS_L || rd.p != rd.end)) atomicOr(status, SG_ST_CORRUPT);
 }
 
 static unsigned grid_of(long long n, int per) { return (unsigned)((n + per - 1) / per); }
@@ -599,13 +667,17 @@ extern "C" int sg_m21_decode_c(int device, void* stream, const unsigned char* in
                                const long long* rbase, const signed char* pint, const long long* pbase, int flags, const void* enc_tab,
                                const unsigned char* lut, unsigned char* blocks) {
     int rc = common_c(blocks, pos, skip, meta, seg_t, seg_r0, seg_nr, seg_slot, nseg, cfi, row_m, fbin, rbase, pint, pbase);
-    if (rc != SG_OK || !in || !in_off || !in_end || !enc_tab || !lut || seg0 < 0) return SG_ERR_ARG;
+    (void)lut;                                   // the kernel builds its own compact tables from the encoder entries
+    if (rc != SG_OK || !in || !in_off || !in_end || !enc_tab || seg0 < 0) return SG_ERR_ARG;
     if ((uintptr_t)in % 16) return SG_ERR_ALIGN;
     if (nseg <= seg0) return SG_OK;
     if ((rc = use_device(device)) != SG_OK) return rc;
     const m21::SegC sg = {seg_t, seg_r0, seg_nr, seg_slot};
     const m21::SideC sd = {cfi, row_m, fbin, rbase, pint, pbase};
-    m21::k_dec_c<<<m21::grid_of(nseg - seg0, 64), 64, 0, (cudaStream_t)stream>>>(in, in_off, in_end, seg0, pos, skip, (const Meta*)meta, sg, nseg, sd,
-                                                                                opt_of(flags), (const RansSym*)enc_tab, lut, blocks, status_word(device));
+    const size_t smem = m21::dec_c_smem(64 + ((flags & 8) ? 24 : 0));
+    if ((rc = cuda_ok(cudaFuncSetAttribute(m21::k_dec_c, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem))) != SG_OK) return rc;
+    m21::k_dec_c<<<(unsigned)(nseg - seg0), m21::DEC_C_THREADS, smem, (cudaStream_t)stream>>>(in, in_off, in_end, seg0, pos, skip, (const Meta*)meta, sg,
+                                                                                             nseg, sd, opt_of(flags), (const RansSym*)enc_tab, blocks,
+                                                                                             status_word(device));
     return cuda_ok(cudaGetLastError());
 }

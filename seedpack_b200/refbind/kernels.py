@@ -403,7 +403,7 @@ def _m21_enc_c(args, d):
 def _m21_dec_c(args, d):
     stream, offs, seg0, pos = args[:4]
     remap, freq, cum, lut, blocks = args[17:]
-    enc, l = _m21_tables(remap, freq, True)
+    enc, l = _m21_tables(remap, freq, False)                  # the decoder keeps compact tables in shared memory: no symbol table
     o = offs.dev_in().view(torch.int64)
     e = _DEC_C_ENDS.get(id(offs.st))
     if e is None or e[0] is not offs.st:
