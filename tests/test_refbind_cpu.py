@@ -76,6 +76,26 @@ def test_reference_over_the_array_module_gives_the_reference_archive(tmp_path):
     same_tree(repo, out_b)
 
 
+@pytest.mark.skipif(not (_have_reference() and _have_oracle()), reason="needs the reference package (baseline/_ref or "
+                    "$SEEDPACK_REFERENCE) and oracle/_ref")
+def test_row_planner_twin_gives_the_reference_archive(tmp_path):
+    """a Q8_0 file without a base goes through M21, whose phase C plans the token embedding's rows: the binding's twin of
+    that planner (refbind/plan.py, here on CPU tensors) must lead to the archive the reference's own planner leads to"""
+    from oracle import ref
+    from seedpack_b200 import synthrepo
+    repo = str(tmp_path / "repo")
+    made = synthrepo.make_repo(repo, "c1-nano", lambda ty, bits, w: ref.quantize(ty, ref.bf16_to_f32(bits), w), seed=3, only=["Q8_0"])
+    for p in made["base"]:
+        os.remove(p)
+    a, b = str(tmp_path / "cpu.seedpack"), str(tmp_path / "emu.seedpack")
+    run("cpu", "pack", "--cpu", "-q", "-o", a, repo, cwd=tmp_path)
+    r = run("emu", "pack", "-q", "-o", b, repo, cwd=tmp_path)
+    assert digest(a) == digest(b)
+    out = str(tmp_path / "out")
+    run("emu", "unpack", "-o", out, a, cwd=tmp_path)
+    same_tree(repo, out)
+
+
 def test_array_module_residency_and_views():
     """cupy_shim.ndarray on the host side only (no device is touched while nothing asks for one)"""
     from seedpack_b200.refbind import cupy_shim as cp

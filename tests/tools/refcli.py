@@ -87,6 +87,10 @@ def run_emu(argv):
     xp.CPU = True                        # GPUQuant builds its CPU module (no NVRTC); arrays stay the binding's
     from seedpack import gpuquant
     gpuquant.xp.CPU = True
+    # the binding's twin of M21's row planner (refbind/plan.py), here on CPU tensors over the reference's CPU detmath kernels
+    from seedpack import detmath, gpu3
+    from seedpack_b200.refbind import plan
+    gpu3.GPU3._plan_tensor = plan.make(detmath)
     from seedpack.cli import main
     sys.argv = ["seedpack"] + argv
     main()
