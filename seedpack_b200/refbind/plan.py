@@ -55,117 +55,161 @@ def row_matrix(self, allb, f, nb, rowlen):
     return W.reshape(-1, rowlen)
 
 
-def make(detmath):
-    """-> plan_tensor(self, W, valid) over the reference's detmath module"""
+class Planner:
+    """one matrix's plan, step by step on the device.  dm = the reference's detmath module (bound kernels); codec = the
+    GPU3 instance whose class constants (WAVES, K, NCAND, COEF_BITS, ADAPTIVE_K, COLRES) choose the variant"""
+    SEARCH_ROWS = 512          # rows whose products with all earlier rows are held at once
+    FIT_ROWS = 2048            # rows fitted per batch of small systems
+    UNIT_ROWS = 8192
 
-    def f64(a):
-        return dev(a).clone()
+    def __init__(self, dm, codec, W, valid):
+        self.dm, self.codec, self.W = dm, codec, W
+        self.n, self.cols = W.shape
+        self.Wt = dev(W, write=True)
+        self.valid = valid
+        self.ok = dev(valid if valid.dtype == np.bool_ else valid.astype(np.bool_))
+        self.D = self.Wt.device
+        self.row = torch.arange(self.n, device=self.D)
+        wave = (self.row * codec.WAVES) // self.n
+        self.wave_first = torch.searchsorted(wave, wave, right=False)          # first row of each row's wave
+
+    def sums(self, a, *more, **kw):
+        """a detmath reduction -> float64 tensor of its result"""
+        return dev(a(*more, **kw)).clone()
+
+    def centre(self):
+        """subtract the mean of the valid rows (in place) -> (mean float32, column energy before centring)"""
+        count = max(float(int(self.ok.sum())), 1.0)
+        mean = div(self.sums(self.dm.cols, self.W, mask=self.valid), count).to(torch.float32)
+        energy = self.dm.cols(self.W, True, mask=self.valid)
+        self.Wt -= mean
+        return mean, energy
+
+    def unit_rows(self):
+        """rows scaled to unit length and rounded to int8 (exact similarities afterwards); rows left out are zero"""
+        U = torch.empty((self.n, self.cols), dtype=torch.int8, device=self.D)
+        for a in range(0, self.n, self.UNIT_ROWS):
+            x = self.Wt[a:a + self.UNIT_ROWS]
+            length = torch.clamp_min(torch.sqrt(self.sums(self.dm.rows, arr(x), True)), 1e-12)[:, None]
+            U[a:a + self.UNIT_ROWS] = torch.clamp(torch.round(x.to(torch.float64) / length * 127), -127, 127).to(torch.int8)
+        U[~self.ok] = 0
+        return U
+
+    def nearest(self, U):
+        """-> (n, K) int32: the K most similar valid rows of earlier waves, best first, -1 where there is none.  A product
+        of int8 rows over at most SIM_COLS columns is an integer below 2^24, exact in an fp32 GEMM whatever its order; the
+        key puts the lower row first among equal products, as a first-maximum search does"""
+        K = min(self.codec.NCAND, self.codec.K)
+        parents = torch.full((self.n, self.codec.K), -1, dtype=torch.int32, device=self.D)
+        first = self.wave_first.cpu().numpy()
+        bits = max(self.n.bit_length(), 1)
+        step = self.dm.SIM_COLS
+        parts = [U[:, c:c + step].float() for c in range(0, self.cols, step)]
+        keep = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            for a in range(0, self.n, self.SEARCH_ROWS):
+                b = min(a + self.SEARCH_ROWS, self.n)
+                m = int(first[b - 1])
+                if m == 0:
+                    continue
+                dots = None
+                for part in parts:
+                    d = (part[a:b] @ part[:m].T).to(torch.int64)
+                    dots = d if dots is None else dots + d
+                key = dots * (1 << bits) + ((1 << bits) - 1 - self.row[:m])[None, :]
+                allowed = (self.row[None, :m] < self.wave_first[a:b, None]) & self.ok[None, :m]
+                key = torch.where(allowed, key, torch.full_like(key, _LOW))
+                line = torch.arange(b - a, device=self.D)
+                for k in range(K):
+                    top, at = key.max(1)
+                    parents[a:b, k] = torch.where(top > _LOW, at, torch.full_like(at, -1)).to(torch.int32)
+                    key[line, at] = _LOW
+                del dots, key, allowed
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = keep
+        return parents
+
+    def stored(self, c):
+        """coefficients as the archive holds them: fp16, or int8 in steps of 1/64"""
+        if self.codec.COEF_BITS == 16:
+            return c.to(torch.float16).to(torch.float32)
+        return div(torch.clamp(torch.round(c * 64), -127, 127), 64)
+
+    def fit(self, parents):
+        """least squares of every row on its parents -> (energy left / energy float32, parents used int32,
+        coefficients (n, K) float32, column energy of what is left float64)"""
+        dm, K, D = self.dm, self.codec.K, self.D
+        left = torch.ones(self.n, dtype=torch.float32, device=D)
+        weights = torch.zeros((self.n, K), dtype=torch.float32, device=D)
+        used = torch.zeros(self.n, dtype=torch.int32, device=D)
+        col_left = torch.zeros(self.cols, dtype=torch.float64, device=D)
+        side_bits = 17 + self.codec.COEF_BITS
+        free = self.cols - self.cols // 32                                      # codes the prediction helps: all but one a block
+        for a in range(0, self.n, self.FIT_ROWS):
+            b = min(a + self.FIT_ROWS, self.n)
+            y = self.Wt[a:b]
+            y_arr = arr(y)
+            energy = torch.clamp_min(self.sums(dm.rows, y_arr, True), 1e-12)
+            pa = parents[a:b]
+            P = self.Wt[torch.clamp_min(pa, 0).long()] * (pa >= 0)[..., None]
+            win_left = torch.ones(b - a, dtype=torch.float64, device=D)
+            win_k = torch.zeros(b - a, dtype=torch.int32, device=D)
+            win_c = torch.zeros((b - a, K), dtype=torch.float32, device=D)
+            win_bits = torch.zeros(b - a, dtype=torch.float64, device=D)       # no parent: 0 bits against itself
+            win_rest = y.clone()
+            for k in (range(1, K + 1) if self.codec.ADAPTIVE_K else (K,)):
+                X = P[:, :k].contiguous()
+                X_arr = arr(X)
+                normal = dev(dm.gram(X_arr)) + (1e-3 * torch.eye(k, dtype=torch.float32, device=D))[None]
+                c = self.stored(dev(dm.solve(arr(normal), dm.bdot(X_arr, y_arr))))
+                rest = y.clone()
+                for q in range(k):                                              # product and difference rounded apart, in index order
+                    rest = rest - c[:, q, None] * X[:, q, :]
+                share = torch.clamp(self.sums(dm.rows, arr(rest), True) / energy, 1e-3, 4)
+                bits = 0.5 * self.sums(dm.log2, arr(share)) * free + k * side_bits
+                wins = bits < win_bits
+                win_bits = torch.where(wins, bits, win_bits)
+                win_left = torch.where(wins, share, win_left)
+                win_k = torch.where(wins, torch.full_like(win_k, k), win_k)
+                padded = torch.zeros((b - a, K), dtype=torch.float32, device=D)
+                padded[:, :k] = c
+                win_c = torch.where(wins[:, None], padded, win_c)
+                win_rest = torch.where(wins[:, None], rest, win_rest)
+            left[a:b] = win_left.to(torch.float32)
+            used[a:b] = win_k
+            weights[a:b] = win_c
+            col_left += self.sums(dm.cols, arr(win_rest), True, mask=arr(self.ok[a:b]))
+        return left, used, weights, col_left
+
+    def classes(self, left, col_left, energy):
+        """-> (row class int8, column adjustment int8): quarter octaves of the energy the prediction leaves"""
+        dm = self.dm
+        if self.codec.COLRES:
+            whole = float(dm.total(arr(col_left))) / max(float(dm.total(energy)), 1e-30)
+            ratio = torch.clamp_min(col_left / torch.clamp_min(dev(energy), 1e-30), 1e-6)
+            col_adj = torch.clamp(torch.round(4 * self.sums(dm.log2, arr(ratio))), -60, 0).to(torch.int8)
+            row_cls = torch.clamp(torch.round(self.sums(dm.log2, arr(div(left, max(whole, 1e-6)))) * 4), -40, 20).to(torch.int8)
+        else:
+            col_adj = torch.zeros(self.cols, dtype=torch.int8, device=self.D)
+            row_cls = torch.clamp(torch.round(self.sums(dm.log2, arr(left)) * 4), -40, 0).to(torch.int8)
+        return row_cls, col_adj
+
+
+def make(detmath):
+    """-> the replacement of GPU3._plan_tensor(self, W, valid) over the reference's detmath module: parents (n, K) int32,
+    coefficients (n, K) float32, row classes int8, column means float32, column adjustments int8"""
 
     def plan_tensor(self, W, valid):
-        n, C = W.shape
-        P, K, NC = self.WAVES, self.K, self.NCAND
-        Wt = dev(W, write=True)
-        vt = dev(valid.astype(np.bool_) if valid.dtype != np.bool_ else valid)
-        D = Wt.device
-        idx = torch.arange(n, device=D)
-        wave = (idx * P) // n
-        wstart = torch.searchsorted(wave, wave, right=False)                    # first row of the row's wave
-        nvalid = float(int(vt.sum()))
-        mu = div(f64(detmath.cols(W, mask=valid)), max(nvalid, 1.0)).to(torch.float32)
-        col_w = detmath.cols(W, True, mask=valid)
-        Wt -= mu                                                                # centred in place
-        Wq = torch.empty((n, C), dtype=torch.int8, device=D)
-        for i in range(0, n, 8192):
-            x = Wt[i:i + 8192]
-            nrm = torch.clamp_min(torch.sqrt(f64(detmath.rows(arr(x), True))), 1e-12)[:, None]
-            Wq[i:i + 8192] = torch.clamp(torch.round(x.to(torch.float64) / nrm * 127), -127, 127).to(torch.int8)
-        Wq[~vt] = 0
-        # the K most similar valid rows of earlier waves; ties go to the lower row as arg-max over the products does
-        par = torch.full((n, K), -1, dtype=torch.int32, device=D)
-        CH = 512
-        ws_host = wstart.cpu().numpy()
-        sh = max(n.bit_length(), 1)                                             # key = product, then the lower row first
-        tf32 = torch.backends.cuda.matmul.allow_tf32
-        torch.backends.cuda.matmul.allow_tf32 = False                           # the products must be exact
-        Wf = [Wq[:, c0:c0 + detmath.SIM_COLS].float() for c0 in range(0, C, detmath.SIM_COLS)]
-        for i in range(0, n, CH):
-            j = min(i + CH, n)
-            m = int(ws_host[j - 1])
-            if m == 0:
-                continue
-            S = None
-            for part in Wf:                                                     # every partial sum an integer below 2^24
-                p = (part[i:j] @ part[:m].T).to(torch.int64)
-                S = p if S is None else S + p
-            key = S * (1 << sh) + ((1 << sh) - 1 - idx[:m])[None, :]
-            ok = (idx[None, :m] < wstart[i:j, None]) & vt[None, :m]
-            key = torch.where(ok, key, torch.full_like(key, _LOW))
-            rows = torch.arange(j - i, device=D)
-            for k in range(min(NC, K)):
-                best, at = key.max(1)
-                par[i:j, k] = torch.where(best > _LOW, at, torch.full_like(at, -1)).to(torch.int32)
-                key[rows, at] = _LOW
-            del S, key, ok
-        del Wf
-        torch.backends.cuda.matmul.allow_tf32 = tf32
-        frac = torch.ones(n, dtype=torch.float32, device=D)
-        coefs = torch.zeros((n, K), dtype=torch.float32, device=D)
-        kuse = torch.zeros(n, dtype=torch.int32, device=D)
-        col_res = torch.zeros(C, dtype=torch.float64, device=D)
-        cost_side = 17 + self.COEF_BITS
-        for i in range(0, n, 2048):
-            j = min(i + 2048, n)
-            r = j - i
-            y = Wt[i:j]
-            ya = arr(y)
-            yy = torch.clamp_min(f64(detmath.rows(ya, True)), 1e-12)
-            pj = par[i:j]
-            Xa = Wt[torch.clamp_min(pj, 0).long()] * (pj >= 0)[..., None]
-            best = torch.ones(r, dtype=torch.float64, device=D)
-            bestk = torch.zeros(r, dtype=torch.int32, device=D)
-            bestc = torch.zeros((r, K), dtype=torch.float32, device=D)
-            best_cost = torch.zeros(r, dtype=torch.float64, device=D)           # cost (bits) of no parent
-            res_best = y.clone()
-            for k in (range(1, K + 1) if self.ADAPTIVE_K else (K,)):
-                X = Xa[:, :k].contiguous()
-                Xs = arr(X)
-                A = dev(detmath.gram(Xs)) + (1e-3 * torch.eye(k, dtype=torch.float32, device=D))[None]
-                c = dev(detmath.solve(arr(A), detmath.bdot(Xs, ya)))
-                if self.COEF_BITS == 16:
-                    c = c.to(torch.float16).to(torch.float32)
-                else:
-                    c = div(torch.clamp(torch.round(c * 64), -127, 127), 64)
-                res = y.clone()
-                for kk in range(k):                                             # in a fixed order, product and difference rounded apart
-                    res = res - c[:, kk, None] * X[:, kk, :]
-                f = torch.clamp(f64(detmath.rows(arr(res), True)) / yy, 1e-3, 4)
-                cost = 0.5 * f64(detmath.log2(arr(f))) * (C - C // 32) + k * cost_side
-                better = cost < best_cost
-                best_cost = torch.where(better, cost, best_cost)
-                best = torch.where(better, f, best)
-                bestk = torch.where(better, torch.full_like(bestk, k), bestk)
-                cpad = torch.zeros((r, K), dtype=torch.float32, device=D)
-                cpad[:, :k] = c
-                bestc = torch.where(better[:, None], cpad, bestc)
-                res_best = torch.where(better[:, None], res, res_best)
-            frac[i:j] = best.to(torch.float32)
-            kuse[i:j] = bestk
-            coefs[i:j] = bestc
-            col_res += f64(detmath.cols(arr(res_best), True, mask=arr(vt[i:j])))
-        valid_par = (torch.arange(K, device=D)[None, :] < kuse[:, None]) & vt[:, None]
-        par = torch.where(valid_par, par, torch.full_like(par, -1))
-        coefs = torch.where(valid_par, coefs, torch.zeros_like(coefs))
-        frac = torch.where(kuse > 0, frac, torch.ones_like(frac))
-        if self.COLRES:
-            # column factor of the residual (1/8 octave of RMS) and row class relative to the mean
-            cw = dev(col_w)
-            gfrac = float(detmath.total(arr(col_res))) / max(float(detmath.total(col_w)), 1e-30)
-            ratio = torch.clamp_min(col_res / torch.clamp_min(cw, 1e-30), 1e-6)
-            cadj = torch.clamp(torch.round(4 * f64(detmath.log2(arr(ratio)))), -60, 0).to(torch.int8)
-            fbin = torch.clamp(torch.round(f64(detmath.log2(arr(div(frac, max(gfrac, 1e-6))))) * 4), -40, 20).to(torch.int8)
-        else:
-            cadj = torch.zeros(C, dtype=torch.int8, device=D)
-            fbin = torch.clamp(torch.round(f64(detmath.log2(arr(frac))) * 4), -40, 0).to(torch.int8)
-        return arr(par), arr(coefs), arr(fbin), arr(mu), arr(cadj)
+        pl = Planner(detmath, self, W, valid)
+        mean, energy = pl.centre()
+        parents = pl.nearest(pl.unit_rows())
+        left, used, weights, col_left = pl.fit(parents)
+        live = (torch.arange(self.K, device=pl.D)[None, :] < used[:, None]) & pl.ok[:, None]
+        parents = torch.where(live, parents, torch.full_like(parents, -1))
+        weights = torch.where(live, weights, torch.zeros_like(weights))
+        left = torch.where(used > 0, left, torch.ones_like(left))
+        row_cls, col_adj = pl.classes(left, col_left, energy)
+        return arr(parents), arr(weights), arr(row_cls), arr(mean), arr(col_adj)
 
     return plan_tensor
