@@ -63,6 +63,8 @@ SG_DEVINL int magnitude_bin(int cf, int sh) {
 SG_DEVINL int clamp63(int v) { return v < 0 ? 0 : (v > 63 ? 63 : v); }
 
 // ---- phase A ---------------------------------------------------------------------------------------------------------
+// (column classes, spreads and column-block factors come from the archive's side information: 16 of each by format, masked
+// to that range where they select a table)
 struct SideA { const unsigned char* bcf; const unsigned char* spread; const unsigned char* perm; const unsigned char* rankof; const unsigned char* scls; };
 struct TabA {
     int lo, pos, mx, per_group;
@@ -75,11 +77,11 @@ SG_DEVINL int symbols_a(const unsigned char* __restrict__ blocks, const unsigned
     const int inrow = (b - m.first) % m.nb_row;
     const int cb = m.colbase / 32 + inrow, c0 = m.colbase + inrow * 32, base = m.grp * ta.per_group;
     const int hi = blk[1], p = pos[b];
-    out[0] = (unsigned)(base + prev + (o.hicf ? 256 * sd.bcf[cb] : 0)) << 8 | (unsigned)hi;
+    out[0] = (unsigned)(base + prev + (o.hicf ? 256 * (sd.bcf[cb] & 15) : 0)) << 8 | (unsigned)hi;
     out[1] = (unsigned)(base + ta.lo + hi) << 8 | blk[0];
     if (skip[b] & 4) return 2;
-    out[2] = o.rank ? (unsigned)(base + ta.pos + sd.spread[cb]) << 8 | sd.rankof[cb * 32 + p] : (unsigned)(base + ta.pos) << 8 | (unsigned)p;
-    out[3] = (unsigned)(base + ta.mx + (o.sign ? sd.scls[c0 + p] : 0)) << 8 | blk[2 + p];
+    out[2] = o.rank ? (unsigned)(base + ta.pos + (sd.spread[cb] & 15)) << 8 | sd.rankof[cb * 32 + p] : (unsigned)(base + ta.pos) << 8 | (unsigned)p;
+    out[3] = (unsigned)(base + ta.mx + (o.sign ? (sd.scls[c0 + p] & 15) : 0)) << 8 | blk[2 + p];
     return 4;
 }
 
@@ -151,15 +153,15 @@ __global__ void __launch_bounds__(64) k_dec_a(const unsigned char* __restrict__ 
         const int inrow = (b - m.first) % m.nb_row;
         const int cb = m.colbase / 32 + inrow, c0 = m.colbase + inrow * 32, base = m.grp * ta.per_group;
         if (inrow == 0 || b == (int)b0) prev = 0;
-        const int hi = get(base + prev + (o.hicf ? 256 * sd.bcf[cb] : 0));
+        const int hi = get(base + prev + (o.hicf ? 256 * (sd.bcf[cb] & 15) : 0));
         const int lo = get(base + ta.lo + hi);
         blk[0] = (unsigned char)lo; blk[1] = (unsigned char)hi; prev = hi;
         if (!(skip[b] & 4)) {
             int p;
-            if (o.rank) p = sd.perm[cb * 32 + (get(base + ta.pos + sd.spread[cb]) & 31)];
+            if (o.rank) p = sd.perm[cb * 32 + (get(base + ta.pos + (sd.spread[cb] & 15)) & 31)];
             else p = get(base + ta.pos);
             p &= 31;
-            const int mx = get(base + ta.mx + (o.sign ? sd.scls[c0 + p] : 0));
+            const int mx = get(base + ta.mx + (o.sign ? (sd.scls[c0 + p] & 15) : 0));
             blk[2 + p] = (unsigned char)mx; pos[b] = (unsigned char)p;
         }
     }
@@ -195,7 +197,7 @@ __global__ void __launch_bounds__(64) k_hist_b(const unsigned char* __restrict__
             if (o.sign) {
                 const int mag = v < 0 ? -v : v;
                 atomicAdd(counts + (size_t)(qb + pb) * 256 + mag, 1u);
-                if (mag) atomicAdd(counts + (size_t)(qb + 64 + pb * 16 + sd.scls[c]) * 256 + (v < 0), 1u);
+                if (mag) atomicAdd(counts + (size_t)(qb + 64 + pb * 16 + (sd.scls[c] & 15)) * 256 + (v < 0), 1u);
             } else atomicAdd(counts + (size_t)(qb + pb) * 256 + (v + 128), 1u);
         }
     }
@@ -225,7 +227,7 @@ __global__ void __launch_bounds__(64) k_enc_b(const unsigned char* __restrict__ 
             const int c = c0 + j, pb = magnitude_bin(sd.cfi[c], sh), v = (signed char)blk[2 + j];
             if (o.sign) {
                 const int mag = v < 0 ? -v : v;
-                if (mag) rans_put<12>(x, wr, enc[(size_t)(qb + 64 + pb * 16 + sd.scls[c]) * 256 + (v < 0)]);
+                if (mag) rans_put<12>(x, wr, enc[(size_t)(qb + 64 + pb * 16 + (sd.scls[c] & 15)) * 256 + (v < 0)]);
                 rans_put<12>(x, wr, enc[(size_t)(qb + pb) * 256 + mag]);
             } else rans_put<12>(x, wr, enc[(size_t)(qb + pb) * 256 + (v + 128)]);
         }
@@ -260,7 +262,7 @@ __global__ void __launch_bounds__(64) k_dec_b(const unsigned char* __restrict__ 
             int v;
             if (o.sign) {
                 const int mag = get(qb + pb);
-                const int neg = mag ? get(qb + 64 + pb * 16 + sd.scls[c]) : 0;
+                const int neg = mag ? get(qb + 64 + pb * 16 + (sd.scls[c] & 15)) : 0;
                 v = neg ? -mag : mag;
             } else v = get(qb + pb) - 128;
             blk[2 + j] = (unsigned char)(v & 0xff);
