@@ -37,3 +37,14 @@ def test_extra_golden_equals_reference_c_code():
         y = ref.quantize(t, x, None, threads=1)
         assert np.array_equal(y, g[f"q_{t}"]), t
         assert np.array_equal(ref.dequantize(t, y, x.size).view(np.uint32), g[f"d_{t}"].view(np.uint32)), t
+
+
+def test_pack_config_names_the_workload():
+    """both arms print the same `config`; the side lines without the BF16 file say so in it"""
+    sys.path.insert(0, ROOT)
+    import bench
+    base = bench.pack_config("c1", 1)
+    assert "0.5% of blocks disturbed" in base["workload"] and "one repository per GPU" not in base["workload"]
+    assert bench.pack_config("c1", 8)["workload"].endswith("one repository per GPU")
+    assert "Q8_0 file alone" in bench.pack_config("c1", 1, "q8")["workload"] and "BF16 file removed" in bench.pack_config("c1", 1, "all")["workload"]
+    assert bench.pack_config("c1", 1, "no") == base
